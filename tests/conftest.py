@@ -1,0 +1,24 @@
+import importlib
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200 box)")
+
+
+@pytest.fixture(scope="session")
+def adb():
+    return importlib.import_module("autodiff-ir-rust_b200")
+
+
+@pytest.fixture()
+def oracle_device():
+    from oracle.oracle import OracleDevice
+    return OracleDevice()
