@@ -11,5 +11,5 @@ Layout:
   devices.py   `B200`: the `Device` implementation (execute + get_tensor) over the C-ABI
   configs.py   the five benchmark programs and their seeded synthetic inputs
 """
-from . import ir, autodiff, nn  # noqa: F401
+from . import ir, autodiff, nn, configs  # noqa: F401
 from . import devices  # noqa: F401

@@ -778,11 +778,15 @@ class ViewNode(_UnaryBase):
         self.target_dim = list(target_dim)
 
     def forward(self):
-        # upstream checks the cached field, not val(): a view is never re-emitted (view.rs:19-27)
-        if self._val is not None:
-            return self._val.clone()
-        v = self.parent.forward()
-        res = _c_view(v, self.target_dim, None)
+        # Divergence from upstream: there the cached field is returned unconditionally
+        # (src/graph/data/view.rs:19-27), so a reshape inside a loop condition is never
+        # re-forwarded and the condition goes stale.  Here a view re-forwards like every other
+        # node (same result id), which is what `.all()` inside `ir_while` needs.
+        v = self.val()
+        if v is not None:
+            return v
+        p = self.parent.forward()
+        res = _c_view(p, self.target_dim, self._val.id if self._val is not None else None)
         self._val = res.clone()
         return res
 

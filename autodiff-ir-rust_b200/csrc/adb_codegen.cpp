@@ -1,0 +1,473 @@
+// CUDA source for the fused kernels of a plan.
+//
+// The reference emits one OpenCL C string per kernel and builds it at first use
+// (src/devices/opencl/kernels/{unary,binary,movement,reduce,fuse_elw,fuse_reduce_elw}.rs,
+// cache in src/devices/opencl/context.rs:90-106): one work-item per output element, scalar loads,
+// index expressions spelled out with / and %.  Here the skeletons are hand-written for sm_100a
+// (128-bit loads/stores, grid-stride loops sized to the 148 SMs, warp-shuffle + shared-memory
+// reduction trees, a column-sum variant whose lanes run along the contiguous axis) and only the
+// straight-line SSA body between load and store is spliced in from the plan.
+//
+// Arithmetic contract (matches the CPU restatement of the reference semantics):
+//   + and * are __fadd_rn / __fmul_rn (never contracted into FMA), 1/x is __frcp_rn,
+//   sqrt is __fsqrt_rn(fabsf(x)), comparisons give 1.0f / 0.0f against 0.0f
+//   (src/devices/opencl/kernels/unary.rs:3-17), exp2f / log2f / sinf are CUDA's (<= 2 ulp).
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <sstream>
+
+#include "adb_lower.hpp"
+
+namespace adb {
+
+namespace {
+
+struct Access {
+    enum Mode { SCALAR, VEC4, GATHER } mode = SCALAR;
+    int64_t lane_stride = 0;  // GATHER: element stride between the 4 lanes
+};
+
+std::string hexf(float v) {
+    uint32_t bits;
+    std::memcpy(&bits, &v, 4);
+    char buf[48];
+    std::snprintf(buf, sizeof buf, "__int_as_float(0x%08x)", bits);
+    return buf;
+}
+
+bool needs_wide(int64_t n, const std::vector<const Operand*>& ops) {
+    if (n >= (int64_t(1) << 31) - 1024) return true;
+    for (auto* o : ops) {
+        int64_t m = 0;
+        for (auto& s : o->subs) m += (s.size - 1) * std::max<int64_t>(s.stride, 0);
+        for (auto& s : o->xsubs) m += (s.size - 1) * std::max<int64_t>(s.stride, 0);
+        if (m >= (int64_t(1) << 31) - 1024) return true;
+    }
+    return false;
+}
+
+// offset expression of a digit list from index variable `iv` (outermost digit needs no modulo)
+std::string offset_expr(const std::vector<Sub>& subs, const std::string& iv, std::ostringstream& pre,
+                        const std::string& tag, const char* idx_t) {
+    if (subs.empty()) return "0";
+    if (subs.size() == 1) {
+        if (subs[0].stride == 0) return "0";
+        if (subs[0].stride == 1) return iv;
+        return iv + " * " + std::to_string(subs[0].stride);
+    }
+    std::string r = "r_" + tag;
+    pre << "      " << idx_t << " " << r << " = " << iv << ";\n";
+    std::string expr;
+    for (size_t t = subs.size(); t-- > 1;) {
+        std::string d = "d_" + tag + "_" + std::to_string(t);
+        pre << "      " << idx_t << " " << d << " = " << r << " % " << subs[t].size << "; " << r << " /= " << subs[t].size << ";\n";
+        if (subs[t].stride != 0) {
+            if (!expr.empty()) expr += " + ";
+            expr += subs[t].stride == 1 ? d : d + " * " + std::to_string(subs[t].stride);
+        }
+    }
+    if (subs[0].stride != 0) {
+        if (!expr.empty()) expr += " + ";
+        expr += subs[0].stride == 1 ? r : r + " * " + std::to_string(subs[0].stride);
+    }
+    return expr.empty() ? "0" : expr;
+}
+
+Access classify(const std::vector<Sub>& subs, int64_t offset, int vec, bool is_store) {
+    Access a;
+    if (vec == 1) return a;
+    if (subs.empty()) { a.mode = Access::SCALAR; return a; }
+    const Sub& in = subs.back();
+    if (in.stride == 0 && !is_store) { a.mode = Access::SCALAR; return a; }
+    bool aligned = offset % 4 == 0;
+    for (size_t i = 0; i + 1 < subs.size(); i++)
+        if (subs[i].stride % 4) aligned = false;
+    if (in.stride == 1 && aligned) { a.mode = Access::VEC4; return a; }
+    a.mode = Access::GATHER;
+    a.lane_stride = in.stride;
+    return a;
+}
+
+// can the innermost digit of every operand hold 4 consecutive lanes?
+bool lanes_ok(const std::vector<Sub>& subs) { return subs.empty() || subs.back().size % 4 == 0; }
+
+void emit_ssa(std::ostringstream& o, const KernelSpec& k, int vec, const std::vector<std::string>& load_names,
+              const std::vector<Access>& acc, const char* ind) {
+    static const char L[4] = {'x', 'y', 'z', 'w'};
+    for (size_t i = 0; i < k.ssa.size(); i++) {
+        const Ssa& s = k.ssa[i];
+        for (int l = 0; l < vec; l++) {
+            std::string lhs = "v" + std::to_string(i) + "_" + std::to_string(l);
+            o << ind << "const float " << lhs << " = ";
+            if (s.kind == Ssa::LOAD) {
+                const std::string& nm = load_names[s.operand];
+                if (vec == 1 || acc[s.operand].mode == Access::SCALAR) o << nm;
+                else if (acc[s.operand].mode == Access::VEC4) o << nm << "." << L[l];
+                else o << nm << "_" << l;
+            } else if (s.kind == Ssa::CONST) {
+                o << hexf(s.c);
+            } else {
+                std::string a = "v" + std::to_string(s.a) + "_" + std::to_string(l);
+                std::string b = s.b >= 0 ? "v" + std::to_string(s.b) + "_" + std::to_string(l) : "";
+                switch (s.op) {
+                case E_ADD: o << "__fadd_rn(" << a << ", " << b << ")"; break;
+                case E_MUL: o << "__fmul_rn(" << a << ", " << b << ")"; break;
+                case E_EXP2: o << "exp2f(" << a << ")"; break;
+                case E_LOG2: o << "log2f(" << a << ")"; break;
+                case E_SIN: o << "sinf(" << a << ")"; break;
+                case E_RECIP: o << "__frcp_rn(" << a << ")"; break;
+                case E_SQRT: o << "__fsqrt_rn(fabsf(" << a << "))"; break;
+                case E_EQZ: o << "(" << a << " == 0.0f ? 1.0f : 0.0f)"; break;
+                case E_GTZ: o << "(" << a << " > 0.0f ? 1.0f : 0.0f)"; break;
+                case E_LTZ: o << "(" << a << " < 0.0f ? 1.0f : 0.0f)"; break;
+                }
+            }
+            o << ";\n";
+        }
+    }
+}
+
+void emit_loads(std::ostringstream& o, const KernelSpec& k, int vec, const std::vector<Access>& acc,
+                const std::vector<std::string>& off, std::vector<std::string>& names, const char* ind) {
+    names.resize(k.ins.size());
+    for (size_t i = 0; i < k.ins.size(); i++) {
+        std::string nm = "l" + std::to_string(i);
+        names[i] = nm;
+        std::string p = "a.in[" + std::to_string(i) + "]";
+        if (vec == 1 || acc[i].mode == Access::SCALAR)
+            o << ind << "const float " << nm << " = " << p << "[" << off[i] << "];\n";
+        else if (acc[i].mode == Access::VEC4)
+            o << ind << "const float4 " << nm << " = *reinterpret_cast<const float4*>(" << p << " + (" << off[i] << "));\n";
+        else
+            for (int l = 0; l < 4; l++)
+                o << ind << "const float " << nm << "_" << l << " = " << p << "[(" << off[i] << ") + " << l * acc[i].lane_stride << "];\n";
+    }
+}
+
+uint64_t fnv(const std::string& s) {
+    uint64_t h = 1469598103934665603ull;
+    for (unsigned char c : s) { h ^= c; h *= 1099511628211ull; }
+    return h;
+}
+
+void finish(KernelSpec& k, const std::string& body, const char* prefix) {
+    char name[64];
+    std::snprintf(name, sizeof name, "%s_%016llx", prefix, (unsigned long long)fnv(body));
+    k.entry = name;
+    std::string src = body;
+    size_t p;
+    while ((p = src.find("@ENTRY@")) != std::string::npos) src.replace(p, 7, name);
+    k.source = src;
+}
+
+// -------------------------------------------------------------------------------- element-wise
+void gen_elw(KernelSpec& k) {
+    std::vector<const Operand*> ops;
+    for (auto& i : k.ins) ops.push_back(&i);
+    for (auto& o : k.outs) ops.push_back(&o.dst);
+    k.wide_index = needs_wide(k.n, ops);
+    const char* idx_t = k.wide_index ? "long long" : "unsigned int";
+    int vec = 4;
+    if (k.n % 4) vec = 1;
+    for (auto* o : ops)
+        if (!lanes_ok(o->subs)) vec = 1;
+    for (auto& o : k.outs)
+        if (o.dst.subs.empty() || o.dst.subs.back().stride == 0) vec = 1;
+    k.vec = vec;
+    k.threads = 256;
+
+    std::vector<Access> in_acc(k.ins.size()), out_acc(k.outs.size());
+    for (size_t i = 0; i < k.ins.size(); i++) in_acc[i] = classify(k.ins[i].subs, k.ins[i].offset, vec, false);
+    for (size_t i = 0; i < k.outs.size(); i++) out_acc[i] = classify(k.outs[i].dst.subs, k.outs[i].dst.offset, vec, true);
+
+    std::ostringstream o;
+    o << "struct Args { const float* in[" << std::max<size_t>(1, k.ins.size()) << "]; float* out[" << k.outs.size()
+      << "]; long long n; };\n";
+    o << "extern \"C\" __global__ void __launch_bounds__(256) @ENTRY@(const __grid_constant__ Args a) {\n";
+    o << "  const " << idx_t << " nv = (" << idx_t << ")(a.n / " << vec << ");\n";
+    o << "  for (" << idx_t << " j = blockIdx.x * 256u + threadIdx.x; j < nv; j += (" << idx_t << ")gridDim.x * 256u) {\n";
+    o << "      const " << idx_t << " i = j * " << vec << ";\n";
+    // offsets, shared between operands with the same digits
+    std::vector<std::pair<std::vector<Sub>, std::string>> seen;
+    auto offset_of = [&](const std::vector<Sub>& subs) {
+        for (auto& s : seen)
+            if (s.first == subs) return s.second;
+        std::ostringstream pre;
+        std::string tag = std::to_string(seen.size());
+        std::string e = offset_expr(subs, "i", pre, tag, idx_t);
+        o << pre.str();
+        std::string var = "o" + tag;
+        o << "      const " << idx_t << " " << var << " = " << e << ";\n";
+        seen.push_back({subs, var});
+        return var;
+    };
+    std::vector<std::string> in_off(k.ins.size()), out_off(k.outs.size());
+    for (size_t i = 0; i < k.ins.size(); i++) in_off[i] = offset_of(k.ins[i].subs);
+    for (size_t i = 0; i < k.outs.size(); i++) out_off[i] = offset_of(k.outs[i].dst.subs);
+    std::vector<std::string> names;
+    emit_loads(o, k, vec, in_acc, in_off, names, "      ");
+    emit_ssa(o, k, vec, names, in_acc, "      ");
+    for (size_t i = 0; i < k.outs.size(); i++) {
+        std::string p = "a.out[" + std::to_string(i) + "]";
+        std::string v = "v" + std::to_string(k.outs[i].ssa);
+        if (vec == 1)
+            o << "      " << p << "[" << out_off[i] << "] = " << v << "_0;\n";
+        else if (out_acc[i].mode == Access::VEC4)
+            o << "      *reinterpret_cast<float4*>(" << p << " + (" << out_off[i] << ")) = make_float4(" << v << "_0, " << v
+              << "_1, " << v << "_2, " << v << "_3);\n";
+        else
+            for (int l = 0; l < 4; l++)
+                o << "      " << p << "[(" << out_off[i] << ") + " << l * out_acc[i].lane_stride << "] = " << v << "_" << l << ";\n";
+    }
+    o << "  }\n}\n";
+    finish(k, o.str(), "adb_elw");
+}
+
+// -------------------------------------------------------------------------------- reduce
+int64_t pow2_floor(int64_t v) {
+    int64_t p = 1;
+    while (p * 2 <= v) p *= 2;
+    return p;
+}
+
+int64_t footprint(const Operand& o) {
+    int64_t n = 1;
+    for (auto& s : o.subs) if (s.stride) n *= s.size;
+    for (auto& s : o.xsubs) if (s.stride) n *= s.size;
+    return n;
+}
+
+void gen_reduce(KernelSpec& k) {
+    std::vector<const Operand*> ops;
+    for (auto& i : k.ins) ops.push_back(&i);
+    ops.push_back(&k.outs[0].dst);
+    k.wide_index = needs_wide(std::max(k.n, k.r) * std::max<int64_t>(1, k.split), ops) || k.n * k.r >= (int64_t(1) << 31);
+    const char* idx_t = k.wide_index ? "long long" : "unsigned int";
+    const int64_t R = k.r, S = k.split;
+    const int64_t chunk = (R + S - 1) / S;  // summed elements per partial
+    std::ostringstream o;
+    o << "struct Args { const float* in[" << std::max<size_t>(1, k.ins.size()) << "]; float* out[1]; long long n; };\n";
+
+    if (k.mode == 0) {
+        // lanes along the summed axis: TPR threads cooperate on one row, 256/TPR rows per block
+        int vec = k.vec;
+        const int TPR = k.threads;  // threads per row (power of two <= 256)
+        const int RPB = 256 / TPR;
+        std::vector<Access> acc(k.ins.size());
+        for (size_t i = 0; i < k.ins.size(); i++) acc[i] = classify(k.ins[i].subs, k.ins[i].offset, vec, false);
+        if (vec == 4)
+            for (size_t i = 0; i < k.ins.size(); i++)
+                if (acc[i].mode == Access::VEC4)
+                    for (auto& s : k.ins[i].xsubs)
+                        if (s.stride % 4) { acc[i].mode = Access::GATHER; acc[i].lane_stride = 1; }
+        o << "extern \"C\" __global__ void __launch_bounds__(256) @ENTRY@(const __grid_constant__ Args a) {\n";
+        if (TPR > 32) o << "  __shared__ float sm[8];\n";
+        o << "  const unsigned int lane = threadIdx.x % " << TPR << "u, rib = threadIdx.x / " << TPR << "u;\n";
+        o << "  const " << idx_t << " V = (" << idx_t << ")a.n;\n";
+        o << "  const " << idx_t << " ybeg = (" << idx_t << ")blockIdx.y * " << chunk << ";\n";
+        o << "  const " << idx_t << " yend = ybeg + " << chunk << " < " << R << " ? ybeg + " << chunk << " : " << R << ";\n";
+        o << "  for (" << idx_t << " xb = (" << idx_t << ")blockIdx.x * " << RPB << "u; xb < V; xb += (" << idx_t << ")gridDim.x * " << RPB << "u) {\n";
+        o << "    const " << idx_t << " x = xb + rib;\n";
+        o << "    const bool valid = x < V;\n";
+        o << "    float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;\n";
+        o << "    if (valid) {\n";
+        std::vector<std::pair<std::vector<Sub>, std::string>> seenx, seeny;
+        std::vector<std::string> xo(k.ins.size());
+        for (size_t i = 0; i < k.ins.size(); i++) {
+            bool found = false;
+            for (auto& s : seenx)
+                if (s.first == k.ins[i].xsubs) { xo[i] = s.second; found = true; }
+            if (found) continue;
+            std::ostringstream pre;
+            std::string tag = "x" + std::to_string(seenx.size());
+            std::string e = offset_expr(k.ins[i].xsubs, "x", pre, tag, idx_t);
+            o << pre.str();
+            o << "      const " << idx_t << " o" << tag << " = " << e << ";\n";
+            xo[i] = "o" + tag;
+            seenx.push_back({k.ins[i].xsubs, xo[i]});
+        }
+        o << "      for (" << idx_t << " y = ybeg + lane * " << vec << "u; y < yend; y += " << TPR * vec << "u) {\n";
+        std::vector<std::string> off(k.ins.size());
+        for (size_t i = 0; i < k.ins.size(); i++) {
+            std::string yo;
+            for (auto& s : seeny)
+                if (s.first == k.ins[i].subs) yo = s.second;
+            if (yo.empty()) {
+                std::ostringstream pre;
+                std::string tag = "y" + std::to_string(seeny.size());
+                std::string e = offset_expr(k.ins[i].subs, "y", pre, tag, idx_t);
+                o << pre.str();
+                o << "      const " << idx_t << " o" << tag << " = " << e << ";\n";
+                yo = "o" + tag;
+                seeny.push_back({k.ins[i].subs, yo});
+            }
+            off[i] = xo[i] + " + " + yo;
+        }
+        std::vector<std::string> names;
+        emit_loads(o, k, vec, acc, off, names, "        ");
+        emit_ssa(o, k, vec, names, acc, "        ");
+        for (int l = 0; l < vec; l++)
+            o << "        acc" << l << " = __fadd_rn(acc" << l << ", v" << k.outs[0].ssa << "_" << l << ");\n";
+        o << "      }\n    }\n";
+        o << "    float s = __fadd_rn(__fadd_rn(acc0, acc1), __fadd_rn(acc2, acc3));\n";
+        for (int m = std::min(TPR, 32) / 2; m >= 1; m /= 2)
+            o << "    s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, " << m << "));\n";
+        if (TPR > 32) {
+            const int wpr = TPR / 32;
+            o << "    __syncthreads();\n";
+            o << "    if ((threadIdx.x & 31u) == 0u) sm[threadIdx.x >> 5] = s;\n";
+            o << "    __syncthreads();\n";
+            o << "    if (lane == 0u) { s = sm[rib * " << wpr << "u];";
+            for (int w = 1; w < wpr; w++) o << " s = __fadd_rn(s, sm[rib * " << wpr << "u + " << w << "u]);";
+            o << " }\n";
+        }
+        {
+            std::ostringstream pre;
+            std::string e = offset_expr(k.outs[0].dst.xsubs, "x", pre, "out", idx_t);
+            o << "    if (valid && lane == 0u) {\n" << pre.str();
+            o << "      a.out[0][(" << e << ")" << (S > 1 ? " * " + std::to_string(S) + " + blockIdx.y" : "") << "] = s;\n    }\n";
+        }
+        o << "  }\n}\n";
+    } else {
+        // lanes along the kept axis (a column sum): 32 x-lanes by 8 y-groups per block, each thread
+        // walks down its column(s); the 8 partials meet in shared memory
+        int vec = k.vec;
+        std::vector<Access> acc(k.ins.size());
+        for (size_t i = 0; i < k.ins.size(); i++) {
+            acc[i] = classify(k.ins[i].xsubs, k.ins[i].offset, vec, false);
+            if (vec == 4 && acc[i].mode == Access::VEC4)
+                for (auto& s : k.ins[i].subs)
+                    if (s.stride % 4) { acc[i].mode = Access::GATHER; acc[i].lane_stride = 1; }
+        }
+        o << "extern \"C\" __global__ void __launch_bounds__(256) @ENTRY@(const __grid_constant__ Args a) {\n";
+        o << "  __shared__ float sm[8][" << 32 * vec << " + 1];\n";
+        o << "  const unsigned int tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;\n";
+        o << "  const " << idx_t << " V = (" << idx_t << ")a.n;\n";
+        o << "  const " << idx_t << " x = ((" << idx_t << ")blockIdx.x * 32u + tx) * " << vec << "u;\n";
+        o << "  const " << idx_t << " ybeg = (" << idx_t << ")blockIdx.y * " << chunk << ";\n";
+        o << "  const " << idx_t << " yend = ybeg + " << chunk << " < " << R << " ? ybeg + " << chunk << " : " << R << ";\n";
+        o << "  float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;\n";
+        o << "  if (x < V) {\n";
+        std::vector<std::pair<std::vector<Sub>, std::string>> seenx, seeny;
+        std::vector<std::string> xo(k.ins.size());
+        for (size_t i = 0; i < k.ins.size(); i++) {
+            bool found = false;
+            for (auto& s : seenx)
+                if (s.first == k.ins[i].xsubs) { xo[i] = s.second; found = true; }
+            if (found) continue;
+            std::ostringstream pre;
+            std::string tag = "x" + std::to_string(seenx.size());
+            std::string e = offset_expr(k.ins[i].xsubs, "x", pre, tag, idx_t);
+            o << pre.str();
+            o << "      const " << idx_t << " o" << tag << " = " << e << ";\n";
+            xo[i] = "o" + tag;
+            seenx.push_back({k.ins[i].xsubs, xo[i]});
+        }
+        o << "    for (" << idx_t << " y = ybeg + ty; y < yend; y += 8u) {\n";
+        std::vector<std::string> off(k.ins.size());
+        for (size_t i = 0; i < k.ins.size(); i++) {
+            std::string yo;
+            for (auto& s : seeny)
+                if (s.first == k.ins[i].subs) yo = s.second;
+            if (yo.empty()) {
+                std::ostringstream pre;
+                std::string tag = "y" + std::to_string(seeny.size());
+                std::string e = offset_expr(k.ins[i].subs, "y", pre, tag, idx_t);
+                o << pre.str();
+                o << "      const " << idx_t << " o" << tag << " = " << e << ";\n";
+                yo = "o" + tag;
+                seeny.push_back({k.ins[i].subs, yo});
+            }
+            off[i] = xo[i] + " + " + yo;
+        }
+        std::vector<std::string> names;
+        emit_loads(o, k, vec, acc, off, names, "      ");
+        emit_ssa(o, k, vec, names, acc, "      ");
+        for (int l = 0; l < vec; l++)
+            o << "      acc" << l << " = __fadd_rn(acc" << l << ", v" << k.outs[0].ssa << "_" << l << ");\n";
+        o << "    }\n  }\n";
+        for (int l = 0; l < vec; l++) o << "  sm[ty][tx * " << vec << " + " << l << "] = acc" << l << ";\n";
+        o << "  __syncthreads();\n";
+        o << "  if (ty == 0u && x < V) {\n";
+        {
+            std::ostringstream pre;
+            std::string e = offset_expr(k.outs[0].dst.xsubs, "x", pre, "out", idx_t);
+            o << pre.str();
+            o << "    const " << idx_t << " oo = (" << e << ")" << (S > 1 ? " + (" + std::string(idx_t) + ")blockIdx.y * V" : "") << ";\n";
+        }
+        int64_t out_stride = k.outs[0].dst.xsubs.empty() ? 0 : k.outs[0].dst.xsubs.back().stride;
+        for (int l = 0; l < vec; l++) {
+            o << "    { float s = sm[0][tx * " << vec << " + " << l << "];";
+            for (int t = 1; t < 8; t++) o << " s = __fadd_rn(s, sm[" << t << "][tx * " << vec << " + " << l << "]);";
+            o << " a.out[0][oo + " << l * out_stride << "] = s; }\n";
+        }
+        o << "  }\n}\n";
+    }
+    finish(k, o.str(), k.mode ? "adb_colsum" : "adb_rowsum");
+}
+
+}  // namespace
+
+// Chooses the thread mapping of a reduce kernel (row / column lanes, vector width, threads per row,
+// split factor).  Called while lowering because a split needs a scratch buffer and a second pass.
+void plan_reduce(KernelSpec& k, int sm_count) {
+    const int64_t V = k.n, R = k.r;
+    // the operand that moves the most bytes decides which axis the lanes follow
+    const Operand* big = nullptr;
+    int64_t best = -1;
+    for (auto& in : k.ins) {
+        int64_t f = footprint(in);
+        if (f > best) { best = f; big = &in; }
+    }
+    k.mode = 0;
+    if (big) {
+        bool y_unit = !big->subs.empty() && big->subs.back().stride == 1;
+        bool x_unit = !big->xsubs.empty() && big->xsubs.back().stride == 1;
+        if (!y_unit && x_unit) k.mode = 1;
+    }
+    if (k.mode == 0) {
+        int vec = R % 4 == 0 ? 4 : 1;
+        for (auto& in : k.ins)
+            if (!lanes_ok(in.subs)) vec = 1;
+        k.vec = vec;
+        int64_t per_row = std::max<int64_t>(1, R / vec);
+        int64_t tpr = std::min<int64_t>(256, pow2_floor(std::max<int64_t>(1, per_row / 4)));
+        k.threads = int(tpr);
+        int64_t blocks = (V + (256 / tpr) - 1) / (256 / tpr);
+        k.split = 1;
+        // few long rows: split each row so that every SM has work
+        if (blocks < sm_count && R >= 16384) {
+            int64_t want = (2 * sm_count + blocks - 1) / blocks;
+            int64_t max_split = std::max<int64_t>(1, R / 4096);
+            k.split = std::max<int64_t>(1, std::min(want, max_split));
+            // keep chunks a multiple of the vector width
+            int64_t chunk = (R + k.split - 1) / k.split;
+            chunk = (chunk + 255) / 256 * 256;
+            k.split = (R + chunk - 1) / chunk;
+        }
+    } else {
+        int vec = V % 4 == 0 ? 4 : 1;
+        for (auto& in : k.ins)
+            if (!lanes_ok(in.xsubs)) vec = 1;
+        if (!lanes_ok(k.outs[0].dst.xsubs)) vec = 1;
+        k.vec = vec;
+        k.threads = 256;
+        int64_t bx = (V + 32 * vec - 1) / (32 * vec);
+        k.split = 1;
+        if (bx < 2 * sm_count && R >= 512) {
+            int64_t want = (2 * sm_count + bx - 1) / bx;
+            k.split = std::max<int64_t>(1, std::min(want, R / 256));
+        }
+    }
+}
+
+void generate_kernels(Plan& plan) {
+    for (auto& k : plan.kernels) {
+        if (!k.source.empty()) continue;
+        if (k.type == KernelSpec::ELW) gen_elw(k);
+        else gen_reduce(k);
+    }
+}
+
+}  // namespace adb

@@ -1,0 +1,34 @@
+// Dot product C[M,N] = A[M,K] . B[K,N] on strided fp32 operands (the reference's `DotProd` kernel,
+// src/devices/opencl/kernels/dotprod.rs:4-75: one work-item per output, scalar k loop).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <string>
+
+namespace adb {
+
+struct GemmArgs {
+    const float* A = nullptr;
+    const float* B = nullptr;
+    float* C = nullptr;  // row-major [M,N], leading dimension N
+    int64_t M = 0, N = 0, K = 0;
+    int64_t a_rs = 0, a_cs = 0, b_rs = 0, b_cs = 0;  // element strides of A[m,k] and B[k,n]
+    bool force_simt = false;
+};
+
+struct GemmContext {
+    int sm_count = 148;
+    void* encode_tiled = nullptr;  // cuTensorMapEncodeTiled, fetched through the runtime (no libcuda link)
+    bool tc_ready = false;
+    int* status = nullptr;         // device word the tensor-core kernel sets when a bounded wait runs out
+    int* status_host = nullptr;
+};
+
+bool gemm_init(GemmContext& ctx, int sm_count, std::string& err);
+void gemm_destroy(GemmContext& ctx);
+
+// Enqueues the product on `stream`; returns the number of kernels launched, or -1 with `err` set.
+int gemm_launch(GemmContext& ctx, const GemmArgs& a, cudaStream_t stream, std::string& err);
+
+}  // namespace adb

@@ -1,0 +1,1341 @@
+// IR -> plan.  Plays the role of the reference's `to_kernel` pipeline (src/kernel/to_kernel.rs:34-107):
+// instruction selection (src/kernel/to_instr/*.rs), alias tracking (src/kernel/trackers/kernel.rs),
+// the three fusion passes (src/kernel/fusion/*.rs), reordering for in-place chains
+// (src/kernel/memory/*.rs) and alloc insertion (src/kernel/alloc/*.rs) -- but organised differently:
+// values stay lazy expression DAGs until something needs them in memory, so fusion, common
+// sub-expression sharing, dead-code removal and "temporaries never touch HBM" fall out of one
+// mechanism instead of a sequence of rewriting passes.
+#include "adb_lower.hpp"
+
+#include <algorithm>
+#include <cstdio>
+#include <map>
+#include <set>
+#include <sstream>
+#include <unordered_map>
+#include <unordered_set>
+
+namespace adb {
+
+namespace {
+
+struct IdInfo {
+    int ndefs = 0;
+    int def_seg = -1;
+    bool cross = false;    // read outside the straight-line segment that defines it (or by the host)
+    bool is_cond = false;
+    bool needed = false;   // reachable from the dep list / a condition (dead-code elimination)
+    int64_t uses = 0;      // remaining reads by live commands
+    int buf = -1;          // persistent buffer once allocated
+    std::vector<uint32_t> alias_kids;
+    // an id owns a persistent buffer when its value must survive the straight-line segment that
+    // computes it; ids that are redefined but only used inside one segment stay in registers
+    bool needs_buffer() const { return cross || is_cond; }
+};
+
+struct Binding {
+    enum Kind : uint8_t { UNDEF, VALUE, ALIAS } kind = UNDEF;
+    Node* node = nullptr;      // VALUE
+    bool pending = false;      // VALUE that still has to be written to the id's persistent buffer
+    const Cmd* cmd = nullptr;  // ALIAS: the View / Index / Permute / Broadcast / Concat command
+    Node* cache = nullptr;
+    Node* cache_pa = nullptr;
+    Node* cache_pb = nullptr;
+};
+
+bool is_alias_op(uint8_t op) {
+    return op == OP_VIEW || op == OP_INDEX || op == OP_PERMUTE || op == OP_BROADCAST || op == OP_CONCAT;
+}
+
+bool has_result(uint8_t op) {
+    switch (op) {
+    case OP_WHILE: case OP_IF: case OP_EX: case OP_HEADING: return false;
+    default: return true;
+    }
+}
+
+// operands read by a command (in-place forms also read their target)
+void cmd_reads(const Cmd& c, uint32_t out[2], int& n) {
+    n = 0;
+    switch (c.op) {
+    case OP_MUL: case OP_ADD: case OP_DOT: case OP_CONCAT: case OP_MUL_EQ: case OP_ADD_EQ:
+        out[n++] = c.a; out[n++] = c.b; break;
+    case OP_EQZ: case OP_GTZ: case OP_LTZ: case OP_SUM: case OP_CONTIG: case OP_EXP2: case OP_LOG2:
+    case OP_SIN: case OP_RECIP: case OP_SQRT: case OP_VIEW: case OP_INDEX: case OP_PERMUTE:
+    case OP_BROADCAST: case OP_ALLREDUCE:
+        out[n++] = c.a; break;
+    default: break;
+    }
+}
+
+struct StoreTask {
+    Node* node;    // plain expression (no PIECE)
+    int buf;
+    View view;     // destination access over node->shape
+};
+
+class Lowerer {
+  public:
+    Lowerer(Program& prog, Plan& plan, const LowerOptions& opt) : prog_(prog), plan_(plan), opt_(opt) {
+        info_.resize(prog.ids.size());
+        bind_.resize(prog.ids.size());
+    }
+
+    void run() {
+        plan_.ir_commands = prog_.n_cmds;
+        is_dep_.assign(prog_.ids.size(), 0);
+        for (auto d : prog_.dep) { info_[d].cross = true; is_dep_[d] = 1; }
+        int seg = 0;
+        analyze(prog_.main, seg);
+        dce();
+        count_uses(prog_.main);
+        // aliases keep their parents alive and make them cross-segment when they are
+        propagate_alias_cross(prog_.main);
+        index_mats(prog_.main);
+        cur_ = &plan_.main;
+        bool stopped = lower_block(prog_.main, true);
+        (void)stopped;
+        finalize_results();
+        plan_.n_steps = pos_;
+        plan_arena();
+    }
+
+  private:
+    Program& prog_;
+    Plan& plan_;
+    LowerOptions opt_;
+    Graph g_;
+    std::vector<IdInfo> info_;
+    std::vector<Binding> bind_;
+    std::vector<char> is_dep_;
+    std::vector<uint32_t> lazy_ids_;   // ids bound to values that do not live in their own buffer yet
+    StepBlock* cur_ = nullptr;
+    int pos_ = 0;
+    int tmp_counter_ = 0;
+    std::vector<std::pair<int, int>> loop_spans_;  // [first,last] step positions of While bodies
+    bool results_done_ = false;
+
+    std::unordered_map<const Cmd*, int> mat_index_;  // CreateMat -> ordinal in program order
+    std::map<std::pair<Node*, Node*>, Node*> dot_cse_;  // (A, B) -> product still in memory
+    std::map<Node*, Node*> sum_cse_;                    // summand -> row sums still in memory
+
+    void index_mats(Block& b) {
+        for (auto& c : b.cmds) {
+            if (c.op == OP_CREATE_MAT) { int n = int(mat_index_.size()); mat_index_[&c] = n; }
+            else if (c.op == OP_WHILE) index_mats(*c.block);
+            else if (c.op == OP_IF) {
+                for (auto& cb : c.conds) index_mats(*cb.second);
+                if (c.else_block) index_mats(*c.else_block);
+            }
+        }
+    }
+
+    [[noreturn]] void fail(const std::string& msg) { throw LowerError(msg); }
+    const std::string& name(uint32_t id) const { return prog_.ids[id]; }
+
+    // ------------------------------------------------------------------ analysis
+    void def(uint32_t id, int seg) {
+        auto& i = info_[id];
+        i.ndefs++;
+        if (i.def_seg < 0) i.def_seg = seg;
+    }
+    void use(uint32_t id, int seg) {
+        auto& i = info_[id];
+        if (i.def_seg != seg) i.cross = true;
+    }
+
+    void analyze(Block& b, int& seg) {
+        int cur = ++seg;
+        for (auto& c : b.cmds) {
+            if (c.op == OP_WHILE) {
+                info_[c.a].is_cond = true;
+                analyze(*c.block, seg);
+                cur = ++seg;
+            } else if (c.op == OP_IF) {
+                for (auto& cb : c.conds) {
+                    info_[cb.first].is_cond = true;
+                    analyze(*cb.second, seg);
+                }
+                if (c.else_block) analyze(*c.else_block, seg);
+                cur = ++seg;
+            } else if (has_result(c.op)) {
+                uint32_t r[2];
+                int n;
+                cmd_reads(c, r, n);
+                for (int k = 0; k < n; k++) use(r[k], cur);
+                def(c.res, cur);
+                if (c.op == OP_ALLREDUCE) info_[c.a].cross = true;
+            }
+        }
+    }
+
+    // flow-insensitive liveness: a command is live when its result can reach the dep list,
+    // a condition or a collective
+    void dce() {
+        for (auto d : prog_.dep) info_[d].needed = true;
+        for (size_t i = 0; i < info_.size(); i++)
+            if (info_[i].is_cond) info_[i].needed = true;
+        bool changed = true;
+        std::function<void(Block&)> walk = [&](Block& b) {
+            for (auto& c : b.cmds) {
+                if (c.op == OP_WHILE) walk(*c.block);
+                else if (c.op == OP_IF) {
+                    for (auto& cb : c.conds) walk(*cb.second);
+                    if (c.else_block) walk(*c.else_block);
+                } else if (has_result(c.op) && info_[c.res].needed) {
+                    uint32_t r[2];
+                    int n;
+                    cmd_reads(c, r, n);
+                    for (int k = 0; k < n; k++)
+                        if (!info_[r[k]].needed) { info_[r[k]].needed = true; changed = true; }
+                }
+            }
+        };
+        while (changed) {
+            changed = false;
+            walk(prog_.main);
+        }
+    }
+    bool live(const Cmd& c) const { return !has_result(c.op) || info_[c.res].needed; }
+
+    void count_uses(Block& b) {
+        for (auto& c : b.cmds) {
+            if (c.op == OP_WHILE) { info_[c.a].uses += 1; count_uses(*c.block); }
+            else if (c.op == OP_IF) {
+                for (auto& cb : c.conds) { info_[cb.first].uses += 1; count_uses(*cb.second); }
+                if (c.else_block) count_uses(*c.else_block);
+            } else if (has_result(c.op) && live(c)) {
+                uint32_t r[2];
+                int n;
+                cmd_reads(c, r, n);
+                for (int k = 0; k < n; k++) info_[r[k]].uses++;
+            }
+        }
+    }
+
+    void propagate_alias_cross(Block& b) {
+        for (size_t ii = b.cmds.size(); ii-- > 0;) {
+            auto& c = b.cmds[ii];
+            if (c.op == OP_WHILE) propagate_alias_cross(*c.block);
+            else if (c.op == OP_IF) {
+                if (c.else_block) propagate_alias_cross(*c.else_block);
+                for (size_t k = c.conds.size(); k-- > 0;) propagate_alias_cross(*c.conds[k].second);
+            } else if (is_alias_op(c.op) && live(c)) {
+                if (info_[c.res].cross || info_[c.res].is_cond) {
+                    info_[c.a].cross = true;
+                    if (c.op == OP_CONCAT) info_[c.b].cross = true;
+                }
+                info_[c.a].alias_kids.push_back(c.res);
+                if (c.op == OP_CONCAT) info_[c.b].alias_kids.push_back(c.res);
+            }
+        }
+    }
+
+    bool id_live(uint32_t id, int depth = 0) const {
+        const auto& i = info_[id];
+        if (i.uses > 0) return true;
+        if (bind_[id].pending) return true;
+        if (results_pending_(id)) return true;
+        if (depth > 64) return true;
+        for (auto k : i.alias_kids)
+            if (bind_[k].kind == Binding::ALIAS && id_live(k, depth + 1)) return true;
+        return false;
+    }
+    bool results_pending_(uint32_t id) const {
+        return !results_done_ && is_dep_[id];
+    }
+
+    // ------------------------------------------------------------------ buffers and steps
+    int new_buffer(int64_t n, const std::string& nm, bool persistent) {
+        BufferInfo b;
+        b.numel = n;
+        b.name = nm;
+        b.persistent = persistent;
+        plan_.bufs.push_back(b);
+        g_.buf_version.push_back(0);
+        return int(plan_.bufs.size()) - 1;
+    }
+    int temp_buffer(int64_t n) { return new_buffer(n, "tmp" + std::to_string(tmp_counter_++), false); }
+
+    int id_buffer(uint32_t id, const Shape& shape) {
+        auto& i = info_[id];
+        int64_t n = numel(shape);
+        if (i.buf >= 0) {
+            if (plan_.bufs[i.buf].numel != n)
+                fail("id '" + name(id) + "' is redefined with a different size; a buffer keeps one size "
+                     "(the reference asserts the same, src/devices/opencl/context.rs:62-64)");
+            return i.buf;
+        }
+        i.buf = new_buffer(n, name(id), true);
+        return i.buf;
+    }
+
+    void touch(int buf, int pos) {
+        auto& b = plan_.bufs[buf];
+        b.first = std::min(b.first, pos);
+        b.last = std::max(b.last, pos);
+    }
+
+    Step& push_step(Step::Kind k) {
+        cur_->steps.emplace_back();
+        Step& s = cur_->steps.back();
+        s.kind = k;
+        s.pos = pos_++;
+        return s;
+    }
+
+    // ------------------------------------------------------------------ bindings
+    Node* resolve(uint32_t id, int depth = 0) {
+        Binding& b = bind_[id];
+        if (depth > 4096) fail("alias chain too deep at '" + name(id) + "'");
+        if (b.kind == Binding::UNDEF) fail("id '" + name(id) + "' is read before it is defined");
+        if (b.kind == Binding::VALUE) {
+            Node* n = g_.canon(b.node);
+            if (!g_.load_valid(n)) fail("internal: stale binding for '" + name(id) + "'");
+            return n;
+        }
+        const Cmd& c = *b.cmd;
+        Node* pa = resolve(c.a, depth + 1);
+        Node* pb = c.op == OP_CONCAT ? resolve(c.b, depth + 1) : nullptr;
+        if (b.cache && b.cache_pa == pa && b.cache_pb == pb) return g_.canon(b.cache);
+        Node* r = nullptr;
+        switch (c.op) {
+        case OP_VIEW: {
+            if (numel(c.dims) != numel(pa->shape)) fail("View of '" + name(c.a) + "' changes the element count");
+            r = g_.reshape(pa, c.dims);
+            if (!r) {
+                Node* m = materialize_node(pa);
+                r = g_.reshape(m, c.dims);
+                if (!r) fail("internal: reshape of a contiguous value failed");
+            }
+            break;
+        }
+        case OP_INDEX:
+            if (c.dim >= pa->shape.size() || int64_t(c.index) >= pa->shape[c.dim]) fail("Index out of range on '" + name(c.a) + "'");
+            r = g_.index(pa, int(c.dim), int64_t(c.index));
+            break;
+        case OP_PERMUTE: {
+            if (c.perm.size() != pa->shape.size()) fail("Permute rank mismatch on '" + name(c.a) + "'");
+            std::vector<char> seen(c.perm.size(), 0);
+            for (auto p : c.perm) {
+                if (p >= c.perm.size() || seen[p]) fail("Permute is not a permutation");
+                seen[p] = 1;
+            }
+            r = g_.permute(pa, c.perm);
+            break;
+        }
+        case OP_BROADCAST:
+            if (c.dim >= pa->shape.size() || pa->shape[c.dim] != 1) fail("Broadcast needs a length-1 axis on '" + name(c.a) + "'");
+            r = g_.broadcast(pa, int(c.dim), int64_t(c.count));
+            break;
+        case OP_CONCAT: {
+            if (pa->shape.size() != pb->shape.size() || c.dim >= pa->shape.size()) fail("Concat rank mismatch");
+            for (size_t i = 0; i < pa->shape.size(); i++)
+                if (i != c.dim && pa->shape[i] != pb->shape[i]) fail("Dim misaligned at concat");
+            r = g_.piece(int(c.dim), {pa, pb});
+            break;
+        }
+        default: fail("internal: bad alias command");
+        }
+        b.cache = r;
+        b.cache_pa = pa;
+        b.cache_pb = pb;
+        return r;
+    }
+
+    void consume(uint32_t id) {
+        if (info_[id].uses > 0) info_[id].uses--;
+    }
+
+    void bind_value(uint32_t id, Node* n) {
+        Binding& b = bind_[id];
+        b.kind = Binding::VALUE;
+        b.node = n;
+        b.cmd = nullptr;
+        b.cache = nullptr;
+        b.pending = false;
+        n = g_.canon(n);
+        bool own = false;
+        if (n->kind == N_LOAD && info_[id].buf == n->buf && view_is_contiguous(n->view, n->shape) && n->view.offset == 0) own = true;
+        if (info_[id].needs_buffer() && !own) b.pending = true;
+        if (!own) lazy_ids_.push_back(id);
+    }
+
+    void bind_own_buffer(uint32_t id, int buf, const Shape& shape) {
+        Binding& b = bind_[id];
+        b.kind = Binding::VALUE;
+        b.node = g_.load(buf, shape, contiguous_view(shape));
+        b.pending = false;
+        b.cmd = nullptr;
+        b.cache = nullptr;
+    }
+
+    // ------------------------------------------------------------------ hazards
+    bool depends_on(Node* n, int buf) {
+        std::unordered_set<Node*> seen;
+        std::vector<Node*> st{g_.canon(n)};
+        while (!st.empty()) {
+            Node* x = st.back();
+            st.pop_back();
+            if (!seen.insert(x).second) continue;
+            switch (x->kind) {
+            case N_LOAD: if (x->buf == buf) return true; break;
+            case N_OP:
+                st.push_back(g_.canon(x->a));
+                if (x->b) st.push_back(g_.canon(x->b));
+                break;
+            case N_PIECE: for (auto k : x->kids) st.push_back(g_.canon(k)); break;
+            default: break;
+            }
+        }
+        return false;
+    }
+
+    // called before a kernel overwrites live contents of `buf`: every lazy value that still reads
+    // the old contents and is needed later is written out first
+    void before_write(int buf, const std::vector<uint32_t>& exclude) {
+        if (g_.buf_version[buf] == 0) return;  // nothing could have read it yet
+        std::vector<uint32_t> todo;
+        std::vector<uint32_t> keep;
+        std::unordered_set<uint32_t> seen;
+        for (auto id : lazy_ids_) {
+            if (!seen.insert(id).second) continue;
+            Binding& b = bind_[id];
+            if (b.kind != Binding::VALUE) continue;
+            Node* n = g_.canon(b.node);
+            bool own = n->kind == N_LOAD && info_[id].buf == n->buf;
+            if (own && !b.pending) continue;  // already in its own buffer
+            if (!id_live(id)) continue;
+            keep.push_back(id);
+            if (std::find(exclude.begin(), exclude.end(), id) != exclude.end()) continue;
+            if (depends_on(n, buf)) todo.push_back(id);
+        }
+        lazy_ids_.swap(keep);
+        if (!todo.empty()) materialize_ids(todo);
+    }
+
+    // ------------------------------------------------------------------ materialisation
+    static bool slice_view(View& v, int dim, int64_t lo, int64_t hi) {
+        auto& subs = v.dims[dim];
+        if (subs.empty()) return lo == 0;
+        if (subs.size() == 1) {
+            v.offset += lo * subs[0].stride;
+            subs[0].size = hi - lo;
+            return true;
+        }
+        int64_t inner = 1;
+        for (size_t i = 1; i < subs.size(); i++) inner *= subs[i].size;
+        if (lo % inner || hi % inner) return false;
+        v.offset += (lo / inner) * subs[0].stride;
+        subs[0].size = (hi - lo) / inner;
+        return true;
+    }
+
+    void collect_stores(Node* n, int buf, const View& view, std::vector<StoreTask>& out) {
+        n = g_.canon(n);
+        if (numel(n->shape) == 0) return;
+        if (n->kind == N_PIECE) {
+            int64_t start = 0;
+            for (size_t i = 0; i < n->kids.size(); i++) {
+                View v = view;
+                if (!slice_view(v, n->pdim, start, n->ends[i])) fail("internal: destination view cannot be cut");
+                for (auto& d : v.dims) canon_subs(d);
+                collect_stores(n->kids[i], buf, v, out);
+                start = n->ends[i];
+            }
+            return;
+        }
+        out.push_back({n, buf, view});
+    }
+
+    // write lazy values of ids into their buffers (persistent buffer for ids that need one, else a temp)
+    void materialize_ids(std::vector<uint32_t> ids) {
+        // ids whose value already sits in its own buffer need nothing
+        std::vector<uint32_t> work;
+        for (auto id : ids) {
+            Binding& b = bind_[id];
+            if (b.kind != Binding::VALUE) continue;
+            Node* n = g_.canon(b.node);
+            bool own = n->kind == N_LOAD && info_[id].buf == n->buf && view_is_contiguous(n->view, n->shape) && n->view.offset == 0;
+            if (own) { b.pending = false; continue; }
+            if (std::find(work.begin(), work.end(), id) == work.end()) work.push_back(id);
+        }
+        if (work.empty()) return;
+        std::vector<int> dst(work.size());
+        for (size_t k = 0; k < work.size(); k++) {
+            uint32_t id = work[k];
+            Node* n = g_.canon(bind_[id].node);
+            dst[k] = info_[id].needs_buffer() ? id_buffer(id, n->shape) : temp_buffer(numel(n->shape));
+        }
+        // old contents of the targets may still be needed by other lazy values
+        for (size_t k = 0; k < work.size(); k++) before_write(dst[k], work);
+        std::vector<StoreTask> tasks;
+        std::vector<std::pair<size_t, size_t>> span(work.size());
+        for (size_t k = 0; k < work.size(); k++) {
+            Node* n = g_.canon(bind_[work[k]].node);
+            span[k].first = tasks.size();
+            collect_stores(n, dst[k], contiguous_view(n->shape), tasks);
+            span[k].second = tasks.size();
+        }
+        emit_stores(tasks);
+        for (size_t k = 0; k < work.size(); k++) {
+            uint32_t id = work[k];
+            Node* old = bind_[id].node;
+            Node* oldc = g_.canon(old);
+            g_.buf_version[dst[k]]++;
+            Node* ld = g_.load(dst[k], oldc->shape, contiguous_view(oldc->shape));
+            if (oldc->kind == N_OP || oldc->kind == N_PIECE) oldc->fwd = ld;
+            bind_[id].node = ld;
+            bind_[id].pending = false;
+        }
+    }
+
+    // write an arbitrary node to a fresh temp and forward the node to it
+    Node* materialize_node(Node* n) {
+        n = g_.canon(n);
+        if (n->kind == N_LOAD && view_is_contiguous(n->view, n->shape)) return n;
+        int buf = temp_buffer(numel(n->shape));
+        std::vector<StoreTask> tasks;
+        collect_stores(n, buf, contiguous_view(n->shape), tasks);
+        emit_stores(tasks);
+        g_.buf_version[buf]++;
+        Node* ld = g_.load(buf, n->shape, contiguous_view(n->shape));
+        if (n->kind == N_OP || n->kind == N_PIECE) n->fwd = ld;
+        return ld;
+    }
+
+    void flush_pending() {
+        std::vector<uint32_t> ids;
+        std::unordered_set<uint32_t> seen;
+        for (auto id : lazy_ids_)
+            if (bind_[id].kind == Binding::VALUE && bind_[id].pending && seen.insert(id).second) ids.push_back(id);
+        if (!ids.empty()) materialize_ids(ids);
+        // everything else that is still lazy is local to the finished segment
+        std::vector<uint32_t> keep;
+        for (auto id : lazy_ids_)
+            if (bind_[id].kind == Binding::VALUE && bind_[id].pending) keep.push_back(id);
+        lazy_ids_.swap(keep);
+    }
+
+    // group store tasks of equal size into fused kernels; a task whose destination is still read
+    // by the group with another access pattern (or from another kernel of the group) is written to
+    // a temporary first and copied over afterwards
+    struct CopyBack {
+        int tmp, buf;
+        View view;
+        Shape shape;
+    };
+    void emit_stores(std::vector<StoreTask>& tasks) {
+        if (tasks.empty()) return;
+        std::vector<CopyBack> copies;
+        for (auto& t : tasks) {
+            if (g_.buf_version[t.buf] == 0) continue;  // fresh buffer: nobody reads it
+            bool conflict = false;
+            for (auto& u : tasks) {
+                if (!depends_on(u.node, t.buf)) continue;
+                if (numel(u.node->shape) != numel(t.node->shape) || reads_other_access(u.node, t.buf, t.view)) {
+                    conflict = true;
+                    break;
+                }
+            }
+            if (conflict) {
+                int tmp = temp_buffer(numel(t.node->shape));
+                copies.push_back({tmp, t.buf, t.view, t.node->shape});
+                t.buf = tmp;
+                t.view = contiguous_view(t.node->shape);
+            }
+        }
+        std::map<int64_t, std::vector<StoreTask*>> groups;
+        for (auto& t : tasks) groups[numel(t.node->shape)].push_back(&t);
+        for (auto& kv : groups) {
+            // keep kernels bounded: split a group when its combined DAG gets too large
+            std::vector<StoreTask*> cur;
+            int64_t sz = 0;
+            for (auto* t : kv.second) {
+                int64_t s = std::min<int64_t>(t->node->nops, opt_.fuse_limit);
+                if (!cur.empty() && (sz + s > opt_.fuse_limit * 2 || cur.size() >= 16)) {
+                    emit_elw(cur);
+                    cur.clear();
+                    sz = 0;
+                }
+                cur.push_back(t);
+                sz += s;
+            }
+            if (!cur.empty()) emit_elw(cur);
+        }
+        for (auto& c : copies) {
+            g_.buf_version[c.tmp]++;
+            StoreTask t{g_.load(c.tmp, c.shape, contiguous_view(c.shape)), c.buf, c.view};
+            std::vector<StoreTask*> one{&t};
+            emit_elw(one);
+        }
+    }
+
+    bool reads_other_access(Node* n, int buf, const View& view) {
+        std::unordered_set<Node*> seen;
+        std::vector<Node*> st{g_.canon(n)};
+        auto want = flat_subs(view);
+        while (!st.empty()) {
+            Node* x = st.back();
+            st.pop_back();
+            if (!seen.insert(x).second) continue;
+            if (x->kind == N_LOAD) {
+                if (x->buf == buf && !(x->view.offset == view.offset && flat_subs(x->view) == want)) return true;
+            } else if (x->kind == N_OP) {
+                st.push_back(g_.canon(x->a));
+                if (x->b) st.push_back(g_.canon(x->b));
+            }
+        }
+        return false;
+    }
+
+    // ------------------------------------------------------------------ kernel construction
+    struct SsaBuilder {
+        Lowerer& L;
+        KernelSpec& k;
+        bool reduce;
+        std::unordered_map<Node*, int> memo;
+        std::map<uint32_t, int> consts;
+        SsaBuilder(Lowerer& l, KernelSpec& ks, bool red) : L(l), k(ks), reduce(red) {}
+
+        Operand make_operand(int buf, const View& v) {
+            Operand o;
+            o.buf = buf;
+            o.offset = v.offset;
+            if (reduce) {
+                o.xsubs = v.dims[0];
+                o.subs = v.dims[1];
+                canon_subs(o.xsubs);
+                canon_subs(o.subs);
+            } else
+                o.subs = flat_subs(v);
+            return o;
+        }
+
+        int build(Node* n0) {
+            // iterative post-order so very deep chains cannot overflow the stack
+            std::vector<std::pair<Node*, int>> st;
+            st.push_back({L.g_.canon(n0), 0});
+            while (!st.empty()) {
+                Node* n = st.back().first;
+                int phase = st.back().second;
+                if (memo.count(n)) { st.pop_back(); continue; }
+                if (n->kind == N_PIECE) L.fail("internal: piecewise value inside a kernel expression");
+                if (n->kind == N_LOAD) {
+                    if (!L.g_.load_valid(n)) L.fail("internal: kernel reads overwritten data");
+                    Operand o = make_operand(n->buf, n->view);
+                    int oi = -1;
+                    for (size_t i = 0; i < k.ins.size(); i++)
+                        if (k.ins[i].same_access(o)) { oi = int(i); break; }
+                    if (oi < 0) { k.ins.push_back(o); oi = int(k.ins.size()) - 1; }
+                    Ssa s; s.kind = Ssa::LOAD; s.operand = oi;
+                    k.ssa.push_back(s);
+                    memo[n] = int(k.ssa.size()) - 1;
+                    st.pop_back();
+                } else if (n->kind == N_CONST) {
+                    uint32_t bits;
+                    std::memcpy(&bits, &n->cval, 4);
+                    auto it = consts.find(bits);
+                    if (it == consts.end()) {
+                        Ssa s; s.kind = Ssa::CONST; s.c = n->cval;
+                        k.ssa.push_back(s);
+                        it = consts.emplace(bits, int(k.ssa.size()) - 1).first;
+                    }
+                    memo[n] = it->second;
+                    st.pop_back();
+                } else {
+                    Node* a = L.g_.canon(n->a);
+                    Node* b = n->b ? L.g_.canon(n->b) : nullptr;
+                    if (phase == 0) {
+                        st.back().second = 1;
+                        if (b && !memo.count(b)) st.push_back({b, 0});
+                        if (!memo.count(a)) st.push_back({a, 0});
+                    } else {
+                        Ssa s; s.kind = Ssa::OP; s.op = n->op; s.a = memo[a]; s.b = b ? memo[b] : -1;
+                        k.ssa.push_back(s);
+                        memo[n] = int(k.ssa.size()) - 1;
+                        st.pop_back();
+                    }
+                }
+            }
+            return memo[L.g_.canon(n0)];
+        }
+    };
+
+    void emit_elw(std::vector<StoreTask*>& tasks) {
+        KernelSpec k;
+        k.type = KernelSpec::ELW;
+        k.n = numel(tasks[0]->node->shape);
+        SsaBuilder sb(*this, k, false);
+        for (auto* t : tasks) {
+            int v = sb.build(t->node);
+            KernelSpec::Out o;
+            o.ssa = v;
+            o.dst.buf = t->buf;
+            o.dst.offset = t->view.offset;
+            o.dst.subs = flat_subs(t->view);
+            k.outs.push_back(o);
+        }
+        plan_.kernels.push_back(std::move(k));
+        Step& s = push_step(Step::ELW);
+        s.kernel = int(plan_.kernels.size()) - 1;
+        auto& ks = plan_.kernels.back();
+        for (auto& o : ks.ins) touch(o.buf, s.pos);
+        for (auto& o : ks.outs) touch(o.dst.buf, s.pos);
+    }
+
+    // ------------------------------------------------------------------ commands
+    Node* elementwise2(EOp op, Node* a, Node* b) {
+        Node* r = g_.op2(op, a, b);
+        if (!r) {
+            a = materialize_node(a);
+            b = materialize_node(b);
+            r = g_.op2(op, a, b);
+            if (!r) fail("internal: element-wise op on materialised operands failed");
+        }
+        return r;
+    }
+
+    void after_op(uint32_t id, Node* r) {
+        bind_value(id, r);
+        r = g_.canon(r);
+        bool too_big = false;
+        if (r->nops > opt_.fuse_limit) {
+            int64_t exact = g_.dag_size(r);
+            if (exact > opt_.fuse_limit) too_big = true;
+            else if (r->kind == N_OP) r->nops = exact;
+        }
+        if ((opt_.no_fusion && (r->kind == N_OP || r->kind == N_PIECE)) || too_big) materialize_ids({id});
+    }
+
+    void check_same_numel(const Cmd& c, Node* a, Node* b) {
+        if (a->kind != N_CONST && b->kind != N_CONST && a->shape != b->shape) {
+            if (numel(a->shape) != numel(b->shape))
+                fail("element-wise operands '" + name(c.a) + "' and '" + name(c.b) + "' differ in size");
+        }
+    }
+
+    void lower_cmd(const Cmd& c) {
+        switch (c.op) {
+        case OP_HEADING: return;
+        case OP_CREATE_MAT: return lower_create_mat(c);
+        case OP_CREATE_CONST: {
+            bind_value(c.res, g_.constant(c.cval, c.dims));
+            return;
+        }
+        case OP_MUL: case OP_ADD: case OP_MUL_EQ: case OP_ADD_EQ: {
+            Node* a = resolve(c.a);
+            Node* b = resolve(c.b);
+            check_same_numel(c, a, b);
+            if (a->kind != N_CONST && b->kind != N_CONST && a->shape != b->shape) {
+                // same element count, different shape: align the right operand to the left one
+                Node* rb = g_.reshape(b, a->shape);
+                if (!rb) rb = g_.reshape(materialize_node(b), a->shape);
+                b = rb;
+            }
+            if (a->kind == N_CONST && b->kind != N_CONST && a->shape != b->shape) a = g_.constant(a->cval, b->shape);
+            if (b->kind == N_CONST && a->shape != b->shape) b = g_.constant(b->cval, a->shape);
+            EOp op = (c.op == OP_MUL || c.op == OP_MUL_EQ) ? E_MUL : E_ADD;
+            Node* r = elementwise2(op, a, b);
+            consume(c.a);
+            consume(c.b);
+            after_op(c.res, r);
+            return;
+        }
+        case OP_EQZ: case OP_GTZ: case OP_LTZ: case OP_EXP2: case OP_LOG2: case OP_SIN: case OP_RECIP: case OP_SQRT: {
+            static const EOp map[] = {E_EQZ, E_GTZ, E_LTZ};
+            EOp op;
+            switch (c.op) {
+            case OP_EQZ: case OP_GTZ: case OP_LTZ: op = map[c.op - OP_EQZ]; break;
+            case OP_EXP2: op = E_EXP2; break;
+            case OP_LOG2: op = E_LOG2; break;
+            case OP_SIN: op = E_SIN; break;
+            case OP_RECIP: op = E_RECIP; break;
+            default: op = E_SQRT; break;
+            }
+            Node* a = resolve(c.a);
+            Node* r = g_.op1(op, a);
+            if (!r) r = g_.op1(op, materialize_node(a));
+            consume(c.a);
+            after_op(c.res, r);
+            return;
+        }
+        case OP_CONTIG: {
+            Node* a = resolve(c.a);
+            consume(c.a);
+            bind_value(c.res, a);
+            return;
+        }
+        case OP_VIEW: case OP_INDEX: case OP_PERMUTE: case OP_BROADCAST: case OP_CONCAT: {
+            if (c.res == c.a || (c.op == OP_CONCAT && c.res == c.b))
+                fail("alias command writes onto its own operand ('" + name(c.res) + "')");
+            // parents stay referenced for as long as the alias is; their reads are counted when the
+            // alias itself is consumed, so only validate now
+            (void)resolve(c.a);
+            consume(c.a);
+            if (c.op == OP_CONCAT) { (void)resolve(c.b); consume(c.b); }
+            Binding& b = bind_[c.res];
+            b.kind = Binding::ALIAS;
+            b.cmd = &c;
+            b.node = nullptr;
+            b.cache = nullptr;
+            b.pending = false;
+            (void)resolve(c.res);  // shape / range checks happen at definition
+            return;
+        }
+        case OP_SUM: return lower_sum(c);
+        case OP_DOT: return lower_dot(c);
+        case OP_ALLREDUCE: return lower_allreduce(c);
+        default: fail("internal: unexpected command in straight-line code");
+        }
+    }
+
+    static bool uniform_payload(const float* p, int64_t n, float& v) {
+        if (n == 0) return false;
+        uint32_t first;
+        std::memcpy(&first, p, 4);
+        const uint32_t* u = reinterpret_cast<const uint32_t*>(p);
+        for (int64_t i = 1; i < n; i++)
+            if (u[i] != first) return false;
+        v = p[0];
+        return true;
+    }
+
+    void lower_create_mat(const Cmd& c) {
+        int64_t n = numel(c.dims);
+        if (int64_t(c.count) != n) fail("CreateMat '" + name(c.res) + "': # of values doesn't match dim size");
+        PayloadSlot slot;
+        slot.kind = c.payload_kind;
+        slot.addr = c.payload;
+        slot.count = n;
+        slot.cmd_index = mat_index_.at(&c);
+        plan_.payloads.push_back(slot);
+        int slot_idx = int(plan_.payloads.size()) - 1;
+        if (n == 0) {
+            bind_value(c.res, g_.constant(0.f, c.dims));
+            return;
+        }
+        float cv;
+        if (c.payload_kind != PAYLOAD_DEVICE && info_[c.res].ndefs == 1 &&
+            uniform_payload(reinterpret_cast<const float*>(uintptr_t(c.payload)), n, cv)) {
+            // a constant-filled tensor (backward seeds, zero padding) never needs to exist in memory
+            plan_.payloads.back().assumed_const = true;  // a cached plan re-checks this on reuse
+            plan_.payloads.back().const_val = cv;
+            bind_value(c.res, g_.constant(cv, c.dims));
+            return;
+        }
+        bool persistent = info_[c.res].needs_buffer();
+        if (c.payload_kind == PAYLOAD_DEVICE && info_[c.res].ndefs == 1 && (c.payload % 16) == 0) {
+            // resident and never written: read the caller's memory in place
+            int buf = new_buffer(n, name(c.res), true);
+            plan_.bufs[buf].external = true;
+            plan_.bufs[buf].payload = slot_idx;
+            info_[c.res].buf = buf;
+            g_.buf_version[buf] = 1;
+            bind_own_buffer(c.res, buf, c.dims);
+            return;
+        }
+        int buf = persistent ? id_buffer(c.res, c.dims) : new_buffer(n, name(c.res), false);
+        if (!persistent) info_[c.res].buf = buf;
+        before_write(buf, {c.res});
+        Step& s = push_step(Step::UPLOAD);
+        s.buf = buf;
+        s.payload = slot_idx;
+        s.nelem = n;
+        touch(buf, s.pos);
+        g_.buf_version[buf]++;
+        bind_own_buffer(c.res, buf, c.dims);
+    }
+
+    // destination buffer of a kernel-producing command (Sum, DotProduct)
+    int result_buffer(uint32_t id, const Shape& shape) {
+        int buf;
+        if (info_[id].needs_buffer()) buf = id_buffer(id, shape);
+        else {
+            buf = new_buffer(numel(shape), name(id), false);
+            info_[id].buf = buf;
+        }
+        return buf;
+    }
+
+    void lower_sum(const Cmd& c) {
+        Node* a = resolve(c.a);
+        if (a->shape.size() != 2) fail("Reduce (sum) node needs dim=2 ('" + name(c.a) + "')");
+        int64_t V = a->shape[0], R = a->shape[1];
+        consume(c.a);
+        if (a->kind == N_CONST && (a->cval == 0.0f)) {
+            after_op(c.res, g_.constant(0.0f, {V}));
+            return;
+        }
+        // the same reduction of the same value was computed before and is still in memory
+        // (what the reference's repeat_opt does on the IR, src/ir/opts/repeat_opt.rs:5-71)
+        {
+            auto it = sum_cse_.find(a);
+            if (it != sum_cse_.end() && g_.load_valid(it->second)) {
+                bind_value(c.res, it->second);
+                return;
+            }
+        }
+        Node* sum_key = a;
+        if (a->kind == N_PIECE && a->pdim != 0) a = materialize_node(a);
+        if (a->nops > opt_.fuse_limit && g_.dag_size(a) > opt_.fuse_limit) a = materialize_node(a);
+        int buf = result_buffer(c.res, {V});
+        before_write(buf, {c.res});
+        std::vector<StoreTask> parts;
+        if (a->kind == N_PIECE) {
+            int64_t start = 0;
+            for (size_t i = 0; i < a->kids.size(); i++) {
+                Node* kid = g_.canon(a->kids[i]);
+                if (kid->kind == N_PIECE) kid = materialize_node(kid);
+                View v = contiguous_view({V});
+                slice_view(v, 0, start, a->ends[i]);
+                parts.push_back({kid, buf, v});
+                start = a->ends[i];
+            }
+        } else
+            parts.push_back({a, buf, contiguous_view({V})});
+        for (auto& p : parts) {
+            KernelSpec k;
+            k.type = KernelSpec::REDUCE;
+            k.n = p.node->shape[0];
+            k.r = R;
+            if (k.n == 0) continue;
+            SsaBuilder sb(*this, k, true);
+            KernelSpec::Out o;
+            o.ssa = sb.build(p.node);
+            o.dst.buf = buf;
+            o.dst.offset = p.view.offset;
+            o.dst.xsubs = p.view.dims[0];
+            k.outs.push_back(o);
+            plan_reduce(k, opt_.sm_count);
+            if (k.split > 1) {
+                // two passes: `split` partial sums per row into scratch memory, then a small reduce of
+                // the partials (row mode keeps them next to each other, column mode one row per part)
+                KernelSpec::Out final_out = k.outs[0];
+                int scratch = temp_buffer(k.n * k.split);
+                k.scratch = scratch;
+                k.outs[0].dst = Operand();
+                k.outs[0].dst.buf = scratch;
+                if (k.n > 1) k.outs[0].dst.xsubs = {{k.n, 1}};
+                KernelSpec k2;
+                k2.type = KernelSpec::REDUCE;
+                k2.n = k.n;
+                k2.r = k.split;
+                Operand in;
+                in.buf = scratch;
+                if (k.mode == 0) {
+                    if (k.n > 1) in.xsubs = {{k.n, k.split}};
+                    in.subs = {{k.split, 1}};
+                } else {
+                    if (k.n > 1) in.xsubs = {{k.n, 1}};
+                    in.subs = {{k.split, k.n}};
+                }
+                k2.ins.push_back(in);
+                Ssa ld;
+                ld.kind = Ssa::LOAD;
+                ld.operand = 0;
+                k2.ssa.push_back(ld);
+                final_out.ssa = 0;
+                k2.outs.push_back(final_out);
+                plan_reduce(k2, opt_.sm_count);
+                k2.split = 1;
+                plan_.kernels.push_back(std::move(k));
+                Step& s1 = push_step(Step::REDUCE);
+                s1.kernel = int(plan_.kernels.size()) - 1;
+                for (auto& in1 : plan_.kernels.back().ins) touch(in1.buf, s1.pos);
+                touch(scratch, s1.pos);
+                plan_.kernels.push_back(std::move(k2));
+                Step& s2 = push_step(Step::REDUCE);
+                s2.kernel = int(plan_.kernels.size()) - 1;
+                touch(scratch, s2.pos);
+                touch(buf, s2.pos);
+                continue;
+            }
+            plan_.kernels.push_back(std::move(k));
+            Step& s = push_step(Step::REDUCE);
+            s.kernel = int(plan_.kernels.size()) - 1;
+            for (auto& in : plan_.kernels.back().ins) touch(in.buf, s.pos);
+            touch(buf, s.pos);
+        }
+        g_.buf_version[buf]++;
+        bind_own_buffer(c.res, buf, {V});
+        sum_cse_[sum_key] = bind_[c.res].node;
+        sum_cse_[g_.canon(sum_key)] = bind_[c.res].node;
+    }
+
+    // a GEMM operand: 2-d strided read of a buffer (anything else is copied out first)
+    struct MatOperand {
+        int buf;
+        int64_t off, rs, cs;
+    };
+    MatOperand matrix_operand(Node* n) {
+        n = g_.canon(n);
+        bool ok = n->kind == N_LOAD && n->view.dims[0].size() <= 1 && n->view.dims[1].size() <= 1;
+        if (ok) {
+            int64_t rs = n->view.dims[0].empty() ? 0 : n->view.dims[0][0].stride;
+            int64_t cs = n->view.dims[1].empty() ? 0 : n->view.dims[1][0].stride;
+            // a broadcast (stride-0) axis of length > 1 is not a matrix in memory
+            if ((rs == 0 && n->shape[0] > 1) || (cs == 0 && n->shape[1] > 1)) ok = false;
+            if (ok) {
+                if (n->shape[0] == 1) rs = n->shape[1] * (cs ? cs : 1);
+                if (n->shape[1] == 1) cs = 1;
+                return {n->buf, n->view.offset, rs, cs};
+            }
+        }
+        Node* m = materialize_node(n);
+        return {m->buf, 0, n->shape[1], 1};
+    }
+
+    void lower_dot(const Cmd& c) {
+        Node* a = resolve(c.a);
+        Node* b = resolve(c.b);
+        if (a->shape.size() != 2) fail("A must be a 2d array");
+        if (b->shape.size() != 2) fail("B must be a 2d array");
+        if (a->shape[1] != b->shape[0]) fail("A's second dimension must equal B's first dimension");
+        int64_t M = a->shape[0], K = a->shape[1], N = b->shape[1];
+        consume(c.a);
+        consume(c.b);
+        std::pair<Node*, Node*> dot_key{a, b};
+        {
+            auto it = dot_cse_.find(dot_key);
+            if (it != dot_cse_.end() && g_.load_valid(it->second)) {
+                bind_value(c.res, it->second);
+                return;
+            }
+        }
+        MatOperand ma = matrix_operand(a);
+        MatOperand mb = matrix_operand(b);
+        Shape rs{M, N};
+        int buf = result_buffer(c.res, rs);
+        before_write(buf, {c.res});
+        Step& s = push_step(Step::GEMM);
+        s.gemm.a = ma.buf; s.gemm.b = mb.buf; s.gemm.c = buf;
+        s.gemm.M = M; s.gemm.N = N; s.gemm.K = K;
+        s.gemm.a_off = ma.off; s.gemm.b_off = mb.off; s.gemm.c_off = 0;
+        s.gemm.a_rs = ma.rs; s.gemm.a_cs = ma.cs; s.gemm.b_rs = mb.rs; s.gemm.b_cs = mb.cs;
+        touch(ma.buf, s.pos);
+        touch(mb.buf, s.pos);
+        touch(buf, s.pos);
+        g_.buf_version[buf]++;
+        bind_own_buffer(c.res, buf, rs);
+        dot_cse_[dot_key] = bind_[c.res].node;
+        // operands that were just written to memory are found under their new identity as well
+        dot_cse_[{g_.canon(a), g_.canon(b)}] = bind_[c.res].node;
+    }
+
+    void lower_allreduce(const Cmd& c) {
+        if (bind_[c.a].kind != Binding::VALUE) fail("AllReduce target '" + name(c.a) + "' must be a tensor, not a view");
+        consume(c.a);
+        materialize_ids({c.a});  // the id is cross-segment by construction, so this is its own buffer
+        Node* a = resolve(c.a);
+        if (a->kind != N_LOAD || info_[c.a].buf != a->buf) fail("internal: AllReduce target has no buffer");
+        int buf = a->buf;
+        before_write(buf, {c.a});
+        Step& s = push_step(Step::ALLREDUCE);
+        s.buf = buf;
+        s.off = 0;
+        s.nelem = numel(a->shape);
+        touch(buf, s.pos);
+        g_.buf_version[buf]++;
+        bind_own_buffer(c.a, buf, a->shape);
+    }
+
+    std::pair<int, int64_t> condition_location(uint32_t id) {
+        Node* n = resolve(id);
+        if (numel(n->shape) != 1) fail("condition '" + name(id) + "' must have dim of [1]");
+        if (n->kind != N_LOAD) {
+            bind_[id].pending = true;
+            if (bind_[id].kind == Binding::ALIAS) {
+                Node* m = materialize_node(n);
+                return {m->buf, m->view.offset};
+            }
+            materialize_ids({id});
+            n = resolve(id);
+        }
+        return {n->buf, n->view.offset};
+    }
+
+    void refresh_bindings() {
+        for (auto& b : bind_) {
+            if (b.kind == Binding::VALUE && b.node) {
+                Node* n = g_.canon(b.node);
+                if (n->kind == N_LOAD && !g_.load_valid(n)) b.node = g_.load(n->buf, n->shape, n->view);
+            }
+            b.cache = nullptr;
+        }
+    }
+
+    // returns true when an EX was reached at this level
+    bool lower_block(Block& blk, bool top) {
+        for (auto& c : blk.cmds) {
+            if (c.op == OP_EX) {
+                flush_pending();
+                if (top) {
+                    finalize_results();
+                    push_step(Step::EXIT);
+                    return true;
+                }
+                push_step(Step::EXIT);
+                continue;
+            }
+            if (c.op == OP_WHILE) {
+                flush_pending();
+                auto loc = condition_location(c.a);
+                consume(c.a);
+                StepBlock* saved = cur_;
+                Step& s = push_step(Step::WHILE);
+                s.cond_buf = loc.first;
+                s.cond_off = loc.second;
+                touch(loc.first, s.pos);
+                s.body = std::make_unique<StepBlock>();
+                int first = pos_;
+                StepBlock* body = s.body.get();
+                cur_ = body;
+                lower_block(*c.block, false);
+                flush_pending();
+                cur_ = saved;
+                loop_spans_.push_back({first, pos_});
+                auto loc2 = condition_location(c.a);
+                if (loc2 != loc) fail("While condition '" + name(c.a) + "' moves to another buffer inside the loop");
+                refresh_bindings();
+                continue;
+            }
+            if (c.op == OP_IF) {
+                flush_pending();
+                StepBlock* saved = cur_;
+                std::vector<std::pair<int, int64_t>> locs;
+                for (auto& cb : c.conds) {
+                    locs.push_back(condition_location(cb.first));
+                    consume(cb.first);
+                }
+                Step& s = push_step(Step::IF);
+                Step* sp = &s;
+                for (auto& loc : locs) {
+                    touch(loc.first, sp->pos);
+                    Step::Branch br;
+                    br.cond_buf = loc.first;
+                    br.cond_off = loc.second;
+                    sp->branches.push_back(std::move(br));
+                }
+                std::vector<Binding> snapshot = bind_;
+                for (size_t k = 0; k < c.conds.size(); k++) {
+                    sp->branches[k].body = std::make_unique<StepBlock>();
+                    cur_ = sp->branches[k].body.get();
+                    lower_block(*c.conds[k].second, false);
+                    flush_pending();
+                    restore_after_branch(snapshot);
+                }
+                if (c.else_block) {
+                    sp->else_body = std::make_unique<StepBlock>();
+                    cur_ = sp->else_body.get();
+                    lower_block(*c.else_block, false);
+                    flush_pending();
+                    restore_after_branch(snapshot);
+                }
+                cur_ = saved;
+                continue;
+            }
+            if (!live(c)) continue;
+            lower_cmd(c);
+        }
+        return false;
+    }
+
+    // after a conditional branch: ids (re)defined inside live in their persistent buffers, everything
+    // else looks as it did before the branch
+    void restore_after_branch(const std::vector<Binding>& snapshot) {
+        for (size_t id = 0; id < bind_.size(); id++) {
+            Binding& b = bind_[id];
+            const Binding& s = snapshot[id];
+            bool changed = b.kind != s.kind || b.node != s.node || b.cmd != s.cmd;
+            if (!changed) continue;
+            if (info_[id].buf >= 0 && info_[id].needs_buffer() && b.kind == Binding::VALUE) {
+                Node* n = g_.canon(b.node);
+                b.node = g_.load(info_[id].buf, n->shape, contiguous_view(n->shape));
+                b.pending = false;
+            } else
+                b = s;
+        }
+        refresh_bindings();
+    }
+
+    void finalize_results() {
+        if (results_done_) return;
+        flush_pending();
+        for (auto id : prog_.dep) {
+            ResultInfo r;
+            r.id = name(id);
+            Binding& b = bind_[id];
+            if (b.kind == Binding::UNDEF) {
+                plan_.results.push_back(r);
+                continue;
+            }
+            Node* n = resolve(id);
+            if (!(n->kind == N_LOAD && view_is_contiguous(n->view, n->shape))) n = materialize_node(n);
+            r.shape = n->shape;
+            r.buf = n->buf;
+            r.off = n->view.offset;
+            plan_.bufs[n->buf].persistent = true;
+            plan_.results.push_back(r);
+        }
+        results_done_ = true;
+    }
+
+    // ------------------------------------------------------------------ arena
+    void plan_arena() {
+        auto& bufs = plan_.bufs;
+        // a buffer touched inside a loop and also outside of it must survive the whole loop
+        for (int pass = 0; pass < 3; pass++)
+        for (auto& b : bufs) {
+            if (b.persistent || b.external || b.last < 0) continue;
+            for (auto& sp : loop_spans_) {
+                bool inside = b.first >= sp.first && b.last < sp.second;
+                bool overlaps = b.last >= sp.first && b.first < sp.second;
+                if (overlaps && !inside) {
+                    b.first = std::min(b.first, sp.first);
+                    b.last = std::max(b.last, sp.second);
+                }
+            }
+        }
+        std::vector<int> order;
+        for (size_t i = 0; i < bufs.size(); i++)
+            if (!bufs[i].external && (bufs[i].last >= 0 || bufs[i].persistent) && bufs[i].numel > 0) order.push_back(int(i));
+        std::sort(order.begin(), order.end(), [&](int x, int y) {
+            if (bufs[x].numel != bufs[y].numel) return bufs[x].numel > bufs[y].numel;
+            return x < y;
+        });
+        struct Placed { int64_t off, size; int first, last; };
+        std::vector<Placed> placed;
+        int64_t top = 0;
+        for (int i : order) {
+            auto& b = bufs[i];
+            int first = b.persistent ? INT_MIN : b.first;
+            int last = b.persistent ? INT_MAX : b.last;
+            int64_t size = ((b.numel * 4 + 255) / 256) * 256;
+            std::vector<std::pair<int64_t, int64_t>> busy;
+            for (auto& p : placed)
+                if (!(p.last < first || last < p.first)) busy.push_back({p.off, p.off + p.size});
+            std::sort(busy.begin(), busy.end());
+            int64_t off = 0;
+            for (auto& iv : busy) {
+                if (off + size <= iv.first) break;
+                off = std::max(off, iv.second);
+            }
+            b.arena_off = off;
+            placed.push_back({off, size, first, last});
+            top = std::max(top, off + size);
+        }
+        plan_.arena_bytes = top;
+    }
+};
+
+}  // namespace
+
+void lower_program(Program& prog, Plan& plan, const LowerOptions& opt) {
+    Lowerer l(prog, plan, opt);
+    l.run();
+}
+
+// ---------------------------------------------------------------------- listing
+static const char* eop_name(EOp o) {
+    switch (o) {
+    case E_ADD: return "+";
+    case E_MUL: return "*";
+    case E_EXP2: return "exp2";
+    case E_LOG2: return "log2";
+    case E_SIN: return "sin";
+    case E_RECIP: return "recip";
+    case E_SQRT: return "sqrt_abs";
+    case E_EQZ: return "eqz";
+    case E_GTZ: return "gtz";
+    case E_LTZ: return "ltz";
+    }
+    return "?";
+}
+
+static std::string subs_str(const std::vector<Sub>& s) {
+    std::ostringstream o;
+    o << "[";
+    for (size_t i = 0; i < s.size(); i++) o << (i ? " " : "") << s[i].size << "x" << s[i].stride;
+    o << "]";
+    return o.str();
+}
+
+static void dump_block(const Plan& p, const StepBlock& b, int ind, bool src, std::ostringstream& o) {
+    std::string pad(size_t(ind) * 2, ' ');
+    for (auto& s : b.steps) {
+        switch (s.kind) {
+        case Step::ELW: case Step::REDUCE: {
+            auto& k = p.kernels[s.kernel];
+            int nops = 0;
+            for (auto& x : k.ssa) nops += x.kind == Ssa::OP;
+            if (s.kind == Step::ELW) o << pad << "#" << s.pos << " elw n=" << k.n;
+            else o << pad << "#" << s.pos << " reduce rows=" << k.n << " len=" << k.r << " mode=" << (k.mode ? "col" : "row") << " split=" << k.split;
+            o << " ops=" << nops << " vec=" << k.vec << " ins=" << k.ins.size() << " outs=" << k.outs.size() << " " << k.entry << "\n";
+            for (auto& in : k.ins)
+                o << pad << "    in  " << p.bufs[in.buf].name << "+" << in.offset << " " << (s.kind == Step::REDUCE ? subs_str(in.xsubs) + "," : "") << subs_str(in.subs) << "\n";
+            for (auto& out : k.outs)
+                o << pad << "    out " << p.bufs[out.dst.buf].name << "+" << out.dst.offset << " " << (s.kind == Step::REDUCE ? subs_str(out.dst.xsubs) : subs_str(out.dst.subs)) << "\n";
+            if (src) {
+                for (size_t i = 0; i < k.ssa.size(); i++) {
+                    auto& x = k.ssa[i];
+                    o << pad << "      v" << i << " = ";
+                    if (x.kind == Ssa::LOAD) o << "load in" << x.operand;
+                    else if (x.kind == Ssa::CONST) o << x.c;
+                    else if (x.b >= 0) o << "v" << x.a << " " << eop_name(x.op) << " v" << x.b;
+                    else o << eop_name(x.op) << "(v" << x.a << ")";
+                    o << "\n";
+                }
+            }
+            break;
+        }
+        case Step::GEMM:
+            o << pad << "#" << s.pos << " gemm " << p.bufs[s.gemm.c].name << "[" << s.gemm.M << "," << s.gemm.N << "] = "
+              << p.bufs[s.gemm.a].name << "+" << s.gemm.a_off << "(" << s.gemm.a_rs << "," << s.gemm.a_cs << ") . "
+              << p.bufs[s.gemm.b].name << "+" << s.gemm.b_off << "(" << s.gemm.b_rs << "," << s.gemm.b_cs << ") K=" << s.gemm.K << "\n";
+            break;
+        case Step::UPLOAD:
+            o << pad << "#" << s.pos << " upload " << p.bufs[s.buf].name << " n=" << s.nelem << "\n";
+            break;
+        case Step::ALLREDUCE:
+            o << pad << "#" << s.pos << " allreduce " << p.bufs[s.buf].name << " n=" << s.nelem << "\n";
+            break;
+        case Step::WHILE:
+            o << pad << "#" << s.pos << " while (" << p.bufs[s.cond_buf].name << "+" << s.cond_off << " != 0) {\n";
+            dump_block(p, *s.body, ind + 1, src, o);
+            o << pad << "}\n";
+            break;
+        case Step::IF:
+            for (size_t k = 0; k < s.branches.size(); k++) {
+                o << pad << "#" << s.pos << (k ? " else if (" : " if (") << p.bufs[s.branches[k].cond_buf].name << "+" << s.branches[k].cond_off << " == 1) {\n";
+                dump_block(p, *s.branches[k].body, ind + 1, src, o);
+                o << pad << "}\n";
+            }
+            if (s.else_body) {
+                o << pad << "else {\n";
+                dump_block(p, *s.else_body, ind + 1, src, o);
+                o << pad << "}\n";
+            }
+            break;
+        case Step::EXIT: o << pad << "#" << s.pos << " exit\n"; break;
+        }
+    }
+}
+
+std::string dump_plan(const Plan& plan, bool with_source) {
+    std::ostringstream o;
+    o << "plan: " << plan.ir_commands << " IR commands -> " << plan.n_steps << " steps, " << plan.kernels.size()
+      << " kernels, arena " << plan.arena_bytes << " B, " << plan.bufs.size() << " buffers\n";
+    dump_block(plan, plan.main, 0, with_source, o);
+    o << "results:";
+    for (auto& r : plan.results) o << " " << r.id << (r.buf >= 0 ? "@" + plan.bufs[r.buf].name : "(none)");
+    o << "\n";
+    if (with_source) {
+        std::set<std::string> seen;
+        for (auto& k : plan.kernels)
+            if (!k.source.empty() && seen.insert(k.entry).second) o << "// ---- " << k.entry << "\n" << k.source << "\n";
+    }
+    return o.str();
+}
+
+}  // namespace adb

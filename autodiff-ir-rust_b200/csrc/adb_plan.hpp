@@ -1,0 +1,142 @@
+// The lowered program: what the reference calls a `KernelProcedure` (src/kernel/kernel_decl.rs:81-189),
+// re-designed for this backend.  Instead of thirteen `Kernels` variants holding `Expression` index
+// trees, a plan is a tree of steps over three kernel kinds:
+//   ELW     one fused element-wise kernel: straight-line SSA over strided loads, one pass, any number
+//           of outputs (covers Unary / Binary / Movement / ElwExpr of the reference)
+//   REDUCE  row sum with the producing expression fused in front (Reduce / ReduceElwExpr)
+//   GEMM    C = A.B on strided 2-d operands (DotProd)
+// plus uploads, collectives and host-driven control flow (While / If / EX).
+#pragma once
+#include <climits>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "adb_node.hpp"
+
+namespace adb {
+
+struct BufferInfo {
+    int64_t numel = 0;
+    bool external = false;   // caller-owned device memory used in place (never written)
+    int payload = -1;        // external: index of the payload slot holding the address
+    bool persistent = false; // live for the whole program (ids that cross blocks, results)
+    int first = INT_MAX, last = -1;
+    int64_t arena_off = -1;  // byte offset in the arena
+    std::string name;
+};
+
+// one strided access of a kernel: flat digits (outer -> inner) over the kernel's index space
+struct Operand {
+    int buf = -1;
+    int64_t offset = 0;          // elements; applied by the host to the pointer at launch
+    std::vector<Sub> subs;       // ELW: digits over the linear index; REDUCE: digits over y (the summed axis)
+    std::vector<Sub> xsubs;      // REDUCE: digits over x (the kept axis)
+    bool same_access(const Operand& o) const {
+        return buf == o.buf && offset == o.offset && subs == o.subs && xsubs == o.xsubs;
+    }
+};
+
+struct Ssa {
+    enum Kind : uint8_t { LOAD, CONST, OP } kind = CONST;
+    int operand = -1;  // LOAD
+    float c = 0.f;     // CONST
+    EOp op = E_ADD;    // OP
+    int a = -1, b = -1;
+};
+
+struct KernelSpec {
+    enum Type { ELW, REDUCE } type = ELW;
+    int64_t n = 0;  // ELW: elements; REDUCE: rows kept (V)
+    int64_t r = 0;  // REDUCE: elements summed per row (R)
+    std::vector<Operand> ins;
+    std::vector<Ssa> ssa;
+    struct Out {
+        int ssa;
+        Operand dst;
+    };
+    std::vector<Out> outs;  // REDUCE: one entry; `ssa` is the summand, dst is indexed by x
+    // filled in by the code generator
+    std::string source, entry;
+    int vec = 1;            // elements per thread along the innermost digit
+    int mode = 0;           // REDUCE: 0 = lanes along y (row), 1 = lanes along x (column)
+    int threads = 256;
+    int64_t split = 1;      // REDUCE: number of partial sums per row (two-pass when > 1)
+    int jit = -1;           // index into the module cache
+    int jit2 = -1;          // REDUCE: second-pass kernel
+    int scratch = -1;       // REDUCE two-pass: buffer holding the partial sums
+    bool wide_index = false;
+};
+
+struct StepBlock;
+
+struct Step {
+    enum Kind { ELW, REDUCE, GEMM, UPLOAD, ALLREDUCE, WHILE, IF, EXIT } kind = EXIT;
+    int pos = 0;
+    int kernel = -1;
+    // GEMM: C[M,N] = A[M,K] . B[K,N], strides in elements
+    struct Gemm {
+        int a = -1, b = -1, c = -1;
+        int64_t M = 0, N = 0, K = 0;
+        int64_t a_off = 0, b_off = 0, c_off = 0;
+        int64_t a_rs = 0, a_cs = 0, b_rs = 0, b_cs = 0;
+    } gemm;
+    // UPLOAD: payload slot -> buffer; ALLREDUCE: buffer range
+    int buf = -1;
+    int payload = -1;
+    int64_t off = 0, nelem = 0;
+    // control flow: conditions are single floats living at (buf, off)
+    int cond_buf = -1;
+    int64_t cond_off = 0;
+    std::unique_ptr<StepBlock> body;  // WHILE
+    struct Branch {
+        int cond_buf;
+        int64_t cond_off;
+        std::unique_ptr<StepBlock> body;
+    };
+    std::vector<Branch> branches;  // IF
+    std::unique_ptr<StepBlock> else_body;
+};
+
+struct StepBlock {
+    std::vector<Step> steps;
+};
+
+struct PayloadSlot {
+    uint8_t kind = 0;   // PayloadKind
+    uint64_t addr = 0;  // host or device address, rebound on every execute
+    int64_t count = 0;  // elements
+    int cmd_index = -1; // which CreateMat of the program (in program order) feeds this slot
+    bool assumed_const = false;  // the plan folded this payload to a constant because every element was equal
+    float const_val = 0.f;
+};
+
+struct ResultInfo {
+    std::string id;
+    Shape shape;
+    int buf = -1;      // -1: the id was never defined
+    int64_t off = 0;
+};
+
+struct Plan {
+    std::vector<BufferInfo> bufs;
+    std::vector<KernelSpec> kernels;
+    StepBlock main;
+    std::vector<PayloadSlot> payloads;
+    std::vector<ResultInfo> results;
+    int64_t arena_bytes = 0;
+    int n_steps = 0;
+    size_t ir_commands = 0;
+    uint64_t key = 0;
+};
+
+struct LowerOptions {
+    bool no_fusion = false;
+    int64_t fuse_limit = 768;  // largest expression DAG fused into one kernel
+    int rank = 0, world = 1;
+    int sm_count = 148;        // B200: 148 SMs; reduce kernels split rows until every SM has work
+};
+
+std::string dump_plan(const Plan& plan, bool with_source);
+
+}  // namespace adb

@@ -1,0 +1,830 @@
+// Runtime behind the C-ABI: JIT of the generated kernels, device arena, executor.
+//
+// Replaces the reference's OpenCL host runtime: `OpenCL::execute` / `proc_exec` / `exec`
+// (src/devices/opencl/device.rs:62-164) and `OpenCLContext` (src/devices/opencl/context.rs:19-106).
+// Differences by design: one arena laid out from buffer lifetimes instead of a buffer per id; no
+// per-kernel wait (one stream, one synchronisation at the end); loop bodies are captured once into
+// CUDA graphs and replayed, the host only reads the 4-byte condition between replays; compiled
+// plans and kernels are cached across `execute` calls instead of being rebuilt every time
+// (device.rs:63-65 builds a fresh context per call).
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <nccl.h>
+#include <nvrtc.h>
+
+#include <chrono>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/adb200.h"
+#include "adb_gemm.hpp"
+#include "adb_lower.hpp"
+#include "adb_shard.hpp"
+
+namespace adb {
+
+// ------------------------------------------------------------------------------------------ JIT
+struct CompiledKernel {
+    std::vector<char> cubin;
+    cudaLibrary_t lib = nullptr;
+    cudaKernel_t fn = nullptr;
+};
+
+static bool nvrtc_compile(const std::string& src, const std::string& entry, std::vector<char>& cubin, std::string& log) {
+    nvrtcProgram prog;
+    if (nvrtcCreateProgram(&prog, src.c_str(), (entry + ".cu").c_str(), 0, nullptr, nullptr) != NVRTC_SUCCESS) {
+        log = "nvrtcCreateProgram failed";
+        return false;
+    }
+    const char* opts[] = {"--gpu-architecture=sm_100a", "--std=c++17", "-default-device", "--fmad=false", "-lineinfo"};
+    nvrtcResult rc = nvrtcCompileProgram(prog, int(sizeof(opts) / sizeof(opts[0])), opts);
+    if (rc != NVRTC_SUCCESS) {
+        size_t n = 0;
+        nvrtcGetProgramLogSize(prog, &n);
+        log.resize(n);
+        if (n) nvrtcGetProgramLog(prog, &log[0]);
+        log = std::string("NVRTC: ") + nvrtcGetErrorString(rc) + "\n" + log;
+        nvrtcDestroyProgram(&prog);
+        return false;
+    }
+    size_t n = 0;
+    nvrtcGetCUBINSize(prog, &n);
+    cubin.resize(n);
+    nvrtcGetCUBIN(prog, cubin.data());
+    nvrtcDestroyProgram(&prog);
+    return true;
+}
+
+// ------------------------------------------------------------------------------------------ NCCL (loaded lazily)
+struct NcclApi {
+    void* handle = nullptr;
+    decltype(&ncclGetUniqueId) GetUniqueId = nullptr;
+    decltype(&ncclCommInitRank) CommInitRank = nullptr;
+    decltype(&ncclAllReduce) AllReduce = nullptr;
+    decltype(&ncclCommDestroy) CommDestroy = nullptr;
+    decltype(&ncclGetErrorString) GetErrorString = nullptr;
+    // libnccl is opened on first use so that single-GPU runs (and hosts without it) never need it; when
+    // the caller's process already holds a libnccl.so.2 (torch.distributed), that copy is the one bound.
+    bool load(std::string& err) {
+        if (handle) return true;
+        handle = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!handle) { err = std::string("cannot load libnccl.so.2: ") + dlerror(); return false; }
+        GetUniqueId = (decltype(GetUniqueId))dlsym(handle, "ncclGetUniqueId");
+        CommInitRank = (decltype(CommInitRank))dlsym(handle, "ncclCommInitRank");
+        AllReduce = (decltype(AllReduce))dlsym(handle, "ncclAllReduce");
+        CommDestroy = (decltype(CommDestroy))dlsym(handle, "ncclCommDestroy");
+        GetErrorString = (decltype(GetErrorString))dlsym(handle, "ncclGetErrorString");
+        if (!GetUniqueId || !CommInitRank || !AllReduce || !CommDestroy) { err = "libnccl.so.2 lacks expected symbols"; return false; }
+        return true;
+    }
+};
+static NcclApi g_nccl;
+
+// ------------------------------------------------------------------------------------------ device
+struct GraphSeg {
+    size_t begin = 0, end = 0;       // [begin, end) steps of the block
+    cudaGraphExec_t exec = nullptr;  // null: run the steps one by one
+    uint64_t launches = 0, gemms = 0;
+};
+
+struct CompiledPlan {
+    Plan plan;
+    std::vector<int> kernel_slot;  // plan kernel -> device kernel cache slot
+    std::map<const StepBlock*, std::vector<GraphSeg>> graphs;
+    uint64_t graph_epoch = 0;      // arena generation + external addresses the graphs were captured with
+    double lower_ms = 0;
+};
+
+}  // namespace adb
+
+using namespace adb;
+
+struct adb_device {
+    int ordinal = 0;
+    int rank = 0, world = 1;
+    uint32_t flags = 0;
+    uint64_t shard_batch = 0;
+    int sm_count = 148;
+    cudaStream_t stream = nullptr;
+    std::string err;
+    // kernels compiled so far, by entry name
+    std::unordered_map<std::string, int> kernel_index;
+    std::vector<CompiledKernel> kernels;
+    // plans by structural key
+    std::unordered_map<uint64_t, std::unique_ptr<CompiledPlan>> plans;
+    CompiledPlan* last = nullptr;
+    // arena
+    char* arena = nullptr;
+    size_t arena_cap = 0;
+    uint64_t arena_gen = 1;
+    // condition read-back
+    float* cond_host = nullptr;
+    // results of the last execute
+    struct HostResult {
+        std::string id;
+        std::vector<uint64_t> dims;
+        float* host = nullptr;      // pinned, cached across calls
+        size_t host_cap = 0;
+        const float* dev = nullptr;
+        size_t n = 0;
+        bool valid = false;
+        bool fetched = false;
+    };
+    std::vector<HostResult> results;
+    std::vector<std::pair<float*, size_t>> pinned_pool;
+    adb_stats stats{};
+    ncclComm_t nccl_comm = nullptr;
+    GemmContext gemm;
+    bool exit_requested = false;
+    std::vector<cudaEvent_t> ev_pool;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> upload_events;
+};
+
+namespace {
+
+struct CudaFail {
+    std::string msg;
+};
+
+void ck(cudaError_t e, const char* what) {
+    if (e != cudaSuccess) throw CudaFail{std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")"};
+}
+
+uint64_t fnv_bytes(const void* p, size_t n, uint64_t h = 1469598103934665603ull) {
+    const unsigned char* c = static_cast<const unsigned char*>(p);
+    for (size_t i = 0; i < n; i++) { h ^= c[i]; h *= 1099511628211ull; }
+    return h;
+}
+
+// hash of everything in the program except payload addresses and payload data
+uint64_t structure_key(Program& prog, uint32_t flags, int rank, int world, uint64_t shard_batch) {
+    struct Saved { Cmd* c; uint64_t payload; uint8_t kind; };
+    std::vector<Saved> saved;
+    std::function<void(Block&)> strip = [&](Block& b) {
+        for (auto& c : b.cmds) {
+            if (c.op == OP_CREATE_MAT) {
+                saved.push_back({&c, c.payload, c.payload_kind});
+                c.payload = 0;
+                // inline payloads would be appended by the serialiser; hash them as pointers instead
+                if (c.payload_kind == PAYLOAD_INLINE) c.payload_kind = PAYLOAD_HOST;
+            } else if (c.op == OP_WHILE) strip(*c.block);
+            else if (c.op == OP_IF) {
+                for (auto& cb : c.conds) strip(*cb.second);
+                if (c.else_block) strip(*c.else_block);
+            }
+        }
+    };
+    strip(prog.main);
+    std::vector<uint8_t> bytes = serialize_program(prog);
+    for (auto& s : saved) { s.c->payload = s.payload; s.c->payload_kind = s.kind; }
+    uint64_t h = fnv_bytes(bytes.data(), bytes.size());
+    // the device-vs-host distinction changes the plan (resident payloads are read in place)
+    for (auto& s : saved) { uint8_t k = s.kind == PAYLOAD_DEVICE ? 1 : 0; h = fnv_bytes(&k, 1, h); }
+    uint64_t extra[4] = {flags, uint64_t(rank), uint64_t(world), shard_batch};
+    return fnv_bytes(extra, sizeof extra, h);
+}
+
+void collect_payload_cmds(Block& b, std::vector<Cmd*>& out, const std::vector<char>* live) {
+    (void)live;
+    for (auto& c : b.cmds) {
+        if (c.op == OP_CREATE_MAT) out.push_back(&c);
+        else if (c.op == OP_WHILE) collect_payload_cmds(*c.block, out, live);
+        else if (c.op == OP_IF) {
+            for (auto& cb : c.conds) collect_payload_cmds(*cb.second, out, live);
+            if (c.else_block) collect_payload_cmds(*c.else_block, out, live);
+        }
+    }
+}
+
+bool payload_uniform(const float* p, int64_t n, float v) {
+    uint32_t want;
+    std::memcpy(&want, &v, 4);
+    const uint32_t* u = reinterpret_cast<const uint32_t*>(p);
+    for (int64_t i = 0; i < n; i++)
+        if (u[i] != want) return false;
+    return n > 0;
+}
+
+class Executor {
+  public:
+    Executor(adb_device* d, CompiledPlan* cp) : d_(d), cp_(cp), plan_(cp->plan) {}
+
+    float* buf_ptr(int buf, int64_t elem_off = 0) {
+        const BufferInfo& b = plan_.bufs[buf];
+        if (b.external) return reinterpret_cast<float*>(uintptr_t(plan_.payloads[b.payload].addr)) + elem_off;
+        if (b.arena_off < 0) throw CudaFail{"internal: buffer '" + b.name + "' has no storage"};
+        return reinterpret_cast<float*>(d_->arena + b.arena_off) + elem_off;
+    }
+
+    void launch_kernel(const KernelSpec& k, int slot) {
+        // Args { const float* in[max(1,NI)]; float* out[NO]; long long n; }
+        std::vector<uint64_t> args;
+        size_t ni = std::max<size_t>(1, k.ins.size());
+        args.resize(ni + k.outs.size() + 1, 0);
+        for (size_t i = 0; i < k.ins.size(); i++) args[i] = uint64_t(uintptr_t(buf_ptr(k.ins[i].buf, k.ins[i].offset)));
+        for (size_t i = 0; i < k.outs.size(); i++)
+            args[ni + i] = uint64_t(uintptr_t(buf_ptr(k.outs[i].dst.buf, k.outs[i].dst.offset)));
+        args[ni + k.outs.size()] = uint64_t(k.n);
+        dim3 grid(1, 1, 1), block(256, 1, 1);
+        const int64_t cap = int64_t(d_->sm_count) * 16;
+        if (k.type == KernelSpec::ELW) {
+            int64_t nv = k.n / k.vec;
+            grid.x = unsigned(std::max<int64_t>(1, std::min<int64_t>((nv + 255) / 256, cap)));
+        } else if (k.mode == 0) {
+            int64_t rpb = 256 / k.threads;
+            grid.x = unsigned(std::max<int64_t>(1, std::min<int64_t>((k.n + rpb - 1) / rpb, cap)));
+            grid.y = unsigned(k.split);
+        } else {
+            grid.x = unsigned(std::max<int64_t>(1, (k.n + 32 * k.vec - 1) / (32 * k.vec)));
+            grid.y = unsigned(k.split);
+        }
+        void* params[1] = {args.data()};
+        ck(cudaLaunchKernel((const void*)d_->kernels[slot].fn, grid, block, params, 0, d_->stream), k.entry.c_str());
+        launches_++;
+    }
+
+    void run_step(const Step& s) {
+        switch (s.kind) {
+        case Step::ELW: case Step::REDUCE:
+            launch_kernel(plan_.kernels[s.kernel], cp_->kernel_slot[s.kernel]);
+            break;
+        case Step::GEMM: {
+            const auto& g = s.gemm;
+            GemmArgs a;
+            a.A = buf_ptr(g.a, g.a_off); a.B = buf_ptr(g.b, g.b_off); a.C = buf_ptr(g.c, g.c_off);
+            a.M = g.M; a.N = g.N; a.K = g.K;
+            a.a_rs = g.a_rs; a.a_cs = g.a_cs; a.b_rs = g.b_rs; a.b_cs = g.b_cs;
+            a.force_simt = (d_->flags & ADB_FLAG_SIMT_DOT) != 0;
+            std::string e;
+            int n = gemm_launch(d_->gemm, a, d_->stream, e);
+            if (n < 0) throw CudaFail{"gemm: " + e};
+            launches_ += uint64_t(n);
+            gemms_++;
+            break;
+        }
+        case Step::UPLOAD: {
+            const PayloadSlot& p = plan_.payloads[s.payload];
+            cudaEvent_t e0 = event(), e1 = event();
+            ck(cudaEventRecord(e0, d_->stream), "event");
+            if (p.kind == PAYLOAD_DEVICE) {
+                ck(cudaMemcpyAsync(buf_ptr(s.buf), reinterpret_cast<const void*>(uintptr_t(p.addr)), size_t(s.nelem) * 4,
+                                   cudaMemcpyDeviceToDevice, d_->stream), "upload (device)");
+            } else {
+                ck(cudaMemcpyAsync(buf_ptr(s.buf), reinterpret_cast<const void*>(uintptr_t(p.addr)), size_t(s.nelem) * 4,
+                                   cudaMemcpyHostToDevice, d_->stream), "upload (host)");
+                d_->stats.h2d_bytes += uint64_t(s.nelem) * 4;
+            }
+            ck(cudaEventRecord(e1, d_->stream), "event");
+            d_->upload_events.push_back({e0, e1});
+            break;
+        }
+        case Step::ALLREDUCE: {
+            if (d_->world > 1) {
+                float* p = buf_ptr(s.buf, s.off);
+                ncclResult_t rc = g_nccl.AllReduce(p, p, size_t(s.nelem), ncclFloat32, ncclSum, d_->nccl_comm, d_->stream);
+                if (rc != ncclSuccess) throw CudaFail{std::string("ncclAllReduce: ") + (g_nccl.GetErrorString ? g_nccl.GetErrorString(rc) : "error")};
+                launches_++;
+            }
+            break;
+        }
+        default: break;
+        }
+    }
+
+    float read_cond(int buf, int64_t off) {
+        ck(cudaMemcpyAsync(d_->cond_host, buf_ptr(buf, off), 4, cudaMemcpyDeviceToHost, d_->stream), "condition read-back");
+        ck(cudaStreamSynchronize(d_->stream), "condition sync");
+        d_->stats.d2h_bytes += 4;
+        return *d_->cond_host;
+    }
+
+    static bool capturable(const Step& s, const Plan& plan) {
+        switch (s.kind) {
+        case Step::ELW: case Step::REDUCE: case Step::GEMM: case Step::ALLREDUCE: return true;
+        case Step::UPLOAD: return plan.payloads[s.payload].kind == PAYLOAD_DEVICE;
+        default: return false;
+        }
+    }
+
+    // straight-line runs of a loop body are captured once and replayed
+    std::vector<GraphSeg>& segments(const StepBlock& blk) {
+        auto it = cp_->graphs.find(&blk);
+        if (it != cp_->graphs.end()) return it->second;
+        std::vector<GraphSeg> segs;
+        size_t i = 0;
+        while (i < blk.steps.size()) {
+            size_t j = i;
+            while (j < blk.steps.size() && capturable(blk.steps[j], plan_)) j++;
+            if (j - i >= 2 && !(d_->flags & ADB_FLAG_NO_GRAPHS)) {
+                GraphSeg g;
+                g.begin = i;
+                g.end = j;
+                uint64_t l0 = launches_, g0 = gemms_;
+                cudaGraph_t graph = nullptr;
+                ck(cudaStreamBeginCapture(d_->stream, cudaStreamCaptureModeThreadLocal), "begin capture");
+                try {
+                    for (size_t t = i; t < j; t++) run_step(blk.steps[t]);
+                } catch (...) {
+                    cudaStreamEndCapture(d_->stream, &graph);
+                    if (graph) cudaGraphDestroy(graph);
+                    throw;
+                }
+                ck(cudaStreamEndCapture(d_->stream, &graph), "end capture");
+                g.launches = launches_ - l0;
+                g.gemms = gemms_ - g0;
+                launches_ = l0;
+                gemms_ = g0;
+                ck(cudaGraphInstantiate(&g.exec, graph, 0), "graph instantiate");
+                cudaGraphDestroy(graph);
+                segs.push_back(g);
+                i = j;
+            } else {
+                GraphSeg g;
+                g.begin = i;
+                g.end = std::max(j, i + 1);
+                segs.push_back(g);
+                i = g.end;
+            }
+        }
+        return cp_->graphs.emplace(&blk, std::move(segs)).first->second;
+    }
+
+    void run_block(const StepBlock& blk, bool in_loop) {
+        if (in_loop) {
+            auto& segs = segments(blk);
+            for (auto& g : segs) {
+                if (g.exec) {
+                    ck(cudaGraphLaunch(g.exec, d_->stream), "graph launch");
+                    launches_ += g.launches;
+                    gemms_ += g.gemms;
+                    d_->stats.graph_replays++;
+                } else {
+                    for (size_t t = g.begin; t < g.end; t++) {
+                        run_one(blk.steps[t], true);
+                        if (d_->exit_requested) return;
+                    }
+                }
+            }
+            return;
+        }
+        for (auto& s : blk.steps) {
+            run_one(s, false);
+            if (d_->exit_requested) return;
+        }
+    }
+
+    void run_one(const Step& s, bool in_loop) {
+        switch (s.kind) {
+        case Step::WHILE:
+            // `while (cond[0] != 0.0)`: src/devices/opencl/device.rs:132-137
+            while (read_cond(s.cond_buf, s.cond_off) != 0.0f) {
+                run_block(*s.body, true);
+                d_->stats.while_iterations++;
+                if (d_->exit_requested) return;
+            }
+            break;
+        case Step::IF: {
+            // first condition equal to 1.0 wins, else the else-block: src/devices/opencl/device.rs:118-131
+            bool taken = false;
+            for (auto& br : s.branches) {
+                if (read_cond(br.cond_buf, br.cond_off) == 1.0f) {
+                    run_block(*br.body, in_loop);
+                    taken = true;
+                    break;
+                }
+            }
+            if (!taken && s.else_body) run_block(*s.else_body, in_loop);
+            break;
+        }
+        case Step::EXIT: d_->exit_requested = true; break;
+        default: run_step(s); break;
+        }
+    }
+
+    cudaEvent_t event() {
+        cudaEvent_t e;
+        if (!d_->ev_pool.empty()) {
+            e = d_->ev_pool.back();
+            d_->ev_pool.pop_back();
+        } else
+            ck(cudaEventCreate(&e), "event create");
+        used_events_.push_back(e);
+        return e;
+    }
+    void release_events() {
+        for (auto e : used_events_) d_->ev_pool.push_back(e);
+        used_events_.clear();
+    }
+
+    uint64_t launches_ = 0, gemms_ = 0;
+
+  private:
+    adb_device* d_;
+    CompiledPlan* cp_;
+    Plan& plan_;
+    std::vector<cudaEvent_t> used_events_;
+};
+
+void destroy_graphs(CompiledPlan& cp) {
+    for (auto& kv : cp.graphs)
+        for (auto& g : kv.second)
+            if (g.exec) cudaGraphExecDestroy(g.exec);
+    cp.graphs.clear();
+}
+
+int ensure_kernel(adb_device* d, KernelSpec& k) {
+    auto it = d->kernel_index.find(k.entry);
+    if (it != d->kernel_index.end()) return it->second;
+    CompiledKernel ck_;
+    std::string log;
+    if (!nvrtc_compile(k.source, k.entry, ck_.cubin, log)) throw CudaFail{"JIT of " + k.entry + " failed: " + log + "\n" + k.source};
+    ck(cudaLibraryLoadData(&ck_.lib, ck_.cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0), "cudaLibraryLoadData");
+    ck(cudaLibraryGetKernel(&ck_.fn, ck_.lib, k.entry.c_str()), "cudaLibraryGetKernel");
+    d->stats.jit_compiles++;
+    d->kernels.push_back(std::move(ck_));
+    int slot = int(d->kernels.size()) - 1;
+    d->kernel_index[k.entry] = slot;
+    return slot;
+}
+
+float* pinned_alloc(adb_device* d, size_t bytes, size_t& cap) {
+    for (size_t i = 0; i < d->pinned_pool.size(); i++)
+        if (d->pinned_pool[i].second >= bytes) {
+            auto p = d->pinned_pool[i];
+            d->pinned_pool.erase(d->pinned_pool.begin() + long(i));
+            cap = p.second;
+            return p.first;
+        }
+    float* p = nullptr;
+    size_t want = std::max<size_t>(bytes, 4096);
+    ck(cudaMallocHost(&p, want), "cudaMallocHost");
+    cap = want;
+    return p;
+}
+
+adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
+    auto t_begin = std::chrono::steady_clock::now();
+    Program prog = parse_program(blob, nbytes);
+    d->stats = adb_stats{};
+    d->stats.ir_commands = prog.n_cmds;
+    if (d->world > 1 && d->shard_batch) shard_program(prog, d->rank, d->world, int64_t(d->shard_batch));
+    uint64_t key = structure_key(prog, d->flags, d->rank, d->world, d->shard_batch);
+
+    std::vector<Cmd*> mats;
+    collect_payload_cmds(prog.main, mats, nullptr);
+
+    CompiledPlan* cp = nullptr;
+    auto it = d->plans.find(key);
+    if (it != d->plans.end()) {
+        cp = it->second.get();
+        // a cached plan may have folded a constant-filled payload; that must still hold
+        bool ok = cp->plan.payloads.size() <= mats.size();
+        if (ok) {
+            // payload slots are recorded in program order together with the command index
+            for (size_t s = 0; s < cp->plan.payloads.size() && ok; s++) {
+                PayloadSlot& ps = cp->plan.payloads[s];
+                if (ps.cmd_index < 0 || size_t(ps.cmd_index) >= mats.size()) { ok = false; break; }
+                Cmd* c = mats[size_t(ps.cmd_index)];
+                if (int64_t(c->count) != ps.count) { ok = false; break; }
+                if (ps.assumed_const) {
+                    if (c->payload_kind == PAYLOAD_DEVICE ||
+                        !payload_uniform(reinterpret_cast<const float*>(uintptr_t(c->payload)), ps.count, ps.const_val))
+                        ok = false;
+                } else {
+                    ps.kind = c->payload_kind;
+                    ps.addr = c->payload;
+                }
+            }
+        }
+        if (!ok) {
+            destroy_graphs(*cp);
+            d->plans.erase(it);
+            cp = nullptr;
+        }
+    }
+    if (!cp) {
+        auto t0 = std::chrono::steady_clock::now();
+        auto fresh = std::make_unique<CompiledPlan>();
+        LowerOptions opt;
+        opt.no_fusion = (d->flags & ADB_FLAG_NO_FUSION) != 0;
+        opt.rank = d->rank;
+        opt.world = d->world;
+        opt.sm_count = d->sm_count;
+        lower_program(prog, fresh->plan, opt);
+        generate_kernels(fresh->plan);
+        fresh->kernel_slot.resize(fresh->plan.kernels.size());
+        for (size_t i = 0; i < fresh->plan.kernels.size(); i++) fresh->kernel_slot[i] = ensure_kernel(d, fresh->plan.kernels[i]);
+        fresh->plan.key = key;
+        fresh->lower_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+        d->stats.lower_ms = fresh->lower_ms;
+        cp = fresh.get();
+        d->plans[key] = std::move(fresh);
+    }
+    d->last = cp;
+    Plan& plan = cp->plan;
+    d->stats.plan_steps = uint64_t(plan.n_steps);
+    d->stats.arena_bytes = uint64_t(plan.arena_bytes);
+
+    // arena
+    if (size_t(plan.arena_bytes) > d->arena_cap) {
+        if (d->arena) ck(cudaFree(d->arena), "cudaFree(arena)");
+        d->arena = nullptr;
+        size_t want = size_t(plan.arena_bytes) + (size_t(1) << 20);
+        cudaError_t e = cudaMalloc(&d->arena, want);
+        if (e != cudaSuccess) {
+            d->arena_cap = 0;
+            cudaGetLastError();
+            d->err = "arena of " + std::to_string(want) + " bytes does not fit in device memory";
+            return ADB_ERR_OOM;
+        }
+        d->arena_cap = want;
+        d->arena_gen++;
+    }
+    // graphs hold raw addresses: rebuild them when the arena or a resident payload moved
+    uint64_t epoch = d->arena_gen;
+    for (auto& b : plan.bufs)
+        if (b.external) epoch = fnv_bytes(&plan.payloads[b.payload].addr, 8, epoch);
+    for (auto& p : plan.payloads)
+        if (p.kind == PAYLOAD_DEVICE) epoch = fnv_bytes(&p.addr, 8, epoch);
+    if (cp->graph_epoch != epoch) {
+        destroy_graphs(*cp);
+        cp->graph_epoch = epoch;
+    }
+
+    Executor ex(d, cp);
+    d->exit_requested = false;
+    d->upload_events.clear();
+    cudaEvent_t ev0 = ex.event(), ev1 = ex.event(), ev2 = ex.event();
+    ck(cudaEventRecord(ev0, d->stream), "event record");
+    ex.run_block(plan.main, false);
+    ck(cudaEventRecord(ev1, d->stream), "event record");
+
+    // read-back of dep-list ids (src/devices/opencl/device.rs:82-87)
+    for (auto& r : d->results) {
+        if (r.host) d->pinned_pool.push_back({r.host, r.host_cap});
+    }
+    d->results.clear();
+    for (auto& ri : plan.results) {
+        adb_device::HostResult hr;
+        hr.id = ri.id;
+        if (ri.buf >= 0) {
+            hr.valid = true;
+            for (auto x : ri.shape) hr.dims.push_back(uint64_t(x));
+            hr.n = size_t(numel(ri.shape));
+            hr.dev = ex.buf_ptr(ri.buf, ri.off);
+            hr.host = pinned_alloc(d, hr.n * 4, hr.host_cap);
+            if (hr.n) ck(cudaMemcpyAsync(hr.host, hr.dev, hr.n * 4, cudaMemcpyDeviceToHost, d->stream), "read-back");
+            d->stats.d2h_bytes += hr.n * 4;
+            hr.fetched = true;
+        }
+        d->results.push_back(std::move(hr));
+    }
+    ck(cudaEventRecord(ev2, d->stream), "event record");
+    ck(cudaStreamSynchronize(d->stream), "synchronize");
+    float ms_run = 0, ms_rb = 0;
+    cudaEventElapsedTime(&ms_run, ev0, ev1);
+    cudaEventElapsedTime(&ms_rb, ev1, ev2);
+    double up = 0;
+    for (auto& pr : d->upload_events) {
+        float m = 0;
+        cudaEventElapsedTime(&m, pr.first, pr.second);
+        up += m;
+    }
+    d->stats.upload_ms = up;
+    d->stats.device_ms = std::max(0.0, double(ms_run) - up);
+    d->stats.readback_ms = ms_rb;
+    d->stats.kernel_launches = ex.launches_;
+    d->stats.gemm_launches = ex.gemms_;
+    ex.release_events();
+    (void)t_begin;
+    return ADB_OK;
+}
+
+}  // namespace
+
+// ============================================================================================ C-ABI
+extern "C" {
+
+const char* adb_version(void) { return "adb200 0.1 (sm_100a)"; }
+
+adb_status adb_create(const adb_config* cfg, adb_device** out) {
+    if (!out) return ADB_ERR_INVALID;
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return ADB_ERR_NO_DEVICE;
+    }
+    auto d = std::make_unique<adb_device>();
+    if (cfg) {
+        d->ordinal = cfg->device_ordinal;
+        d->rank = cfg->rank;
+        d->world = cfg->world_size > 0 ? cfg->world_size : 1;
+        d->flags = cfg->flags;
+        d->shard_batch = cfg->shard_batch;
+    }
+    if (d->ordinal < 0 || d->ordinal >= count) return ADB_ERR_INVALID;
+    try {
+        ck(cudaSetDevice(d->ordinal), "cudaSetDevice");
+        cudaDeviceProp prop;
+        ck(cudaGetDeviceProperties(&prop, d->ordinal), "cudaGetDeviceProperties");
+        d->sm_count = prop.multiProcessorCount;
+        if (prop.major < 10) {
+            // the generated kernels and the tcgen05 GEMM are sm_100a only; no fallback path exists
+            return ADB_ERR_UNSUPPORTED;
+        }
+        ck(cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking), "cudaStreamCreate");
+        ck(cudaMallocHost(&d->cond_host, 64), "cudaMallocHost");
+        std::string gerr;
+        if (!gemm_init(d->gemm, d->sm_count, gerr)) throw CudaFail{gerr};
+        if (d->world > 1) {
+            if (!cfg->nccl_unique_id) return ADB_ERR_INVALID;
+            std::string nerr;
+            if (!g_nccl.load(nerr)) { return ADB_ERR_NCCL; }
+            ncclUniqueId uid;
+            static_assert(sizeof(uid) == 128, "ncclUniqueId is 128 bytes");
+            std::memcpy(&uid, cfg->nccl_unique_id, 128);
+            if (g_nccl.CommInitRank(&d->nccl_comm, d->world, uid, d->rank) != ncclSuccess) return ADB_ERR_NCCL;
+        }
+    } catch (CudaFail& f) {
+        std::fprintf(stderr, "adb_create: %s\n", f.msg.c_str());
+        return ADB_ERR_CUDA;
+    }
+    *out = d.release();
+    return ADB_OK;
+}
+
+void adb_destroy(adb_device* d) {
+    if (!d) return;
+    cudaSetDevice(d->ordinal);
+    if (d->stream) cudaStreamSynchronize(d->stream);
+    for (auto& kv : d->plans) destroy_graphs(*kv.second);
+    d->plans.clear();
+    for (auto& k : d->kernels)
+        if (k.lib) cudaLibraryUnload(k.lib);
+    for (auto& r : d->results)
+        if (r.host) cudaFreeHost(r.host);
+    for (auto& p : d->pinned_pool) cudaFreeHost(p.first);
+    for (auto e : d->ev_pool) cudaEventDestroy(e);
+    gemm_destroy(d->gemm);
+    if (d->nccl_comm && g_nccl.CommDestroy) g_nccl.CommDestroy(d->nccl_comm);
+    if (d->arena) cudaFree(d->arena);
+    if (d->cond_host) cudaFreeHost(d->cond_host);
+    if (d->stream) cudaStreamDestroy(d->stream);
+    delete d;
+}
+
+adb_status adb_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
+    if (!d || !blob) return ADB_ERR_INVALID;
+    d->err.clear();
+    try {
+        if (cudaSetDevice(d->ordinal) != cudaSuccess) { d->err = "cudaSetDevice failed"; return ADB_ERR_CUDA; }
+        return do_execute(d, blob, nbytes);
+    } catch (IrError& e) {
+        d->err = std::string("invalid program: ") + e.what();
+        return ADB_ERR_INVALID;
+    } catch (LowerError& e) {
+        d->err = std::string("cannot lower program: ") + e.what();
+        return ADB_ERR_INVALID;
+    } catch (CudaFail& f) {
+        d->err = f.msg;
+        // leave the stream usable for the next call
+        cudaStreamSynchronize(d->stream);
+        cudaGetLastError();
+        return ADB_ERR_CUDA;
+    } catch (std::exception& e) {
+        d->err = e.what();
+        return ADB_ERR_INVALID;
+    }
+}
+
+adb_status adb_get_tensor(adb_device* d, const char* id, const float** data, const uint64_t** dims, uint32_t* ndim) {
+    if (!d || !id) return ADB_ERR_INVALID;
+    for (auto& r : d->results)
+        if (r.id == id) {
+            if (!r.valid) return ADB_NONE;
+            if (data) *data = r.host;
+            if (dims) *dims = r.dims.data();
+            if (ndim) *ndim = uint32_t(r.dims.size());
+            return ADB_OK;
+        }
+    return ADB_NONE;
+}
+
+adb_status adb_get_tensor_device(adb_device* d, const char* id, const float** dptr, const uint64_t** dims, uint32_t* ndim) {
+    if (!d || !id) return ADB_ERR_INVALID;
+    for (auto& r : d->results)
+        if (r.id == id) {
+            if (!r.valid) return ADB_NONE;
+            if (dptr) *dptr = r.dev;
+            if (dims) *dims = r.dims.data();
+            if (ndim) *ndim = uint32_t(r.dims.size());
+            return ADB_OK;
+        }
+    return ADB_NONE;
+}
+
+void adb_dot_prod_shape(const uint64_t a[2], const uint64_t b[2], uint64_t out[2]) {
+    out[0] = a[0];
+    out[1] = b[1];
+}
+
+const char* adb_last_error(adb_device* d) { return d ? d->err.c_str() : "null device"; }
+
+adb_status adb_get_stats(adb_device* d, adb_stats* out) {
+    if (!d || !out) return ADB_ERR_INVALID;
+    *out = d->stats;
+    return ADB_OK;
+}
+
+size_t adb_dump_plan(adb_device* d, char* buf, size_t cap) {
+    if (!d || !d->last) return 0;
+    std::string s = dump_plan(d->last->plan, false);
+    if (buf && cap) {
+        size_t n = std::min(cap - 1, s.size());
+        std::memcpy(buf, s.data(), n);
+        buf[n] = 0;
+    }
+    return s.size() + 1;
+}
+
+static void set_err(char* err, size_t cap, const std::string& s) {
+    if (err && cap) {
+        size_t n = std::min(cap - 1, s.size());
+        std::memcpy(err, s.data(), n);
+        err[n] = 0;
+    }
+}
+
+adb_status adb_lower_check(const uint8_t* blob, size_t nbytes, const adb_config* cfg, int with_source, char* buf,
+                           size_t cap, size_t* needed, char* err, size_t err_cap) {
+    try {
+        Program prog = parse_program(blob, nbytes);
+        LowerOptions opt;
+        if (cfg) {
+            opt.no_fusion = (cfg->flags & ADB_FLAG_NO_FUSION) != 0;
+            opt.rank = cfg->rank;
+            opt.world = cfg->world_size > 0 ? cfg->world_size : 1;
+            if (opt.world > 1 && cfg->shard_batch) shard_program(prog, opt.rank, opt.world, int64_t(cfg->shard_batch));
+        }
+        Plan plan;
+        lower_program(prog, plan, opt);
+        generate_kernels(plan);
+        std::unordered_map<std::string, bool> done;
+        for (auto& k : plan.kernels) {
+            if (done.count(k.entry)) continue;
+            done[k.entry] = true;
+            std::vector<char> cubin;
+            std::string log;
+            if (!nvrtc_compile(k.source, k.entry, cubin, log)) {
+                set_err(err, err_cap, "JIT of " + k.entry + " failed: " + log + "\n" + k.source);
+                return ADB_ERR_CUDA;
+            }
+        }
+        std::string s = dump_plan(plan, with_source != 0);
+        if (needed) *needed = s.size() + 1;
+        if (buf && cap) {
+            size_t n = std::min(cap - 1, s.size());
+            std::memcpy(buf, s.data(), n);
+            buf[n] = 0;
+        }
+        return ADB_OK;
+    } catch (std::exception& e) {
+        set_err(err, err_cap, e.what());
+        return ADB_ERR_INVALID;
+    }
+}
+
+adb_status adb_shard_ir(const uint8_t* blob, size_t nbytes, int32_t rank, int32_t world_size, uint64_t shard_batch,
+                        uint8_t* out, size_t cap, size_t* needed, char* err, size_t err_cap) {
+    try {
+        Program prog = parse_program(blob, nbytes);
+        shard_program(prog, rank, world_size, int64_t(shard_batch));
+        std::vector<uint8_t> bytes = serialize_program(prog);
+        if (needed) *needed = bytes.size();
+        if (out && cap >= bytes.size()) std::memcpy(out, bytes.data(), bytes.size());
+        return ADB_OK;
+    } catch (std::exception& e) {
+        set_err(err, err_cap, e.what());
+        return ADB_ERR_INVALID;
+    }
+}
+
+adb_status adb_nccl_unique_id(void* out128) {
+    std::string e;
+    if (!out128) return ADB_ERR_INVALID;
+    if (!g_nccl.load(e)) return ADB_ERR_NCCL;
+    ncclUniqueId uid;
+    if (g_nccl.GetUniqueId(&uid) != ncclSuccess) return ADB_ERR_NCCL;
+    std::memcpy(out128, &uid, 128);
+    return ADB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,157 @@
+/*
+ * adb200 — C-ABI of the B200 execution backend for the autodiff-ir `Device` boundary.
+ *
+ * Every entry point is plain C (pointers and sizes only).  The library is what a
+ * `impl Device for B200` in the reference crate would bind through FFI; each function
+ * names the reference interface it replaces (paths are relative to the reference tree).
+ *
+ * Threading: one caller thread per handle; `adb_execute` is synchronous on return
+ * (the reference serialises all calls behind one global mutex, src/core/ir.rs:121).
+ * Errors: status codes, never abort, never a device trap (the reference panics,
+ * src/devices/opencl/context.rs:31,58,75,99).
+ */
+#ifndef ADB200_H
+#define ADB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct adb_device adb_device;
+
+typedef enum adb_status {
+    ADB_OK = 0,
+    ADB_NONE = 1,            /* get_tensor: id was not kept (ValueData::none(), src/core/value_data.rs:27-34) */
+    ADB_ERR_INVALID = 2,     /* malformed blob / IR that cannot be lowered */
+    ADB_ERR_CUDA = 3,        /* a CUDA / NVRTC call failed; see adb_last_error */
+    ADB_ERR_UNSUPPORTED = 4,
+    ADB_ERR_OOM = 5,
+    ADB_ERR_NCCL = 6,
+    ADB_ERR_NO_DEVICE = 7    /* no CUDA device: the backend has no CPU fallback */
+} adb_status;
+
+/* ---- wire format of the program handed to adb_execute -------------------------------
+ * Little-endian.  `id` operands are u32 indices into the id string table.
+ *
+ *   u32 magic = 0x52494441 ('ADIR'), u32 version = 1, u32 flags = 0, u32 n_ids
+ *   n_ids x { u16 len, len bytes }                       id strings (src/ir/base.rs:17-31)
+ *   u32 n_dep, n_dep x u32                                dep list  (src/core/dependency.rs:4-33)
+ *   procedure := u32 n_cmds, n_cmds x command            (struct IRProcedure, src/core/ir.rs:109-112)
+ *   command   := u8 opcode, operands:                    (enum IRCmds, src/core/ir.rs:8-105)
+ *      1 CreateMat      res, u8 nd, nd x u64 dim, u8 kind, u64 where, u64 n
+ *                       kind 0: `where` = byte offset of n f32 inside the blob
+ *                       kind 1: `where` = host address of n f32 (borrowed during the call)
+ *                       kind 2: `where` = device address of n f32 resident in HBM (borrowed)
+ *      2 CreateConstant res, f32 value, u8 nd, nd x u64 dim
+ *      3 ElwMultiply a b res      4 ElwAdd a b res
+ *      5 ElwMultiplyEq s o        6 ElwAddEq s o
+ *      7 EqualZero a res          8 MoreZero a res         9 LessZero a res
+ *     10 Sum a res               11 DotProduct a b res
+ *     12 View a res, u8 nd, nd x u64            13 Index a res, u64 index, u32 dim
+ *     14 Concat a b res, u32 dim                15 Permute a res, u8 n, n x u32
+ *     16 Broadcast a res, u32 dim, u64 r        17 Contigious a res
+ *     18 Exp2  19 Log2  20 Sin  21 Recip  22 Sqrt   (a res)
+ *     23 While cond, procedure
+ *     24 If u32 n, n x { cond, procedure }, u8 has_else, [procedure]
+ *     25 EX                      26 Heading u16 len, bytes
+ *     27 AllReduce id   (extension, no reference counterpart: in-place sum over all ranks)
+ */
+#define ADB_IR_MAGIC 0x52494441u
+#define ADB_IR_VERSION 1u
+
+typedef struct adb_config {
+    uint32_t struct_size;      /* sizeof(adb_config) */
+    int32_t device_ordinal;    /* CUDA device to run on */
+    int32_t rank;              /* data-parallel rank, 0 when world_size == 1 */
+    int32_t world_size;        /* number of data-parallel ranks (one process per GPU) */
+    const void *nccl_unique_id;/* 128 bytes from adb_nccl_unique_id on rank 0; NULL when world_size == 1 */
+    uint32_t flags;            /* ADB_FLAG_* */
+    uint64_t shard_batch;      /* world_size > 1: CreateMat tensors whose dim 0 equals this are split by rank */
+} adb_config;
+
+#define ADB_FLAG_NO_GRAPHS 1u      /* launch loop bodies kernel by kernel instead of replaying CUDA graphs */
+#define ADB_FLAG_NO_FUSION 2u      /* one kernel per IR command (debug aid, like the reference's unfused path) */
+#define ADB_FLAG_SIMT_DOT 4u       /* force the plain fp32 dot kernel instead of the tcgen05 3xTF32 kernel */
+
+/* Replaces OpenCL::new (src/devices/opencl/device.rs:41-58) + autodiff::set_device's device slot
+ * (src/core/autodiff.rs:82-97).  Fails with ADB_ERR_NO_DEVICE when no GPU is present. */
+adb_status adb_create(const adb_config *cfg, adb_device **out);
+void adb_destroy(adb_device *dev);
+
+/* Replaces `Device::execute` (src/core/ir.rs:128; OpenCL: src/devices/opencl/device.rs:62-88) together
+ * with the `to_kernel` lowering that feeds it (src/kernel/to_kernel.rs:34-107): lowers the procedure to
+ * fused kernels, runs it (If / While blocks included, src/devices/opencl/device.rs:107-146), and makes
+ * every dep-list id readable through adb_get_tensor.  The blob and the memory it points to are borrowed
+ * for the duration of the call. */
+adb_status adb_execute(adb_device *dev, const uint8_t *blob, size_t nbytes);
+
+/* Replaces `Device::get_tensor` (src/core/ir.rs:131; OpenCL: src/devices/opencl/device.rs:90-102).
+ * On ADB_OK, *data / *dims point to handle-owned host memory valid until the next adb_execute or
+ * adb_destroy.  ADB_NONE when the id is not in the dep list of the last program. */
+adb_status adb_get_tensor(adb_device *dev, const char *id, const float **data,
+                          const uint64_t **dims, uint32_t *ndim);
+
+/* Like adb_get_tensor but leaves the data in HBM: *dptr is the device address of the id's buffer
+ * (valid until the next adb_execute).  No reference counterpart (the reference always copies back). */
+adb_status adb_get_tensor_device(adb_device *dev, const char *id, const float **dptr,
+                                 const uint64_t **dims, uint32_t *ndim);
+
+/* Replaces the defaulted `Device::dot_prod_shape` (src/core/ir.rs:140-142): result is [a[0], b[1]]. */
+void adb_dot_prod_shape(const uint64_t a[2], const uint64_t b[2], uint64_t out[2]);
+
+/* `Device::ir_callback` (src/core/ir.rs:135) needs no entry point: this backend asks for no IR rewrite. */
+
+const char *adb_last_error(adb_device *dev);
+
+/* Counters of the last adb_execute (the reference only prints a wall-clock time,
+ * src/devices/opencl/device.rs:78-80). */
+typedef struct adb_stats {
+    double device_ms;          /* CUDA-event time of the compute region (first kernel .. last kernel) */
+    double upload_ms;          /* host->device copies of CreateMat payloads before / between kernels */
+    double readback_ms;        /* device->host copies of dep-list tensors */
+    double lower_ms;           /* host time spent lowering + JIT-compiling (0 when the plan was cached) */
+    uint64_t h2d_bytes;
+    uint64_t d2h_bytes;
+    uint64_t kernel_launches;  /* kernels of this library launched (graph replays count their kernel nodes) */
+    uint64_t graph_replays;
+    uint64_t gemm_launches;
+    uint64_t jit_compiles;
+    uint64_t arena_bytes;
+    uint64_t while_iterations;
+    uint64_t ir_commands;
+    uint64_t plan_steps;
+} adb_stats;
+adb_status adb_get_stats(adb_device *dev, adb_stats *out);
+
+/* Text listing of the lowered program of the last adb_execute (kernels, their fused expressions,
+ * buffers): the counterpart of the reference's side-by-side kernel/IR print
+ * (src/core/ir.rs:190-192, src/kernel/helper/debug.rs:149-217).  Returns the number of bytes needed. */
+size_t adb_dump_plan(adb_device *dev, char *buf, size_t cap);
+
+/* Host-only entry points (work without a GPU; used by the CPU test-suite). */
+
+/* Lowers a blob and JIT-compiles every generated kernel for sm_100a without running anything.
+ * Writes the plan listing (and, with `with_source`, the generated CUDA) into buf. */
+adb_status adb_lower_check(const uint8_t *blob, size_t nbytes, const adb_config *cfg, int with_source,
+                           char *buf, size_t cap, size_t *needed, char *err, size_t err_cap);
+
+/* Data-parallel rewrite used when world_size > 1 (no reference counterpart; the reference is
+ * single-device): splits dim 0 of CreateMat tensors whose dim 0 == shard_batch across ranks and
+ * inserts AllReduce commands where batch-partial values meet replicated ones.  Writes the new
+ * blob into out (cap bytes); *needed receives its size. */
+adb_status adb_shard_ir(const uint8_t *blob, size_t nbytes, int32_t rank, int32_t world_size,
+                        uint64_t shard_batch, uint8_t *out, size_t cap, size_t *needed,
+                        char *err, size_t err_cap);
+
+/* 128-byte NCCL unique id for adb_config.nccl_unique_id (rank 0 creates, the caller broadcasts it). */
+adb_status adb_nccl_unique_id(void *out128);
+
+const char *adb_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ADB200_H */

@@ -1,0 +1,244 @@
+"""Structure coverage: broadcasts, permutes, views, index/concat, reductions of every launch shape,
+dot products with folded transposes, control flow -- B200 against the CPU oracle."""
+import numpy as np
+import pytest
+
+from helpers import ad, nn, run_both, assert_exact, assert_rel, assert_ulp, b200
+
+pytestmark = pytest.mark.gpu
+RNG = np.random.default_rng(11)
+
+
+def rnd(*shape):
+    return RNG.standard_normal(int(np.prod(shape))).astype(np.float32)
+
+
+def _run(build, exact=(), rel=(), tol=1e-4):
+    """build() -> {name: Tensor}; everything is forwarded, kept, executed and compared."""
+    def prog(dev):
+        ad.set_device(dev)
+        ad.eager_dep_opt()
+        outs = build()
+        vals = {}
+        for k, t in outs.items():
+            vals[k] = t.forward() if hasattr(t, "forward") else t
+            vals[k].keep()
+        ad.execute()
+        return {k: v.get() for k, v in vals.items()}
+    want, got = run_both(prog)
+    for k in want:
+        if k in rel:
+            assert_rel(k, got[k], want[k], tol)
+        else:
+            assert_exact(k, got[k], want[k])
+    return want, got
+
+
+@pytest.mark.parametrize("shape", [(7,), (4, 5), (3, 8, 16), (2, 3, 4, 5), (1, 1), (33, 1, 7)])
+def test_broadcast_forms(shape):
+    a = rnd(*shape)
+    inner = shape[-1]
+    row = rnd(inner)
+
+    def build():
+        ta = ad.tensor(a, list(shape))
+        tr = ad.tensor(row, [inner])
+        return {"y": ta * tr + 2.0, "z": tr + ta}
+    _run(build)
+
+
+@pytest.mark.parametrize("shape,perm", [((4, 6), [1, 0]), ((3, 4, 5), [0, 2, 1]), ((3, 4, 5), [2, 0, 1]),
+                                         ((2, 3, 4, 5), [3, 1, 0, 2]), ((64, 96), [1, 0]), ((8, 128, 64), [0, 2, 1])])
+def test_permute_contiguous(shape, perm):
+    a = rnd(*shape)
+
+    def build():
+        t = ad.tensor(a, list(shape))
+        p = t.permute(perm)
+        return {"p": p.contigious(), "q": (p * 3.0 + 1.0)}
+    want, got = _run(build)
+    np.testing.assert_array_equal(np.asarray(got["p"].data).reshape(got["p"].dim), a.reshape(shape).transpose(perm))
+
+
+def test_view_of_permuted_needs_copy():
+    a = rnd(6, 10)
+
+    def build():
+        t = ad.tensor(a, [6, 10])
+        v = t.t().view([4, 15])          # not expressible as strides of `a`: forces a copy
+        w = t.view([3, 2, 10]).permute([1, 0, 2]).view([2, 30])
+        return {"v": v * 1.5, "w": w.contigious()}
+    want, got = _run(build)
+    np.testing.assert_array_equal(np.asarray(got["w"].data).reshape(2, 30), a.reshape(3, 2, 10).transpose(1, 0, 2).reshape(2, 30))
+
+
+def test_index_and_concat():
+    a, b = rnd(5, 8), rnd(3, 8)
+
+    def build():
+        ta, tb = ad.tensor(a, [5, 8]), ad.tensor(b, [3, 8])
+        c = ad.concat([ta, tb, ta * 2.0], 0)          # [13, 8]
+        d = ad.concat([ta.i(2, 0).unsqueeze(0), tb], 0)  # [4, 8]
+        e = ad.concat([ta, ta.exp2()], 1)             # [5, 16]
+        return {"c": c.contigious(), "rows": c.r(range(3, 11), 0).contigious(), "col": c.i(5, 1).contigious(),
+                "d": d * d, "e": e.contigious(), "e_t": e.t().contigious()}
+    want, got = _run(build, rel=("e", "e_t"), tol=1e-6)
+    full = np.concatenate([a.reshape(5, 8), b.reshape(3, 8), 2 * a.reshape(5, 8)], 0)
+    np.testing.assert_array_equal(np.asarray(got["rows"].data).reshape(8, 8), full[3:11])
+    np.testing.assert_array_equal(np.asarray(got["col"].data), full[:, 5])
+
+
+@pytest.mark.parametrize("V,R", [(1, 5), (3, 7), (64, 16), (5, 1000), (300, 33), (2, 40000), (1, 100000), (257, 4096)])
+def test_row_sums(V, R):
+    a = rnd(V, R)
+
+    def build():
+        t = ad.tensor(a, [V, R])
+        return {"s": t.sum(1), "m": (t * t + 1.0).sum(1)}
+    _run(build, rel=("s", "m"))
+
+
+@pytest.mark.parametrize("R,V", [(5, 1), (7, 3), (16, 64), (1000, 8), (33, 300), (40000, 4), (4096, 260), (9000, 1024)])
+def test_column_sums(R, V):
+    a = rnd(R, V)
+
+    def build():
+        t = ad.tensor(a, [R, V])
+        return {"s": t.sum(0), "m": (t.sin() * 0.5).sum(0)}
+    _run(build, rel=("s", "m"))
+
+
+def test_sum_middle_axis_and_all():
+    a = rnd(6, 10, 12)
+
+    def build():
+        t = ad.tensor(a, [6, 10, 12])
+        ones = ad.tensor(np.ones(24, np.float32), [4, 6])
+        almost = np.ones(24, np.float32)
+        almost[13] = 0
+        return {"mid": t.sum(1), "mean": t.mean(-1), "var": t.var(0, 1), "all1": ones.all(),
+                "all0": ad.tensor(almost, [4, 6]).all()}
+    want, got = _run(build, rel=("mid", "mean", "var"))
+    assert got["all1"].data[0] == 1.0 and got["all0"].data[0] == 0.0
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 1, 1), (2, 5, 3), (17, 33, 9), (64, 64, 64), (128, 256, 192), (100, 1000, 7), (300, 70, 130)])
+def test_dot_shapes(M, K, N):
+    a, b = rnd(M, K), rnd(K, N)
+    at, bt = rnd(K, M), rnd(N, K)
+
+    def build():
+        ta, tb = ad.tensor(a, [M, K]), ad.tensor(b, [K, N])
+        tat, tbt = ad.tensor(at, [K, M]), ad.tensor(bt, [N, K])
+        return {"nn": ad.dot(ta, tb), "tn": ad.dot(tat.t(), tb), "nt": ad.dot(ta, tbt.t()), "tt": ad.dot(tat.t(), tbt.t()),
+                "fused": ad.dot(ta * 2.0, tb + 1.0)}
+    want, got = _run(build, rel=("nn", "tn", "nt", "tt", "fused"))
+    ref = a.reshape(M, K).astype(np.float64) @ b.reshape(K, N).astype(np.float64)
+    err = np.abs(np.asarray(got["nn"].data).reshape(M, N) - ref).max() / max(np.abs(ref).max(), 1e-30)
+    assert err < 1e-4
+
+
+def test_dot_backward_and_linear_layer():
+    x, w, bias = rnd(9, 6), rnd(6, 4), rnd(4)
+
+    def prog(dev):
+        ad.set_device(dev)
+        tx, tw, tb = ad.tensor(x, [9, 6]), ad.tensor(w, [6, 4]), ad.tensor(bias, [4])
+        y = nn.LinearWithWeights(tw, tb).f(tx).sigmoid()
+        y.forward()
+        y.backward()
+        y.val().keep()
+        ad.execute()
+        return {"y": y.val().get(), "dx": tx.grad().get(), "dw": tw.grad().get(), "db": tb.grad().get()}
+    want, got = run_both(prog)
+    for k in want:
+        assert_rel(k, got[k], want[k], 1e-4)
+
+
+def test_in_place_through_alias_reads_and_loop_carried_state():
+    a = rnd(4, 6)
+
+    def prog(dev):
+        ad.set_device(dev)
+        t = ad.tensor(a, [4, 6])
+        tt = t.t()                      # alias defined before the updates below
+        acc = ad.tensor(np.zeros(24, np.float32), [6, 4])
+
+        def body(i):
+            nonlocal t, acc
+            acc += tt * 1.0             # must see the current contents of t every iteration
+            acc.forward()
+            t *= 2.0
+            t.forward()
+        ad.ir_for(range(0, 3), body)
+        ad.execute()
+        return {"t": t.val().get(), "acc": acc.val().get()}
+    want, got = run_both(prog)
+    assert_exact("t", got["t"], want["t"])
+    assert_exact("acc", got["acc"], want["acc"])
+    np.testing.assert_array_equal(np.asarray(got["acc"].data).reshape(6, 4), a.reshape(4, 6).T * 7.0)
+
+
+def test_nested_control_flow_counts():
+    def prog(dev):
+        ad.set_device(dev)
+        total = ad.scalar(0.0)
+        evens = ad.scalar(0.0)
+
+        def outer(i):
+            nonlocal total
+
+            def inner(j):
+                nonlocal total
+                total += 1.0
+                total.forward()
+            ad.ir_for(range(0, 4), inner)
+
+            def even():
+                nonlocal evens
+                evens += 1.0
+                evens.forward()
+            half = i.clone() * 0.5
+            ad.ir_if(lambda: (half.sin() * 0.0 + half).equal(ad.constant(1.0, [1])), even)   # only i == 2
+        ad.ir_for(range(0, 5), outer)
+        ad.execute()
+        return {"total": total.val().get(), "evens": evens.val().get()}
+    want, got = run_both(prog)
+    assert_exact("total", got["total"], want["total"])
+    assert_exact("evens", got["evens"], want["evens"])
+    assert got["total"].data[0] == 20.0 and got["evens"].data[0] == 1.0
+
+
+def test_plan_is_cached_and_payloads_rebound():
+    dev = b200()
+
+    def run(scale):
+        ad.set_device(dev)
+        ad.eager_dep_opt()
+        x = ad.tensor(np.arange(8, dtype=np.float32) * scale, [8])
+        y = (x * 3.0 + 1.0).exp2().sum(0)
+        y.forward()
+        y.val().keep()
+        ad.execute()
+        return float(y.val().get().data[0]), dev.stats()
+    v1, s1 = run(0.25)
+    v2, s2 = run(0.5)
+    assert s2["jit_compiles"] == 0 and s2["lower_ms"] == 0.0      # same structure: plan and kernels reused
+    assert abs(v1 - float(np.exp2(np.arange(8) * 0.75 + 1).sum())) < 1e-2
+    assert abs(v2 - float(np.exp2(np.arange(8) * 1.5 + 1).sum())) / v2 < 1e-5
+
+
+def test_malformed_blob_is_rejected_without_killing_the_context():
+    dev = b200()
+    with pytest.raises(Exception):
+        dev.execute_blob(b"ADIRgarbage")
+    ad.set_device(dev)
+    x = ad.tensor([1.0, 2.0], [2])
+    bad = ad.dot(x.view([1, 2]), x.view([1, 2]))   # inner dimensions disagree
+    with pytest.raises(AssertionError):
+        bad.forward()
+    y = x + 1.0
+    y.forward()
+    y.val().keep()
+    ad.execute()
+    np.testing.assert_array_equal(y.val().get().data, [2.0, 3.0])
