@@ -245,7 +245,7 @@ void gen_reduce(KernelSpec& k) {
     k.wide_index = needs_wide(std::max(k.n, k.r) * std::max<int64_t>(1, k.split), ops) || k.n * k.r >= (int64_t(1) << 31);
     const char* idx_t = k.wide_index ? "long long" : "unsigned int";
     const int64_t R = k.r, S = k.split;
-    const int64_t chunk = (R + S - 1) / S;  // summed elements per partial
+    const int64_t chunk = k.chunk > 0 ? k.chunk : (R + S - 1) / S;  // summed elements per partial
     std::ostringstream o;
     o << "struct Args { const float* in[" << std::max<size_t>(1, k.ins.size()) << "]; float* out[1]; long long n; };\n";
 
@@ -446,6 +446,8 @@ void plan_reduce(KernelSpec& k, int sm_count) {
             chunk = (chunk + 255) / 256 * 256;
             k.split = (R + chunk - 1) / chunk;
         }
+        k.chunk = (R + k.split - 1) / k.split;
+        if (k.split > 1) k.chunk = (k.chunk + 255) / 256 * 256;
     } else {
         int vec = V % 4 == 0 ? 4 : 1;
         for (auto& in : k.ins)
@@ -459,6 +461,8 @@ void plan_reduce(KernelSpec& k, int sm_count) {
             int64_t want = (2 * sm_count + bx - 1) / bx;
             k.split = std::max<int64_t>(1, std::min(want, R / 256));
         }
+        k.chunk = (R + k.split - 1) / k.split;
+        k.split = (R + k.chunk - 1) / k.chunk;
     }
 }
 

@@ -534,6 +534,7 @@ class Graph {
         std::vector<Sub> all;
         for (auto& d : v.dims)
             for (auto& s : d) all.push_back(s);
+        canon_subs(all);  // digits that are contiguous across an axis boundary may be cut anywhere
         out.offset = v.offset;
         out.dims.assign(shape.size(), {});
         size_t pos = 0;

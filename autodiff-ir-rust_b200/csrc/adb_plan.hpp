@@ -62,6 +62,7 @@ struct KernelSpec {
     int mode = 0;           // REDUCE: 0 = lanes along y (row), 1 = lanes along x (column)
     int threads = 256;
     int64_t split = 1;      // REDUCE: number of partial sums per row (two-pass when > 1)
+    int64_t chunk = 0;      // REDUCE: summed elements per partial (a multiple of the vector width)
     int jit = -1;           // index into the module cache
     int jit2 = -1;          // REDUCE: second-pass kernel
     int scratch = -1;       // REDUCE two-pass: buffer holding the partial sums

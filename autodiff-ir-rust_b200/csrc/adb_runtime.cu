@@ -142,6 +142,8 @@ struct adb_device {
     ncclComm_t nccl_comm = nullptr;
     GemmContext gemm;
     bool exit_requested = false;
+    struct ProfRec { int kind; int kernel; cudaEvent_t e0, e1; double work; };  // kind: Step::Kind
+    std::vector<ProfRec> prof;
     std::vector<cudaEvent_t> ev_pool;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> upload_events;
 };
@@ -249,7 +251,39 @@ class Executor {
         launches_++;
     }
 
+    static double operand_bytes(const Operand& o) {
+        double n = 1;
+        for (auto& s : o.subs) if (s.stride) n *= double(s.size);
+        for (auto& s : o.xsubs) if (s.stride) n *= double(s.size);
+        return 4.0 * n;
+    }
+    // bytes a kernel has to move: every distinct operand once
+    static double kernel_bytes(const KernelSpec& k) {
+        double b = 0;
+        for (auto& in : k.ins) b += operand_bytes(in);
+        for (auto& o : k.outs) b += k.type == KernelSpec::REDUCE ? 4.0 * double(k.n) * double(k.split) : operand_bytes(o.dst);
+        return b;
+    }
+
     void run_step(const Step& s) {
+        const bool prof = (d_->flags & ADB_FLAG_PROFILE) && !capturing_ &&
+                          (s.kind == Step::ELW || s.kind == Step::REDUCE || s.kind == Step::GEMM || s.kind == Step::ALLREDUCE);
+        if (!prof) { run_step_impl(s); return; }
+        adb_device::ProfRec r;
+        r.kind = int(s.kind);
+        r.kernel = s.kernel;
+        r.e0 = event();
+        r.e1 = event();
+        r.work = s.kind == Step::GEMM ? 2.0 * double(s.gemm.M) * double(s.gemm.N) * double(s.gemm.K)
+               : s.kind == Step::ALLREDUCE ? 4.0 * double(s.nelem)
+               : kernel_bytes(plan_.kernels[s.kernel]);
+        ck(cudaEventRecord(r.e0, d_->stream), "event");
+        run_step_impl(s);
+        ck(cudaEventRecord(r.e1, d_->stream), "event");
+        d_->prof.push_back(r);
+    }
+
+    void run_step_impl(const Step& s) {
         switch (s.kind) {
         case Step::ELW: case Step::REDUCE:
             launch_kernel(plan_.kernels[s.kernel], cp_->kernel_slot[s.kernel]);
@@ -321,20 +355,23 @@ class Executor {
         while (i < blk.steps.size()) {
             size_t j = i;
             while (j < blk.steps.size() && capturable(blk.steps[j], plan_)) j++;
-            if (j - i >= 2 && !(d_->flags & ADB_FLAG_NO_GRAPHS)) {
+            if (j - i >= 2 && !(d_->flags & (ADB_FLAG_NO_GRAPHS | ADB_FLAG_PROFILE))) {
                 GraphSeg g;
                 g.begin = i;
                 g.end = j;
                 uint64_t l0 = launches_, g0 = gemms_;
                 cudaGraph_t graph = nullptr;
                 ck(cudaStreamBeginCapture(d_->stream, cudaStreamCaptureModeThreadLocal), "begin capture");
+                capturing_ = true;
                 try {
                     for (size_t t = i; t < j; t++) run_step(blk.steps[t]);
                 } catch (...) {
+                    capturing_ = false;
                     cudaStreamEndCapture(d_->stream, &graph);
                     if (graph) cudaGraphDestroy(graph);
                     throw;
                 }
+                capturing_ = false;
                 ck(cudaStreamEndCapture(d_->stream, &graph), "end capture");
                 g.launches = launches_ - l0;
                 g.gemms = gemms_ - g0;
@@ -423,6 +460,7 @@ class Executor {
     }
 
     uint64_t launches_ = 0, gemms_ = 0;
+    bool capturing_ = false;
 
   private:
     adb_device* d_;
@@ -560,6 +598,7 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
     Executor ex(d, cp);
     d->exit_requested = false;
     d->upload_events.clear();
+    d->prof.clear();
     cudaEvent_t ev0 = ex.event(), ev1 = ex.event(), ev2 = ex.event();
     ck(cudaEventRecord(ev0, d->stream), "event record");
     ex.run_block(plan.main, false);
@@ -601,6 +640,34 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
     d->stats.readback_ms = ms_rb;
     d->stats.kernel_launches = ex.launches_;
     d->stats.gemm_launches = ex.gemms_;
+    if (!d->prof.empty()) {
+        std::map<int, std::pair<double, std::pair<double, uint64_t>>> per_kernel;  // kernel -> (ms, (bytes, launches))
+        for (auto& r : d->prof) {
+            float m = 0;
+            cudaEventElapsedTime(&m, r.e0, r.e1);
+            switch (r.kind) {
+            case Step::ELW: d->stats.elw_ms += m; d->stats.elw_bytes += r.work; d->stats.elw_launches++; break;
+            case Step::REDUCE: d->stats.reduce_ms += m; d->stats.reduce_bytes += r.work; d->stats.reduce_launches++; break;
+            case Step::GEMM: d->stats.gemm_ms += m; d->stats.gemm_flops += r.work; break;
+            case Step::ALLREDUCE: d->stats.collective_ms += m; d->stats.collective_bytes += r.work; d->stats.collective_launches++; break;
+            default: break;
+            }
+            if (r.kind == Step::ELW || r.kind == Step::REDUCE) {
+                auto& pk = per_kernel[r.kernel];
+                pk.first += m;
+                pk.second.first += r.work;
+                pk.second.second++;
+            }
+        }
+        for (auto& kv : per_kernel)
+            if (kv.second.first > d->stats.top_ms) {
+                d->stats.top_ms = kv.second.first;
+                d->stats.top_bytes = kv.second.second.first;
+                d->stats.top_launches = kv.second.second.second;
+                std::snprintf(d->stats.top_name, sizeof d->stats.top_name, "%s", plan.kernels[size_t(kv.first)].entry.c_str());
+            }
+        d->prof.clear();
+    }
     ex.release_events();
     (void)t_begin;
     return ADB_OK;

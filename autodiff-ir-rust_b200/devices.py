@@ -25,7 +25,7 @@ ADB_OK, ADB_NONE = 0, 1
 STATUS = {0: "ADB_OK", 1: "ADB_NONE", 2: "ADB_ERR_INVALID", 3: "ADB_ERR_CUDA", 4: "ADB_ERR_UNSUPPORTED",
           5: "ADB_ERR_OOM", 6: "ADB_ERR_NCCL", 7: "ADB_ERR_NO_DEVICE"}
 
-FLAG_NO_GRAPHS, FLAG_NO_FUSION, FLAG_SIMT_DOT = 1, 2, 4
+FLAG_NO_GRAPHS, FLAG_NO_FUSION, FLAG_SIMT_DOT, FLAG_PROFILE = 1, 2, 4, 8
 
 EXPORTS = ["adb_create", "adb_destroy", "adb_execute", "adb_get_tensor", "adb_get_tensor_device",
            "adb_dot_prod_shape", "adb_last_error", "adb_get_stats", "adb_dump_plan", "adb_lower_check",
@@ -43,10 +43,17 @@ class AdbStats(ctypes.Structure):
                 ("lower_ms", ctypes.c_double), ("h2d_bytes", ctypes.c_uint64), ("d2h_bytes", ctypes.c_uint64),
                 ("kernel_launches", ctypes.c_uint64), ("graph_replays", ctypes.c_uint64),
                 ("gemm_launches", ctypes.c_uint64), ("jit_compiles", ctypes.c_uint64), ("arena_bytes", ctypes.c_uint64),
-                ("while_iterations", ctypes.c_uint64), ("ir_commands", ctypes.c_uint64), ("plan_steps", ctypes.c_uint64)]
+                ("while_iterations", ctypes.c_uint64), ("ir_commands", ctypes.c_uint64), ("plan_steps", ctypes.c_uint64),
+                ("elw_ms", ctypes.c_double), ("reduce_ms", ctypes.c_double), ("gemm_ms", ctypes.c_double),
+                ("collective_ms", ctypes.c_double), ("elw_launches", ctypes.c_uint64), ("reduce_launches", ctypes.c_uint64),
+                ("collective_launches", ctypes.c_uint64), ("elw_bytes", ctypes.c_double), ("reduce_bytes", ctypes.c_double),
+                ("gemm_flops", ctypes.c_double), ("collective_bytes", ctypes.c_double), ("top_ms", ctypes.c_double),
+                ("top_bytes", ctypes.c_double), ("top_launches", ctypes.c_uint64), ("top_name", ctypes.c_char * 64)]
 
     def as_dict(self):
-        return {k: getattr(self, k) for k, _ in self._fields_}
+        d = {k: getattr(self, k) for k, _ in self._fields_}
+        d["top_name"] = d["top_name"].decode(errors="replace")
+        return d
 
 
 class AdbError(RuntimeError):

@@ -75,6 +75,8 @@ typedef struct adb_config {
 #define ADB_FLAG_NO_GRAPHS 1u      /* launch loop bodies kernel by kernel instead of replaying CUDA graphs */
 #define ADB_FLAG_NO_FUSION 2u      /* one kernel per IR command (debug aid, like the reference's unfused path) */
 #define ADB_FLAG_SIMT_DOT 4u       /* force the plain fp32 dot kernel instead of the tcgen05 3xTF32 kernel */
+#define ADB_FLAG_PROFILE 8u        /* CUDA events around every kernel (fills the per-kind times of adb_stats);
+                                      loop bodies are then launched kernel by kernel, not as graphs */
 
 /* Replaces OpenCL::new (src/devices/opencl/device.rs:41-58) + autodiff::set_device's device slot
  * (src/core/autodiff.rs:82-97).  Fails with ADB_ERR_NO_DEVICE when no GPU is present. */
@@ -123,6 +125,15 @@ typedef struct adb_stats {
     uint64_t while_iterations;
     uint64_t ir_commands;
     uint64_t plan_steps;
+    /* filled when ADB_FLAG_PROFILE is set: device time, launches and algorithmic work per kernel kind.
+     * Bytes are the bytes a kernel must move (each operand once, 4 B per element); flops are 2*M*N*K. */
+    double elw_ms, reduce_ms, gemm_ms, collective_ms;
+    uint64_t elw_launches, reduce_launches, collective_launches;
+    double elw_bytes, reduce_bytes, gemm_flops, collective_bytes;
+    /* the single generated kernel with the largest total time */
+    double top_ms, top_bytes;
+    uint64_t top_launches;
+    char top_name[64];
 } adb_stats;
 adb_status adb_get_stats(adb_device *dev, adb_stats *out);
 

@@ -176,7 +176,10 @@ def test_in_place_through_alias_reads_and_loop_carried_state():
     want, got = run_both(prog)
     assert_exact("t", got["t"], want["t"])
     assert_exact("acc", got["acc"], want["acc"])
-    np.testing.assert_array_equal(np.asarray(got["acc"].data).reshape(6, 4), a.reshape(4, 6).T * 7.0)
+    at = a.reshape(4, 6).T
+    ref = (np.float32(0) + at) + at * np.float32(2)
+    ref = ref + at * np.float32(4)
+    np.testing.assert_array_equal(np.asarray(got["acc"].data).reshape(6, 4), ref)
 
 
 def test_nested_control_flow_counts():
