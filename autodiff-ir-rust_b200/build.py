@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libadb200.so")
 CUDA = os.environ.get("CUDA_HOME", "/usr/local/cuda")
-SOURCES = ["adb_runtime.cu", "adb_gemm.cu", "adb_lower.cpp", "adb_codegen.cpp", "adb_shard.cpp"]
+SOURCES = ["adb_runtime.cu", "adb_gemm.cu", "adb_noalloc.cu", "adb_lower.cpp", "adb_codegen.cpp", "adb_shard.cpp"]
 
 
 def needs_build() -> bool:

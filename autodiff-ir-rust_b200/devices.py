@@ -29,7 +29,9 @@ FLAG_NO_GRAPHS, FLAG_NO_FUSION, FLAG_SIMT_DOT, FLAG_PROFILE = 1, 2, 4, 8
 
 EXPORTS = ["adb_create", "adb_destroy", "adb_execute", "adb_get_tensor", "adb_get_tensor_device",
            "adb_dot_prod_shape", "adb_last_error", "adb_get_stats", "adb_dump_plan", "adb_lower_check",
-           "adb_shard_ir", "adb_nccl_unique_id", "adb_version"]
+           "adb_shard_ir", "adb_nccl_unique_id", "adb_version", "adb_row_sum_noalloc"]
+
+NOALLOC_MAX_PARTIALS = 1 << 20
 
 
 class AdbConfig(ctypes.Structure):
@@ -103,6 +105,9 @@ def load_library():
     L.adb_nccl_unique_id.argtypes = [ctypes.c_void_p]
     L.adb_nccl_unique_id.restype = ctypes.c_int
     L.adb_version.restype = ctypes.c_char_p
+    L.adb_row_sum_noalloc.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_void_p,
+                                      ctypes.c_char_p, ctypes.c_size_t]
+    L.adb_row_sum_noalloc.restype = ctypes.c_int
     _lib = L
     return L
 
@@ -235,6 +240,18 @@ class B200:
         buf = ctypes.create_string_buffer(int(n) + 16)
         self._L.adb_dump_plan(self._h, buf, len(buf))
         return buf.value.decode(errors="replace")
+
+
+def row_sum_noalloc(d_in: int, d_out: int, rows: int, length: int, stream: int = 0) -> None:
+    """out[r] = sum(in[r, :]) on device pointers, through the entry point that allocates nothing.
+
+    For callers that cannot allocate device memory where they call from: the scratch of the two-pass
+    sum is a fixed array inside the library (see include/adb200.h for the limit and the sharing rules).
+    Raises AdbError when `rows` exceeds NOALLOC_MAX_PARTIALS."""
+    err = ctypes.create_string_buffer(256)
+    rc = load_library().adb_row_sum_noalloc(d_in, d_out, rows, length, stream, err, len(err))
+    if rc != ADB_OK:
+        raise AdbError(rc, err.value.decode(errors="replace"))
 
 
 def nccl_unique_id() -> bytes:

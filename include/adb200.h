@@ -160,6 +160,23 @@ adb_status adb_shard_ir(const uint8_t *blob, size_t nbytes, int32_t rank, int32_
 /* 128-byte NCCL unique id for adb_config.nccl_unique_id (rank 0 creates, the caller broadcasts it). */
 adb_status adb_nccl_unique_id(void *out128);
 
+/* No counterpart in the reference.  Row sums (out[r] = sum of in[r*len .. r*len+len)) of a row-major
+ * f32 matrix resident in HBM, for callers that cannot allocate device memory at the point of the call
+ * (host callbacks, code running while a capture is open, processes whose memory belongs to another
+ * pool): the scratch of the two-pass sum lives in a fixed device array inside the library, so the call
+ * performs no cudaMalloc / cudaFree and uses no allocating routine.
+ *   - limit: rows <= ADB_NOALLOC_MAX_PARTIALS (the array holds that many floats, 4 MiB, on every GPU
+ *     that loads the library, until exit); larger inputs return ADB_ERR_INVALID with a message in err.
+ *   - the first call on a device resolves the array's address and should happen before any stream
+ *     capture starts.
+ *   - all calls share the array: calls that overlap on the GPU race; calls ordered on one stream are safe
+ *     and need no clearing in between (each call only reads partial sums it wrote itself).
+ * d_in / d_out are device pointers, `stream` a cudaStream_t (NULL = default stream); the call is
+ * asynchronous with respect to the host. */
+#define ADB_NOALLOC_MAX_PARTIALS (1u << 20)
+adb_status adb_row_sum_noalloc(const float *d_in, float *d_out, uint64_t rows, uint64_t len, void *stream,
+                               char *err, size_t err_cap);
+
 const char *adb_version(void);
 
 #ifdef __cplusplus
