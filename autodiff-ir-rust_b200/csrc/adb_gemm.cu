@@ -1,11 +1,29 @@
-// fp32 dot product kernels.
+// fp32 dot product C[M,N] = A[M,K] . B[K,N] for sm_100a.
+//
+// Two kernels:
+//   adb_dot_tc    TMA-fed tcgen05.mma (kind::tf32) with the 3xTF32 split: every fp32 operand is cut
+//                 into hi = tf32(a) and lo = tf32(a - hi), and hi.hi + hi.lo + lo.hi is accumulated in
+//                 fp32 in tensor memory, which recovers fp32-level accuracy from tf32 multipliers.
+//   adb_dot_simt  plain CUDA-core tiles for small or unaligned problems.
+// The reference computes one output per work-item with a scalar k loop
+// (src/devices/opencl/kernels/dotprod.rs:4-75); transposed operands arrive as index expressions there
+// and as (row stride, column stride) pairs here, which map onto K-major / MN-major shared-memory
+// descriptors, so `A^T` and `B^T` need no copy.
 #include "adb_gemm.hpp"
+
+#include <cuda.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
 
 namespace adb {
 
-// Plain CUDA-core path: 64x64 tile per block, 4x4 outputs per thread, fp32 FMA with k ascending in
-// every output element (the order of the reference kernel, src/devices/opencl/kernels/dotprod.rs:31-41).
-// Handles any strides and sizes; used for small or unaligned problems.
+// ====================================================================================================
+// CUDA-core path
+// ====================================================================================================
+// 64x64 tile per block, 4x4 outputs per thread, fp32 FMA with k ascending in every output element
+// (the order of the reference kernel, dotprod.rs:31-41).  Handles any strides and sizes.
 template <int BM, int BN, int BK>
 __global__ void __launch_bounds__(256) adb_dot_simt(const float* __restrict__ A, const float* __restrict__ B,
                                                     float* __restrict__ C, long long M, long long N, long long K,
@@ -20,7 +38,7 @@ __global__ void __launch_bounds__(256) adb_dot_simt(const float* __restrict__ A,
     for (int i = 0; i < 4; i++)
 #pragma unroll
         for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
-    // loader mapping: pick the thread->element assignment that walks the unit-stride axis of each operand
+    // loader mapping: walk the unit-stride axis of each operand with consecutive threads
     const bool a_k_fast = a_cs == 1;
     const bool b_n_fast = b_cs == 1;
     for (long long k0 = 0; k0 < K; k0 += BK) {
@@ -63,23 +81,470 @@ __global__ void __launch_bounds__(256) adb_dot_simt(const float* __restrict__ A,
     }
 }
 
+// ====================================================================================================
+// Tensor-core path
+// ====================================================================================================
+namespace tc {
+
+constexpr int BM = 128;          // rows of C per tile (one tcgen05.mma M)
+constexpr int BN = 256;          // columns of C per tile (one tcgen05.mma N)
+constexpr int BK = 32;           // fp32 elements per k-block: 128 bytes = one 128B-swizzle span
+constexpr int UMMA_K = 8;        // k elements of one kind::tf32 instruction (32 bytes)
+constexpr int STAGES = 2;
+// The tensor core adds each K=8 partial product into the fp32 accumulator with truncation, so the error of a
+// long accumulation grows linearly with the number of instructions.  The k loop is therefore cut into chunks of
+// CHUNK_KB k-blocks (1024 elements): each chunk accumulates into a fresh TMEM buffer and the epilogue warps add
+// finished chunks into C with round-to-nearest fp32 adds (the C tile stays in L2 between chunks).
+constexpr int CHUNK_KB = 32;
+constexpr int A_BYTES = BM * BK * 4;                  // 16 KiB
+constexpr int B_BYTES = BN * BK * 4;                  // 32 KiB
+constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);  // hi and lo copies of both operands: 96 KiB
+constexpr int TMEM_COLS = 512;                        // two 128 x 256 fp32 accumulators
+constexpr int NUM_THREADS = 320;                      // warp 0 TMA, warp 1 MMA, warps 2-5 split, warps 6-9 epilogue
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;             // bounded waits: ~0.2-1 s, then the kernel gives up
+
+enum Status { OK = 0, TIMEOUT_EMPTY = 1, TIMEOUT_RAW = 2, TIMEOUT_SPLIT = 3, TIMEOUT_ACC_EMPTY = 4, TIMEOUT_ACC_FULL = 5, TIMEOUT_DRAIN = 6 };
+
+struct Params {
+    float* C;
+    int M, N, K;
+    int tiles_m, tiles_n, k_blocks;
+    int* status;
+    // shared-memory descriptor geometry of the two operands (bytes)
+    uint32_t a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep;
+    uint32_t a_layout, b_layout;  // descriptor swizzle mode: 2 = 128B (K-major), 1 = 128B with 32B atoms (MN-major tf32)
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait.  Returns false when the block was told to stop or the limit ran out (then it also
+// raises the block-wide stop flag and records `code` in the global status word).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* stop, int* status, int code) {
+    for (uint32_t it = 0; it < SPIN_LIMIT; it++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*stop) return false;
+        if (it > 64) __nanosleep(64);
+    }
+    *stop = 1;
+    atomicCAS(status, 0, code);
+    return false;
+}
+
+// All lanes of a warp wait (each observes the phase itself), then agree on the outcome so that the
+// warp never diverges around .aligned instructions or __syncwarp().
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* stop, int* status, int code) {
+    bool ok = mbar_wait(bar, parity, stop, status, code);
+    return __all_sync(0xffffffffu, ok);
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+// shared-memory matrix descriptor: start address, leading / stride byte offsets in 16-byte units, swizzle mode
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;  // descriptor version of this architecture
+    d |= (uint64_t)layout << 61;
+    return d;
+}
+
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// mbarrier arrives once every tcgen05.mma issued so far by this thread has finished
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_load_32cols(uint32_t taddr, float* v) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+
+// A_MN / B_MN: the operand is contiguous along M (resp. N) in global memory instead of along K.
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+adb_dot_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    // operand tiles need 1024-byte alignment for the 128B swizzle pattern
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+    // per stage: [A hi][B hi][A lo][B lo]
+    auto a_hi = [&](int s) { return base + s * STAGE_BYTES; };
+    auto b_hi = [&](int s) { return base + s * STAGE_BYTES + A_BYTES; };
+    const uint32_t bars = base + STAGES * STAGE_BYTES;
+    auto bar_raw = [&](int s) { return bars + 8u * s; };                    // TMA landed
+    auto bar_split = [&](int s) { return bars + 8u * (STAGES + s); };       // hi/lo written
+    auto bar_empty = [&](int s) { return bars + 8u * (2 * STAGES + s); };   // MMAs of the stage done
+    auto bar_acc_full = [&](int a) { return bars + 8u * (3 * STAGES + a); };
+    auto bar_acc_empty = [&](int a) { return bars + 8u * (3 * STAGES + 2 + a); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen_base + STAGES * STAGE_BYTES + 8 * (3 * STAGES + 4));
+    volatile int* stop = reinterpret_cast<volatile int*>(gen_base + STAGES * STAGE_BYTES + 8 * (3 * STAGES + 4) + 8);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_tiles = p.tiles_m * p.tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(bar_raw(s), 1);
+            mbar_init(bar_split(s), 4);   // one arrival per split warp
+            mbar_init(bar_empty(s), 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(bar_acc_full(a), 1);
+            mbar_init(bar_acc_empty(a), 4);  // one arrival per epilogue warp
+        }
+        *stop = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
+                for (int kb = 0; kb < p.k_blocks; kb++, it++) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(bar_empty(s), ph ^ 1, stop, p.status, TIMEOUT_EMPTY)) { ok = false; break; }
+                    mbar_expect_tx(bar_raw(s), A_BYTES + B_BYTES);
+                    const int k0 = kb * BK;
+                    if (A_MN) {
+#pragma unroll
+                        for (int c = 0; c < BM / 32; c++) tma_load_2d(a_hi(s) + c * (BK * 128), &map_a, bar_raw(s), m0 + 32 * c, k0);
+                    } else {
+                        tma_load_2d(a_hi(s), &map_a, bar_raw(s), k0, m0);
+                    }
+                    if (B_MN) {
+#pragma unroll
+                        for (int c = 0; c < BN / 32; c++) tma_load_2d(b_hi(s) + c * (BK * 128), &map_b, bar_raw(s), n0 + 32 * c, k0);
+                    } else {
+                        tma_load_2d(b_hi(s), &map_b, bar_raw(s), k0, n0);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            // instruction descriptor: fp32 accumulate, tf32 x tf32, operand majorness, N, M
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+                                   ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            // K-major tiles: rows of 128 B, 8-row groups 1024 B apart (SBO), a k-step moves 32 B inside the
+            // swizzle span.  MN-major tiles (tf32 allows only the 128B swizzle with 32-byte atoms there):
+            // 32-element column chunks of BK rows x 128 B, chunks BK*128 B apart (LBO), 4-row groups 512 B
+            // apart (SBO), a k-step moves 8 rows = 1024 B.
+            const uint32_t a_lbo = p.a_lbo, a_sbo = p.a_sbo, a_kstep = p.a_kstep;
+            const uint32_t b_lbo = p.b_lbo, b_sbo = p.b_sbo, b_kstep = p.b_kstep;
+            uint32_t it = 0, chunk_no = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                for (int kb0 = 0; kb0 < p.k_blocks && ok; kb0 += CHUNK_KB, chunk_no++) {
+                    const int acc = chunk_no & 1;
+                    const uint32_t acc_ph = (chunk_no >> 1) & 1;
+                    if (!mbar_wait(bar_acc_empty(acc), acc_ph ^ 1, stop, p.status, TIMEOUT_ACC_EMPTY)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t d_tmem = tmem_base + acc * BN;
+                    const int kb_end = min(kb0 + CHUNK_KB, p.k_blocks);
+                    for (int kb = kb0; kb < kb_end; kb++, it++) {
+                        const int s = it % STAGES;
+                        const uint32_t ph = (it / STAGES) & 1;
+                        if (!mbar_wait(bar_split(s), ph, stop, p.status, TIMEOUT_SPLIT)) { ok = false; break; }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                        for (int j = 0; j < BK / UMMA_K; j++) {
+                            const uint64_t ah = make_desc(a_hi(s) + j * a_kstep, a_lbo, a_sbo, p.a_layout);
+                            const uint64_t bh = make_desc(b_hi(s) + j * b_kstep, b_lbo, b_sbo, p.b_layout);
+                            const uint64_t al = make_desc(a_hi(s) + (A_BYTES + B_BYTES) + j * a_kstep, a_lbo, a_sbo, p.a_layout);
+                            const uint64_t bl = make_desc(b_hi(s) + (A_BYTES + B_BYTES) + j * b_kstep, b_lbo, b_sbo, p.b_layout);
+                            // small terms first, then the dominant one
+                            umma_tf32(d_tmem, al, bh, idesc, ((kb - kb0) | j) != 0);
+                            umma_tf32(d_tmem, ah, bl, idesc, 1);
+                            umma_tf32(d_tmem, ah, bh, idesc, 1);
+                        }
+                        umma_commit(bar_empty(s));
+                    }
+                    if (ok) umma_commit(bar_acc_full(acc));
+                }
+            }
+        }
+    } else if (warp < 6) {
+        // ------------------------------------------------------------------ split: raw fp32 -> tf32 hi (in place) + tf32 lo
+        const int t = threadIdx.x - 64;  // 0..127
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int kb = 0; kb < p.k_blocks; kb++, it++) {
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1;
+                if (!mbar_wait_warp(bar_raw(s), ph, stop, p.status, TIMEOUT_RAW)) { ok = false; break; }
+                uint4* hi = reinterpret_cast<uint4*>(gen_base + s * STAGE_BYTES);
+                uint4* lo = reinterpret_cast<uint4*>(gen_base + s * STAGE_BYTES + A_BYTES + B_BYTES);
+#pragma unroll 4
+                for (int i = t; i < (A_BYTES + B_BYTES) / 16; i += 128) {
+                    uint4 v = hi[i];
+                    uint4 h, l;
+                    h.x = v.x & 0xffffe000u; h.y = v.y & 0xffffe000u; h.z = v.z & 0xffffe000u; h.w = v.w & 0xffffe000u;
+                    l.x = __float_as_uint(__uint_as_float(v.x) - __uint_as_float(h.x)) & 0xffffe000u;
+                    l.y = __float_as_uint(__uint_as_float(v.y) - __uint_as_float(h.y)) & 0xffffe000u;
+                    l.z = __float_as_uint(__uint_as_float(v.z) - __uint_as_float(h.z)) & 0xffffe000u;
+                    l.w = __float_as_uint(__uint_as_float(v.w) - __uint_as_float(h.w)) & 0xffffe000u;
+                    hi[i] = h;
+                    lo[i] = l;
+                }
+                // make the generic-proxy writes visible to the tensor core (async proxy) before signalling
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_split(s));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue: TMEM -> registers -> global
+        const int q = warp & 3;  // TMEM lane quadrant this warp may read
+        uint32_t chunk_no = 0;
+        bool ok = true;
+        const bool vec_ok = (p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
+            const int row = m0 + q * 32 + lane;
+            float* crow = p.C + (size_t)row * p.N;
+            for (int kb0 = 0; kb0 < p.k_blocks && ok; kb0 += CHUNK_KB, chunk_no++) {
+                const int acc = chunk_no & 1;
+                const uint32_t acc_ph = (chunk_no >> 1) & 1;
+                const bool first = kb0 == 0;  // first chunk of the tile overwrites C, later ones add to it
+                if (!mbar_wait_warp(bar_acc_full(acc), acc_ph, stop, p.status, TIMEOUT_ACC_FULL)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; c++) {
+                    float v[32];
+                    tmem_load_32cols(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, v);
+                    const int col0 = n0 + c * 32;
+                    if (row < p.M && col0 < p.N) {
+                        if (vec_ok && col0 + 32 <= p.N) {
+                            float4* dst = reinterpret_cast<float4*>(crow + col0);
+                            if (first) {
+#pragma unroll
+                                for (int j = 0; j < 8; j++) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                            } else {
+                                // fire-and-forget fp32 adds performed at the L2 (round to nearest): no load latency
+                                // in the epilogue and no extra registers; same-thread same-address ordering keeps
+                                // them behind the stores of the first chunk
+#pragma unroll
+                                for (int j = 0; j < 8; j++)
+                                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "f"(v[4 * j]),
+                                                 "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3]) : "memory");
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
+                                if (col0 + j < p.N) {
+                                    if (first) crow[col0 + j] = v[j];
+                                    else atomicAdd(crow + col0 + j, v[j]);
+                                }
+                        }
+                    }
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_acc_empty(acc));
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    __syncthreads();
+    if (*stop && threadIdx.x == 0) {
+        // a role gave up: give bulk copies that may still be in flight a bounded time to land
+        for (int i = 0; i < 256; i++) __nanosleep(1000);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// 2-d fp32 tensor map: inner axis `inner` elements (unit stride), outer axis `outer` elements with
+// `outer_stride` elements between rows; boxes are 32 inner elements (128 B, swizzled) by `box_outer` rows.
+static bool encode(EncodeTiledFn fn, CUtensorMap* map, const float* ptr, long long inner, long long outer, long long outer_stride,
+                   int box_outer, bool mn_major) {
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+    cuuint64_t strides[1] = {(cuuint64_t)outer_stride * 4};
+    cuuint32_t box[2] = {32, (cuuint32_t)box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+}  // namespace tc
+
 bool gemm_init(GemmContext& ctx, int sm_count, std::string& err) {
     ctx.sm_count = sm_count;
-    (void)err;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess && fn &&
+        q == cudaDriverEntryPointSuccess) {
+        ctx.encode_tiled = fn;
+    } else {
+        cudaGetLastError();
+        err = "cuTensorMapEncodeTiled is not available from this driver";
+        return false;
+    }
+    if (cudaMalloc(&ctx.status, sizeof(int)) != cudaSuccess) { err = "cudaMalloc(status)"; return false; }
+    cudaMemset(ctx.status, 0, sizeof(int));
+    if (cudaMallocHost(&ctx.status_host, sizeof(int)) != cudaSuccess) { err = "cudaMallocHost(status)"; return false; }
+    *ctx.status_host = 0;
+    cudaError_t e = cudaSuccess;
+    e = cudaFuncSetAttribute(tc::adb_dot_tc<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::adb_dot_tc<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::adb_dot_tc<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::adb_dot_tc<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
+    if (e != cudaSuccess) { err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e); return false; }
+    ctx.tc_ready = true;
     return true;
 }
 
-void gemm_destroy(GemmContext& ctx) { (void)ctx; }
+void gemm_destroy(GemmContext& ctx) {
+    if (ctx.status) cudaFree(ctx.status);
+    if (ctx.status_host) cudaFreeHost(ctx.status_host);
+    ctx.status = nullptr;
+    ctx.status_host = nullptr;
+}
+
+// An operand can be fed by TMA when one axis has unit stride, the other a stride that is a multiple
+// of 16 bytes, and the base is 16-byte aligned.
+static bool tma_ok(const float* p, long long unit_len, long long other_stride) {
+    (void)unit_len;
+    return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && other_stride % 4 == 0 && other_stride > 0;
+}
 
 int gemm_launch(GemmContext& ctx, const GemmArgs& a, cudaStream_t stream, std::string& err) {
-    (void)ctx;
     if (a.M <= 0 || a.N <= 0) return 0;
+    bool use_tc = ctx.tc_ready && !a.force_simt && a.K >= 8 && a.M >= 32 && a.N >= 32 &&
+                  (double)a.M * (double)a.N * (double)a.K >= double(1 << 21) && a.M < (1ll << 31) && a.N < (1ll << 31) &&
+                  a.K < (1ll << 31);
+    bool a_k = a.a_cs == 1 && tma_ok(a.A, a.K, a.a_rs);    // K contiguous
+    bool a_mn = a.a_rs == 1 && tma_ok(a.A, a.M, a.a_cs);   // M contiguous
+    bool b_mn = a.b_cs == 1 && tma_ok(a.B, a.N, a.b_rs);   // N contiguous
+    bool b_k = a.b_rs == 1 && tma_ok(a.B, a.K, a.b_cs);    // K contiguous
+    if (use_tc && (a_k || a_mn) && (b_k || b_mn)) {
+        using namespace tc;
+        auto enc = reinterpret_cast<EncodeTiledFn>(ctx.encode_tiled);
+        CUtensorMap ma, mb;
+        const bool A_MN = !a_k, B_MN = !b_k;
+        bool ok = A_MN ? encode(enc, &ma, a.A, a.M, a.K, a.a_cs, BK, true) : encode(enc, &ma, a.A, a.K, a.M, a.a_rs, BM, false);
+        ok = ok && (B_MN ? encode(enc, &mb, a.B, a.N, a.K, a.b_rs, BK, true) : encode(enc, &mb, a.B, a.K, a.N, a.b_cs, BN, false));
+        if (ok) {
+            Params p;
+            p.C = a.C;
+            p.M = (int)a.M; p.N = (int)a.N; p.K = (int)a.K;
+            p.tiles_m = (int)((a.M + BM - 1) / BM);
+            p.tiles_n = (int)((a.N + BN - 1) / BN);
+            p.k_blocks = (int)((a.K + BK - 1) / BK);
+            p.status = ctx.status;
+            p.a_lbo = A_MN ? BK * 128 : 16; p.a_sbo = A_MN ? 512 : 1024; p.a_kstep = A_MN ? 1024 : UMMA_K * 4; p.a_layout = A_MN ? 1 : 2;
+            p.b_lbo = B_MN ? BK * 128 : 16; p.b_sbo = B_MN ? 512 : 1024; p.b_kstep = B_MN ? 1024 : UMMA_K * 4; p.b_layout = B_MN ? 1 : 2;
+            if (const char* dbg = getenv("ADB_TC_DESC")) {
+                unsigned l, sb, ks;
+                if (sscanf(dbg, "%u,%u,%u", &l, &sb, &ks) == 3) {
+                    if (A_MN) { p.a_lbo = l; p.a_sbo = sb; p.a_kstep = ks; }
+                    if (B_MN) { p.b_lbo = l; p.b_sbo = sb; p.b_kstep = ks; }
+                }
+            }
+            int grid = p.tiles_m * p.tiles_n;
+            if (grid > ctx.sm_count) grid = ctx.sm_count;
+            if (A_MN && B_MN) adb_dot_tc<true, true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, p);
+            else if (A_MN) adb_dot_tc<true, false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, p);
+            else if (B_MN) adb_dot_tc<false, true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, p);
+            else adb_dot_tc<false, false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, p);
+            cudaError_t e = cudaGetLastError();
+            if (e != cudaSuccess) { err = std::string("adb_dot_tc launch: ") + cudaGetErrorString(e); return -1; }
+            ctx.tc_launches++;
+            ctx.tc_total++;
+            return 1;
+        }
+        // descriptor could not be encoded (odd strides): fall through to the CUDA-core kernel
+    }
     dim3 grid((unsigned)((a.N + 63) / 64), (unsigned)((a.M + 63) / 64));
     if (grid.y > 65535) { err = "M too large for the SIMT dot kernel"; return -1; }
     adb_dot_simt<64, 64, 16><<<grid, 256, 0, stream>>>(a.A, a.B, a.C, a.M, a.N, a.K, a.a_rs, a.a_cs, a.b_rs, a.b_cs);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { err = cudaGetErrorString(e); return -1; }
     return 1;
+}
+
+int gemm_check_status(GemmContext& ctx, cudaStream_t stream) {
+    if (!ctx.status || ctx.tc_launches == 0) return 0;
+    if (cudaMemcpyAsync(ctx.status_host, ctx.status, sizeof(int), cudaMemcpyDeviceToHost, stream) != cudaSuccess) return -1;
+    if (cudaStreamSynchronize(stream) != cudaSuccess) return -1;
+    int s = *ctx.status_host;
+    if (s != 0) cudaMemsetAsync(ctx.status, 0, sizeof(int), stream);
+    ctx.tc_launches = 0;
+    return s;
 }
 
 }  // namespace adb

@@ -23,6 +23,8 @@ struct GemmContext {
     bool tc_ready = false;
     int* status = nullptr;         // device word the tensor-core kernel sets when a bounded wait runs out
     int* status_host = nullptr;
+    unsigned long long tc_launches = 0;  // tensor-core launches since the last status check
+    unsigned long long tc_total = 0;     // tensor-core launches since the context was created
 };
 
 bool gemm_init(GemmContext& ctx, int sm_count, std::string& err);
@@ -30,5 +32,9 @@ void gemm_destroy(GemmContext& ctx);
 
 // Enqueues the product on `stream`; returns the number of kernels launched, or -1 with `err` set.
 int gemm_launch(GemmContext& ctx, const GemmArgs& a, cudaStream_t stream, std::string& err);
+
+// Reads the status word of the tensor-core kernel (0 = fine; otherwise which bounded wait ran out).
+// Synchronises `stream`.  Returns -1 when the status itself could not be read.
+int gemm_check_status(GemmContext& ctx, cudaStream_t stream);
 
 }  // namespace adb

@@ -596,6 +596,7 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
     }
 
     Executor ex(d, cp);
+    const unsigned long long tc_before = d->gemm.tc_total;
     d->exit_requested = false;
     d->upload_events.clear();
     d->prof.clear();
@@ -626,6 +627,11 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
     }
     ck(cudaEventRecord(ev2, d->stream), "event record");
     ck(cudaStreamSynchronize(d->stream), "synchronize");
+    if (int gs = gemm_check_status(d->gemm, d->stream)) {
+        d->err = "tensor-core dot product gave up on a bounded wait (code " + std::to_string(gs) + "); results are invalid";
+        ex.release_events();
+        return ADB_ERR_CUDA;
+    }
     float ms_run = 0, ms_rb = 0;
     cudaEventElapsedTime(&ms_run, ev0, ev1);
     cudaEventElapsedTime(&ms_rb, ev1, ev2);
@@ -640,6 +646,7 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
     d->stats.readback_ms = ms_rb;
     d->stats.kernel_launches = ex.launches_;
     d->stats.gemm_launches = ex.gemms_;
+    d->stats.tc_gemm_launches = d->gemm.tc_total - tc_before;
     if (!d->prof.empty()) {
         std::map<int, std::pair<double, std::pair<double, uint64_t>>> per_kernel;  // kernel -> (ms, (bytes, launches))
         for (auto& r : d->prof) {

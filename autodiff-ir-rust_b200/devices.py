@@ -50,7 +50,8 @@ class AdbStats(ctypes.Structure):
                 ("collective_ms", ctypes.c_double), ("elw_launches", ctypes.c_uint64), ("reduce_launches", ctypes.c_uint64),
                 ("collective_launches", ctypes.c_uint64), ("elw_bytes", ctypes.c_double), ("reduce_bytes", ctypes.c_double),
                 ("gemm_flops", ctypes.c_double), ("collective_bytes", ctypes.c_double), ("top_ms", ctypes.c_double),
-                ("top_bytes", ctypes.c_double), ("top_launches", ctypes.c_uint64), ("top_name", ctypes.c_char * 64)]
+                ("top_bytes", ctypes.c_double), ("top_launches", ctypes.c_uint64), ("top_name", ctypes.c_char * 64),
+                ("tc_gemm_launches", ctypes.c_uint64)]
 
     def as_dict(self):
         d = {k: getattr(self, k) for k, _ in self._fields_}

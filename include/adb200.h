@@ -134,6 +134,7 @@ typedef struct adb_stats {
     double top_ms, top_bytes;
     uint64_t top_launches;
     char top_name[64];
+    uint64_t tc_gemm_launches; /* dot products of this execute that ran on the tcgen05 3xTF32 kernel */
 } adb_stats;
 adb_status adb_get_stats(adb_device *dev, adb_stats *out);
 

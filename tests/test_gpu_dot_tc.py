@@ -1,0 +1,80 @@
+"""The tcgen05 3xTF32 dot product: every operand majorness, ragged edges, long K, against float64."""
+import numpy as np
+import pytest
+
+from helpers import ad, b200, oracle, assert_rel
+
+pytestmark = pytest.mark.gpu
+RNG = np.random.default_rng(23)
+
+
+def _dot(dev, a, b, ta, tb, M, K, N):
+    ad.set_device(dev)
+    ad.eager_dep_opt()
+    A = ad.tensor(a, [K, M] if ta else [M, K])
+    B = ad.tensor(b, [N, K] if tb else [K, N])
+    y = ad.dot(A.t() if ta else A, B.t() if tb else B)
+    y.forward()
+    y.val().keep()
+    ad.execute()
+    return y.val().get()
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (True, False), (False, True), (True, True)])
+@pytest.mark.parametrize("M,K,N", [(128, 64, 256), (256, 32, 512), (200, 100, 300), (384, 1024, 520), (96, 4096, 1000)])
+def test_tc_dot_matches_float64(M, K, N, ta, tb):
+    a = RNG.standard_normal(M * K).astype(np.float32)
+    b = RNG.standard_normal(K * N).astype(np.float32)
+    dev = b200()
+    got = _dot(dev, a, b, ta, tb, M, K, N)
+    assert dev.stats()["tc_gemm_launches"] == 1, "expected the tensor-core kernel for this shape"
+    A = a.reshape(K, M).T if ta else a.reshape(M, K)
+    B = b.reshape(N, K).T if tb else b.reshape(K, N)
+    ref = A.astype(np.float64) @ B.astype(np.float64)
+    g = np.asarray(got.data, np.float64).reshape(M, N)
+    err = np.abs(g - ref).max() / np.abs(ref).max()
+    # fp32-level: the tensor core truncates when it accumulates, the kernel bounds that by flushing the
+    # accumulator every 1024 k-elements; what remains is ~1e-5 of the largest element for any K
+    assert err < 1.5e-5, f"relative error {err:.3e} (3xTF32 should be at fp32 level)"
+
+
+@pytest.mark.parametrize("M,K,N,ta,tb", [(256, 16384, 256, False, False), (128, 65536, 256, True, False)])
+def test_tc_dot_error_does_not_grow_with_k(M, K, N, ta, tb):
+    a = RNG.standard_normal(M * K).astype(np.float32)
+    b = RNG.standard_normal(K * N).astype(np.float32)
+    dev = b200()
+    got = _dot(dev, a, b, ta, tb, M, K, N)
+    assert dev.stats()["tc_gemm_launches"] == 1
+    A = a.reshape(K, M).T if ta else a.reshape(M, K)
+    B = b.reshape(N, K).T if tb else b.reshape(K, N)
+    ref = A.astype(np.float64) @ B.astype(np.float64)
+    g = np.asarray(got.data, np.float64).reshape(M, N)
+    err = np.abs(g - ref).max() / np.abs(ref).max()
+    assert err < 2e-5, f"relative error {err:.3e} at K={K}"
+
+
+def test_tc_dot_matches_oracle_and_simt():
+    M, K, N = 256, 512, 512
+    a = RNG.standard_normal(M * K).astype(np.float32)
+    b = RNG.standard_normal(K * N).astype(np.float32)
+    want = _dot(oracle(), a, b, False, False, M, K, N)
+    got = _dot(b200(), a, b, False, False, M, K, N)
+    assert_rel("tc vs oracle", got, want, 1e-4)
+    adb = __import__("importlib").import_module("autodiff-ir-rust_b200")
+    simt = adb.devices.B200(0, flags=adb.devices.FLAG_SIMT_DOT)
+    try:
+        ref = _dot(simt, a, b, False, False, M, K, N)
+        assert simt.stats()["tc_gemm_launches"] == 0
+    finally:
+        simt.close()
+    assert_rel("tc vs simt", got, ref, 1e-5)
+
+
+def test_tc_dot_exact_on_small_integers():
+    """Products of small integers are exact in every term of the split: the result must be exact."""
+    M, K, N = 128, 256, 256
+    a = RNG.integers(-8, 9, M * K).astype(np.float32)
+    b = RNG.integers(-8, 9, K * N).astype(np.float32)
+    got = _dot(b200(), a, b, False, False, M, K, N)
+    ref = a.reshape(M, K).astype(np.int64) @ b.reshape(K, N).astype(np.int64)
+    np.testing.assert_array_equal(np.asarray(got.data).reshape(M, N), ref.astype(np.float32))
