@@ -982,12 +982,17 @@ def try_broadcast(a: Tensor, b: Tensor):
 # --------------------------------------------------------------------------------------
 # public constructors and session control (src/core/autodiff.rs)
 # --------------------------------------------------------------------------------------
-def tensor(data, dim) -> Tensor:
+def tensor(data, dim, local_rows=None) -> Tensor:
+    """`autodiff::tensor` (src/core/autodiff.rs:24-41).  `local_rows`: for data-parallel runs the caller may
+    hand over only its own rows of a tensor whose `dim` is the global shape (the device splits axis 0)."""
     dim = list(dim)
     if isinstance(data, (list, tuple)):
         data = np.asarray(data, dtype=f32)
     n = len(data)
-    if n != (int(np.prod(dim)) if dim else 1):
+    full = int(np.prod(dim)) if dim else 1
+    if local_rows is not None:
+        full = full // dim[0] * local_rows
+    if n != full:
         raise ValueError("# of values doesn't match dim size when calling from_vec")
     v = Value.new(data, dim)
     if not is_harsh():

@@ -1,11 +1,350 @@
+// Data-parallel rewrite of an IR program: one process per GPU, the batch axis split across ranks,
+// parameters replicated, gradients summed with an all-reduce before they meet replicated values.
+// The reference is single-device and has nothing comparable; this pass works on the same IR commands
+// (src/core/ir.rs:8-105) and inserts the extension command AllReduce.
+//
+// Every id gets a tag while the program is walked in order:
+//   REP        the same value on every rank (parameters, scalars)
+//   SHARD(d)   the rank holds its 1/world slice of axis d (the batch, wherever views / permutes moved it)
+//   PART       per-rank partial sum whose true value is the sum over ranks (a contraction over the batch)
+//   CONST      CreateConstant: conforms to anything
+// Linear ops keep PART (scaling by a constant, adding two partial sums, Sum); everything else forces an
+// AllReduce of the partial operand first.  That puts the collective where the SGD update consumes the
+// gradient: `p += -1 * (lr * grad)` all-reduces the scaled gradient right before the in-place add.
 #include "adb_shard.hpp"
+
+#include <functional>
+#include <set>
 
 namespace adb {
 
+namespace {
+
+enum Tag : uint8_t { T_UNDEF, T_REP, T_SHARD, T_PART, T_CONST };
+
+struct Info {
+    Tag tag = T_UNDEF;
+    int axis = 0;
+    std::vector<int64_t> dims;  // global shape
+};
+
+struct Sharder {
+    Program& prog;
+    int rank, world;
+    int64_t batch;
+    std::vector<Info> info;
+    std::vector<char> needed, is_dep;
+
+    Sharder(Program& p, int r, int w, int64_t b) : prog(p), rank(r), world(w), batch(b) {
+        info.resize(p.ids.size());
+        needed.assign(p.ids.size(), 0);
+        is_dep.assign(p.ids.size(), 0);
+    }
+
+    [[noreturn]] void fail(const std::string& m) { throw IrError("data-parallel rewrite: " + m); }
+    const std::string& name(uint32_t id) { return prog.ids[id]; }
+
+    static void reads(const Cmd& c, uint32_t out[2], int& n) {
+        n = 0;
+        switch (c.op) {
+        case OP_MUL: case OP_ADD: case OP_DOT: case OP_CONCAT: case OP_MUL_EQ: case OP_ADD_EQ: out[n++] = c.a; out[n++] = c.b; break;
+        case OP_EQZ: case OP_GTZ: case OP_LTZ: case OP_SUM: case OP_CONTIG: case OP_EXP2: case OP_LOG2: case OP_SIN:
+        case OP_RECIP: case OP_SQRT: case OP_VIEW: case OP_INDEX: case OP_PERMUTE: case OP_BROADCAST: case OP_ALLREDUCE:
+            out[n++] = c.a; break;
+        default: break;
+        }
+    }
+    static bool has_result(uint8_t op) { return !(op == OP_WHILE || op == OP_IF || op == OP_EX || op == OP_HEADING); }
+
+    // commands whose result cannot reach the dep list or a condition are left alone (no collectives for dead values)
+    void mark_needed() {
+        for (auto d : prog.dep) { needed[d] = 1; is_dep[d] = 1; }
+        std::function<void(Block&)> conds = [&](Block& b) {
+            for (auto& c : b.cmds) {
+                if (c.op == OP_WHILE) { needed[c.a] = 1; conds(*c.block); }
+                else if (c.op == OP_IF) {
+                    for (auto& cb : c.conds) { needed[cb.first] = 1; conds(*cb.second); }
+                    if (c.else_block) conds(*c.else_block);
+                }
+            }
+        };
+        conds(prog.main);
+        bool changed = true;
+        std::function<void(Block&)> walk = [&](Block& b) {
+            for (auto& c : b.cmds) {
+                if (c.op == OP_WHILE) walk(*c.block);
+                else if (c.op == OP_IF) {
+                    for (auto& cb : c.conds) walk(*cb.second);
+                    if (c.else_block) walk(*c.else_block);
+                } else if (has_result(c.op) && needed[c.res]) {
+                    uint32_t r[2];
+                    int n;
+                    reads(c, r, n);
+                    for (int k = 0; k < n; k++)
+                        if (!needed[r[k]]) { needed[r[k]] = 1; changed = true; }
+                }
+            }
+        };
+        while (changed) { changed = false; walk(prog.main); }
+    }
+
+    Cmd make_allreduce(uint32_t id) {
+        Cmd c;
+        c.op = OP_ALLREDUCE;
+        c.a = id;
+        c.res = id;
+        return c;
+    }
+
+    // make sure `id` is a full value before a non-linear use
+    void resolve_partial(uint32_t id, std::vector<Cmd>& out) {
+        if (info[id].tag == T_PART) {
+            out.push_back(make_allreduce(id));
+            info[id].tag = T_REP;
+            prog.n_cmds++;
+        }
+    }
+
+    void set(uint32_t id, Tag t, int axis, const std::vector<int64_t>& dims, const Cmd&) {
+        Info& i = info[id];
+        // an id that is assigned again (loop-carried state, op-assign) must stay sharded / unsharded as it was
+        const bool was = i.tag == T_SHARD, now = t == T_SHARD;
+        if (i.tag != T_UNDEF && (was != now || (now && i.axis != axis)))
+            fail("id '" + name(id) + "' changes its distribution between assignments");
+        i.tag = t;
+        i.axis = axis;
+        i.dims = dims;
+    }
+
+    void block(Block& b) {
+        std::vector<Cmd> out;
+        out.reserve(b.cmds.size() + 8);
+        for (auto& c : b.cmds) {
+            if (c.op == OP_WHILE) {
+                if (info[c.a].tag == T_SHARD) fail("loop condition '" + name(c.a) + "' is sharded");
+                resolve_partial(c.a, out);
+                block(*c.block);
+                // the condition is recomputed inside the body into the same id
+                if (info[c.a].tag == T_PART) {
+                    c.block->cmds.push_back(make_allreduce(c.a));
+                    info[c.a].tag = T_REP;
+                    prog.n_cmds++;
+                }
+                out.push_back(std::move(c));
+                continue;
+            }
+            if (c.op == OP_IF) {
+                for (auto& cb : c.conds) {
+                    if (info[cb.first].tag == T_SHARD) fail("condition '" + name(cb.first) + "' is sharded");
+                    resolve_partial(cb.first, out);
+                }
+                for (auto& cb : c.conds) block(*cb.second);
+                if (c.else_block) block(*c.else_block);
+                out.push_back(std::move(c));
+                continue;
+            }
+            if (!has_result(c.op) || !needed[c.res]) {
+                out.push_back(std::move(c));
+                continue;
+            }
+            step(c, out);
+            uint32_t res = c.res;
+            out.push_back(std::move(c));
+            if (is_dep[res] && info[res].tag == T_PART) {
+                // a kept partial value is completed right where it is produced
+                out.push_back(make_allreduce(res));
+                info[res].tag = T_REP;
+                prog.n_cmds++;
+            }
+        }
+        b.cmds = std::move(out);
+    }
+
+    static int64_t prod(const std::vector<int64_t>& d, size_t from, size_t to) {
+        int64_t p = 1;
+        for (size_t i = from; i < to; i++) p *= d[i];
+        return p;
+    }
+
+    void step(Cmd& c, std::vector<Cmd>& out) {
+        switch (c.op) {
+        case OP_CREATE_MAT: {
+            std::vector<int64_t> g = c.dims;
+            int64_t n = prod(g, 0, g.size());
+            if (!g.empty() && g[0] == batch) {
+                if (batch % world) fail("batch is not divisible by the number of ranks");
+                int64_t local = n / world;
+                if (int64_t(c.count) == n) {
+                    c.payload += uint64_t(rank) * uint64_t(local) * 4;  // this rank's rows of the full tensor
+                } else if (int64_t(c.count) != local) {
+                    fail("CreateMat '" + name(c.res) + "' holds neither the full batch nor this rank's share");
+                }
+                c.count = uint64_t(local);
+                c.dims[0] = batch / world;
+                set(c.res, T_SHARD, 0, g, c);
+            } else
+                set(c.res, T_REP, 0, g, c);
+            return;
+        }
+        case OP_CREATE_CONST: {
+            std::vector<int64_t> g = c.dims;
+            for (auto& d : c.dims)
+                if (d == batch) { d = batch / world; break; }
+            set(c.res, T_CONST, 0, g, c);
+            return;
+        }
+        case OP_MUL: case OP_ADD: case OP_MUL_EQ: case OP_ADD_EQ: {
+            const bool mul = c.op == OP_MUL || c.op == OP_MUL_EQ;
+            Info a = info[c.a], b = info[c.b];
+            if (a.tag == T_UNDEF || b.tag == T_UNDEF) fail("'" + name(a.tag == T_UNDEF ? c.a : c.b) + "' is read before it is defined");
+            // linear cases keep partial sums partial
+            bool keep_partial = (mul && ((a.tag == T_PART && b.tag == T_CONST) || (a.tag == T_CONST && b.tag == T_PART))) ||
+                                (!mul && a.tag == T_PART && b.tag == T_PART);
+            if (!keep_partial) {
+                resolve_partial(c.a, out);
+                resolve_partial(c.b, out);
+                a = info[c.a];
+                b = info[c.b];
+            }
+            const Info& shape_src = a.tag == T_CONST ? b : a;
+            if (keep_partial) { set(c.res, T_PART, 0, shape_src.dims, c); return; }
+            if (a.tag == T_CONST && b.tag == T_CONST) { set(c.res, T_CONST, 0, a.dims, c); return; }
+            if (a.tag == T_SHARD || b.tag == T_SHARD) {
+                const Info& s = a.tag == T_SHARD ? a : b;
+                const Info& o = a.tag == T_SHARD ? b : a;
+                if (o.tag == T_REP) fail("'" + name(c.a) + "' and '" + name(c.b) + "' mix a sharded and a replicated tensor of the same shape");
+                if (o.tag == T_SHARD && o.axis != s.axis) fail("operands are sharded along different axes");
+                set(c.res, T_SHARD, s.axis, s.dims, c);
+                return;
+            }
+            set(c.res, T_REP, 0, shape_src.dims, c);
+            return;
+        }
+        case OP_EQZ: case OP_GTZ: case OP_LTZ: case OP_EXP2: case OP_LOG2: case OP_SIN: case OP_RECIP: case OP_SQRT: case OP_CONTIG: {
+            if (info[c.a].tag == T_UNDEF) fail("'" + name(c.a) + "' is read before it is defined");
+            resolve_partial(c.a, out);
+            Info a = info[c.a];
+            set(c.res, a.tag, a.axis, a.dims, c);
+            return;
+        }
+        case OP_SUM: {
+            Info a = info[c.a];
+            if (a.dims.size() != 2) fail("Sum needs a 2-d operand");
+            std::vector<int64_t> g{a.dims[0]};
+            if (a.tag == T_SHARD) {
+                if (a.axis == 0) set(c.res, T_SHARD, 0, g, c);
+                else set(c.res, T_PART, 0, g, c);
+            } else if (a.tag == T_PART) set(c.res, T_PART, 0, g, c);
+            else set(c.res, T_REP, 0, g, c);
+            return;
+        }
+        case OP_DOT: {
+            resolve_partial(c.a, out);
+            resolve_partial(c.b, out);
+            Info a = info[c.a], b = info[c.b];
+            if (a.dims.size() != 2 || b.dims.size() != 2) fail("DotProduct needs 2-d operands");
+            std::vector<int64_t> g{a.dims[0], b.dims[1]};
+            bool a_rep = a.tag == T_REP || a.tag == T_CONST, b_rep = b.tag == T_REP || b.tag == T_CONST;
+            if (a.tag == T_SHARD && a.axis == 0 && b_rep) set(c.res, T_SHARD, 0, g, c);
+            else if (a.tag == T_SHARD && a.axis == 1 && b.tag == T_SHARD && b.axis == 0) set(c.res, T_PART, 0, g, c);
+            else if (a_rep && b.tag == T_SHARD && b.axis == 1) set(c.res, T_SHARD, 1, g, c);
+            else if (a_rep && b_rep) set(c.res, T_REP, 0, g, c);
+            else fail("DotProduct of '" + name(c.a) + "' and '" + name(c.b) + "' cannot be split over the batch");
+            return;
+        }
+        case OP_VIEW: {
+            Info a = info[c.a];
+            std::vector<int64_t> g = c.dims;
+            if (a.tag == T_SHARD) {
+                int64_t before = prod(a.dims, 0, size_t(a.axis));
+                int64_t p = 1;
+                int nd = -1;
+                for (size_t i = 0; i < g.size(); i++) {
+                    if (p == before && g[i] != 1) { nd = int(i); break; }
+                    p *= g[i];
+                }
+                if (nd < 0) fail("View of '" + name(c.a) + "' loses the sharded axis");
+                int64_t old_ext = a.dims[a.axis], new_ext = g[nd];
+                bool ok = new_ext % world == 0 && (new_ext % old_ext == 0 || old_ext % new_ext == 0);
+                if (!ok) fail("View of '" + name(c.a) + "' cuts through the sharded axis");
+                c.dims[nd] = new_ext / world;
+                set(c.res, T_SHARD, nd, g, c);
+            } else
+                set(c.res, a.tag, 0, g, c);
+            return;
+        }
+        case OP_INDEX: {
+            Info a = info[c.a];
+            std::vector<int64_t> g = a.dims;
+            if (c.dim >= g.size()) fail("Index axis out of range");
+            g.erase(g.begin() + c.dim);
+            if (a.tag == T_SHARD) {
+                if (int(c.dim) == a.axis) fail("Index into the sharded axis of '" + name(c.a) + "'");
+                set(c.res, T_SHARD, a.axis - (int(c.dim) < a.axis ? 1 : 0), g, c);
+            } else
+                set(c.res, a.tag, 0, g, c);
+            return;
+        }
+        case OP_PERMUTE: {
+            Info a = info[c.a];
+            std::vector<int64_t> g(c.perm.size());
+            int nd = 0;
+            for (size_t i = 0; i < c.perm.size(); i++) {
+                if (c.perm[i] >= a.dims.size()) fail("Permute index out of bounds");
+                g[i] = a.dims[c.perm[i]];
+                if (int(c.perm[i]) == a.axis) nd = int(i);
+            }
+            set(c.res, a.tag, a.tag == T_SHARD ? nd : 0, g, c);
+            return;
+        }
+        case OP_BROADCAST: {
+            resolve_partial(c.a, out);
+            Info a = info[c.a];
+            std::vector<int64_t> g = a.dims;
+            if (c.dim >= g.size()) fail("Broadcast axis out of range");
+            g[c.dim] = int64_t(c.count);
+            if (a.tag == T_SHARD) {
+                if (int(c.dim) == a.axis) fail("Broadcast along the sharded axis");
+                set(c.res, T_SHARD, a.axis, g, c);
+            } else if (int64_t(c.count) == batch) {
+                // a replicated value repeated along the batch: every rank materialises only its rows
+                c.count = uint64_t(batch / world);
+                set(c.res, T_SHARD, int(c.dim), g, c);
+            } else
+                set(c.res, a.tag, 0, g, c);
+            return;
+        }
+        case OP_CONCAT: {
+            resolve_partial(c.a, out);
+            resolve_partial(c.b, out);
+            Info a = info[c.a], b = info[c.b];
+            std::vector<int64_t> g = a.dims;
+            if (c.dim >= g.size() || b.dims.size() != g.size()) fail("Concat rank mismatch");
+            g[c.dim] += b.dims[c.dim];
+            if (a.tag == T_SHARD || b.tag == T_SHARD) {
+                if (a.tag != b.tag || a.axis != b.axis || a.axis == int(c.dim)) fail("Concat of differently distributed tensors");
+                set(c.res, T_SHARD, a.axis, g, c);
+            } else
+                set(c.res, T_REP, 0, g, c);
+            return;
+        }
+        case OP_ALLREDUCE:
+            info[c.a].tag = T_REP;
+            return;
+        default: return;
+        }
+    }
+};
+
+}  // namespace
+
 void shard_program(Program& prog, int rank, int world, int64_t batch) {
-    (void)prog; (void)rank; (void)batch;
     if (world <= 1) return;
-    throw IrError("data-parallel rewrite not built yet");
+    if (batch <= 0) throw IrError("data-parallel rewrite: shard_batch must be positive");
+    if (rank < 0 || rank >= world) throw IrError("data-parallel rewrite: rank out of range");
+    Sharder s(prog, rank, world, batch);
+    s.mark_needed();
+    s.block(prog.main);
 }
 
 }  // namespace adb

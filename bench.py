@@ -96,7 +96,7 @@ def mlp_flops_per_step(batch, widths):
     return fwd + dw + dx
 
 
-def trace_c4(adb, dev, inputs, batch, widths, steps, upload_in_loop):
+def trace_c4(adb, dev, inputs, batch, widths, steps, upload_in_loop, local_rows=None):
     """Traces config 4.  With `upload_in_loop` the batch tensors are created inside the loop body."""
     ad, nn, f32 = adb.autodiff, adb.nn, adb.autodiff.f32
     ad.set_device(dev)
@@ -105,8 +105,8 @@ def trace_c4(adb, dev, inputs, batch, widths, steps, upload_in_loop):
     ws = [ad.tensor(inputs[f"w{i}"], [widths[i], widths[i + 1]]) for i in range(L)]
     bs = [ad.tensor(inputs[f"b{i}"], [widths[i + 1]]) for i in range(L)]
     if not upload_in_loop:
-        x = ad.tensor(inputs["x"], [batch, widths[0]])
-        t = ad.tensor(inputs["t"], [batch, widths[-1]])
+        x = ad.tensor(inputs["x"], [batch, widths[0]], local_rows)
+        t = ad.tensor(inputs["t"], [batch, widths[-1]], local_rows)
     net = nn.Sequential()
     for i in range(L):
         net.insert(nn.LinearWithWeights(ws[i], bs[i]))
@@ -116,8 +116,8 @@ def trace_c4(adb, dev, inputs, batch, widths, steps, upload_in_loop):
     box = {}
 
     def body(_):
-        xx = ad.tensor(inputs["x"], [batch, widths[0]]) if upload_in_loop else x
-        tt = ad.tensor(inputs["t"], [batch, widths[-1]]) if upload_in_loop else t
+        xx = ad.tensor(inputs["x"], [batch, widths[0]], local_rows) if upload_in_loop else x
+        tt = ad.tensor(inputs["t"], [batch, widths[-1]], local_rows) if upload_in_loop else t
         y = net.f(xx)
         d = y - tt
         loss = d.pow2().sum(1).sum(0) * f32(1.0 / (batch * widths[-1]))
@@ -186,7 +186,7 @@ def run_ours(args):
         return float(t.item())
 
     def once(inputs, steps, upload_in_loop):
-        loss = trace_c4(adb, dev, inputs, batch, widths, steps, upload_in_loop)
+        loss = trace_c4(adb, dev, inputs, batch, widths, steps, upload_in_loop, lb if world > 1 else None)
         barrier()
         t0 = time.perf_counter()
         adb.autodiff.execute()

@@ -1,0 +1,51 @@
+"""Data-parallel MLP training on 2 GPUs (one process per GPU, NCCL all-reduce of the gradients) against
+the same program on one GPU.  Skipped when fewer than two GPUs are visible."""
+import importlib
+import os
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+KW = dict(batch=256, widths=(64, 128, 128, 64, 16), steps=4, lr=1e-2)
+
+
+def _worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    adb = importlib.import_module("autodiff-ir-rust_b200")
+    box = [adb.devices.nccl_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    dev = adb.devices.B200(rank, rank=rank, world_size=world, nccl_unique_id=box[0], shard_batch=KW["batch"])
+    inputs = adb.configs.c4_inputs(batch=KW["batch"], widths=KW["widths"])     # full tensors: the device takes its rows
+    out = adb.configs.c4_mlp_train(dev, inputs=inputs, **KW)
+    np.savez(os.path.join(out_dir, f"rank{rank}.npz"), **{k: v.numpy() for k, v in out.items()})
+    dev.close()
+    dist.destroy_process_group()
+
+
+def test_two_gpus_match_one_gpu(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    adb = importlib.import_module("autodiff-ir-rust_b200")
+    port = 29600 + (os.getpid() % 2000)
+    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    dev = adb.devices.B200(0)
+    want = adb.configs.c4_mlp_train(dev, inputs=adb.configs.c4_inputs(batch=KW["batch"], widths=KW["widths"]), **KW)
+    dev.close()
+    for r in range(2):
+        got = np.load(tmp_path / f"rank{r}.npz")
+        for k, v in want.items():
+            ref = v.numpy()
+            err = np.abs(got[k] - ref).max() / max(np.abs(ref).max(), 1e-30)
+            assert err < 1e-4, (r, k, err)
