@@ -90,7 +90,7 @@ static NcclApi g_nccl;
 struct GraphSeg {
     size_t begin = 0, end = 0;       // [begin, end) steps of the block
     cudaGraphExec_t exec = nullptr;  // null: run the steps one by one
-    uint64_t launches = 0, gemms = 0;
+    uint64_t launches = 0, gemms = 0, tc = 0;
 };
 
 struct CompiledPlan {
@@ -296,10 +296,12 @@ class Executor {
             a.a_rs = g.a_rs; a.a_cs = g.a_cs; a.b_rs = g.b_rs; a.b_cs = g.b_cs;
             a.force_simt = (d_->flags & ADB_FLAG_SIMT_DOT) != 0;
             std::string e;
+            const unsigned long long tc0 = d_->gemm.tc_total;
             int n = gemm_launch(d_->gemm, a, d_->stream, e);
             if (n < 0) throw CudaFail{"gemm: " + e};
             launches_ += uint64_t(n);
             gemms_++;
+            tc_ += d_->gemm.tc_total - tc0;
             break;
         }
         case Step::UPLOAD: {
@@ -359,7 +361,7 @@ class Executor {
                 GraphSeg g;
                 g.begin = i;
                 g.end = j;
-                uint64_t l0 = launches_, g0 = gemms_;
+                uint64_t l0 = launches_, g0 = gemms_, t0 = tc_;
                 cudaGraph_t graph = nullptr;
                 ck(cudaStreamBeginCapture(d_->stream, cudaStreamCaptureModeThreadLocal), "begin capture");
                 capturing_ = true;
@@ -375,8 +377,10 @@ class Executor {
                 ck(cudaStreamEndCapture(d_->stream, &graph), "end capture");
                 g.launches = launches_ - l0;
                 g.gemms = gemms_ - g0;
+                g.tc = tc_ - t0;
                 launches_ = l0;
                 gemms_ = g0;
+                tc_ = t0;
                 ck(cudaGraphInstantiate(&g.exec, graph, 0), "graph instantiate");
                 cudaGraphDestroy(graph);
                 segs.push_back(g);
@@ -400,6 +404,7 @@ class Executor {
                     ck(cudaGraphLaunch(g.exec, d_->stream), "graph launch");
                     launches_ += g.launches;
                     gemms_ += g.gemms;
+                    tc_ += g.tc;
                     d_->stats.graph_replays++;
                 } else {
                     for (size_t t = g.begin; t < g.end; t++) {
@@ -459,7 +464,7 @@ class Executor {
         used_events_.clear();
     }
 
-    uint64_t launches_ = 0, gemms_ = 0;
+    uint64_t launches_ = 0, gemms_ = 0, tc_ = 0;
     bool capturing_ = false;
 
   private:
@@ -596,7 +601,6 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
     }
 
     Executor ex(d, cp);
-    const unsigned long long tc_before = d->gemm.tc_total;
     d->exit_requested = false;
     d->upload_events.clear();
     d->prof.clear();
@@ -627,6 +631,7 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
     }
     ck(cudaEventRecord(ev2, d->stream), "event record");
     ck(cudaStreamSynchronize(d->stream), "synchronize");
+    d->gemm.tc_launches = ex.tc_;  // graph replays launch the kernel without passing through gemm_launch
     if (int gs = gemm_check_status(d->gemm, d->stream)) {
         d->err = "tensor-core dot product gave up on a bounded wait (code " + std::to_string(gs) + "); results are invalid";
         ex.release_events();
@@ -646,7 +651,7 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
     d->stats.readback_ms = ms_rb;
     d->stats.kernel_launches = ex.launches_;
     d->stats.gemm_launches = ex.gemms_;
-    d->stats.tc_gemm_launches = d->gemm.tc_total - tc_before;
+    d->stats.tc_gemm_launches = ex.tc_;
     if (!d->prof.empty()) {
         std::map<int, std::pair<double, std::pair<double, uint64_t>>> per_kernel;  // kernel -> (ms, (bytes, launches))
         for (auto& r : d->prof) {
