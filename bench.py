@@ -236,6 +236,10 @@ def run_ours(args):
                      "avg_ms": st["gemm_ms"] / max(1, st["gemm_launches"])},
         "breakdown_ms_per_step": {"gemm": st["gemm_ms"] / K, "elementwise": st["elw_ms"] / K, "reduce": st["reduce_ms"] / K,
                                   "allreduce": st["collective_ms"] / K},
+        # the HBM-bound kernels of the same timed region: fused bias + sigmoid chains, sigmoid backward, SGD updates
+        "elementwise_in_step": {"bound": "hbm", "achieved": st["elw_bytes"] / max(st["elw_ms"], 1e-9) / 1e6, "peak": pk["hbm_gbs"],
+                                "unit": "GB/s", "frac": st["elw_bytes"] / max(st["elw_ms"], 1e-9) / 1e6 / pk["hbm_gbs"],
+                                "launches": int(st["elw_launches"]), "peak_note": "copy bandwidth of " + pk["source"]},
     }
     if world == 1 and rank == 0 and not args.skip_extras:
         line["fused_elw"] = bench_c2(adb, dev, pk, args)
@@ -273,7 +277,10 @@ def bench_c2(adb, dev, pk, args):
             "ms": best["device_ms"], "algorithmic_bytes": algorithmic, "algorithmic_GBps": achieved,
             "frac_of_hbm_peak": achieved / pk["hbm_gbs"], "kernels": int(best["kernel_launches"]),
             "roofline": {"bound": "hbm", "kernel": best["top_name"], "achieved": top, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                         "frac": top / pk["hbm_gbs"], "traffic": None, "launches": int(best["top_launches"]),
+                         "frac": top / pk["hbm_gbs"],
+                         # dram__bytes_read + dram__bytes_write of this kernel at this size, from the ncu capture summarised in
+                         # profiles/c2_fused_elementwise_8192.md (one launch)
+                         "traffic": 1030936832 if rows == 8192 else None, "launches": int(best["top_launches"]),
                          "peak_note": "copy bandwidth of " + pk["source"]}}
 
 
