@@ -287,6 +287,7 @@ void gen_reduce(KernelSpec& k) {
             xo[i] = "o" + tag;
             seenx.push_back({k.ins[i].xsubs, xo[i]});
         }
+        o << "#pragma unroll 4\n";
         o << "      for (" << idx_t << " y = ybeg + lane * " << vec << "u; y < yend; y += " << TPR * vec << "u) {\n";
         std::vector<std::string> off(k.ins.size());
         for (size_t i = 0; i < k.ins.size(); i++) {
@@ -364,6 +365,7 @@ void gen_reduce(KernelSpec& k) {
             xo[i] = "o" + tag;
             seenx.push_back({k.ins[i].xsubs, xo[i]});
         }
+        o << "#pragma unroll 4\n";
         o << "    for (" << idx_t << " y = ybeg + ty; y < yend; y += 8u) {\n";
         std::vector<std::string> off(k.ins.size());
         for (size_t i = 0; i < k.ins.size(); i++) {
@@ -432,7 +434,8 @@ void plan_reduce(KernelSpec& k, int sm_count) {
             if (!lanes_ok(in.subs)) vec = 1;
         k.vec = vec;
         int64_t per_row = std::max<int64_t>(1, R / vec);
-        int64_t tpr = std::min<int64_t>(256, pow2_floor(std::max<int64_t>(1, per_row / 4)));
+        // up to a warp per row needs no shared memory and no block barrier; only very long rows get a block
+        int64_t tpr = per_row >= 4096 ? 256 : std::min<int64_t>(32, pow2_floor(std::max<int64_t>(1, per_row / 2)));
         k.threads = int(tpr);
         int64_t blocks = (V + (256 / tpr) - 1) / (256 / tpr);
         k.split = 1;

@@ -98,6 +98,8 @@ struct CompiledPlan {
     std::vector<int> kernel_slot;  // plan kernel -> device kernel cache slot
     std::map<const StepBlock*, std::vector<GraphSeg>> graphs;
     uint64_t graph_epoch = 0;      // arena generation + external addresses the graphs were captured with
+    uint64_t runs = 0;             // completed executions of this plan
+    bool top_level_graphs = false; // straight-line top-level code is replayed as graphs (addresses were stable)
     double lower_ms = 0;
 };
 
@@ -397,7 +399,9 @@ class Executor {
     }
 
     void run_block(const StepBlock& blk, bool in_loop) {
-        if (in_loop) {
+        // loop bodies always replay graphs; straight-line top-level code does so once a cached plan is
+        // executed again with unchanged buffer addresses (otherwise capture would cost more than it saves)
+        if (in_loop || cp_->top_level_graphs) {
             auto& segs = segments(blk);
             for (auto& g : segs) {
                 if (g.exec) {
@@ -408,7 +412,7 @@ class Executor {
                     d_->stats.graph_replays++;
                 } else {
                     for (size_t t = g.begin; t < g.end; t++) {
-                        run_one(blk.steps[t], true);
+                        run_one(blk.steps[t], in_loop);
                         if (d_->exit_requested) return;
                     }
                 }
@@ -595,6 +599,8 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
         if (b.external) epoch = fnv_bytes(&plan.payloads[b.payload].addr, 8, epoch);
     for (auto& p : plan.payloads)
         if (p.kind == PAYLOAD_DEVICE) epoch = fnv_bytes(&p.addr, 8, epoch);
+    // top-level code is only worth capturing when the same addresses come back run after run
+    cp->top_level_graphs = cp->runs > 0 && cp->graph_epoch == epoch;
     if (cp->graph_epoch != epoch) {
         destroy_graphs(*cp);
         cp->graph_epoch = epoch;
@@ -649,6 +655,7 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
     d->stats.upload_ms = up;
     d->stats.device_ms = std::max(0.0, double(ms_run) - up);
     d->stats.readback_ms = ms_rb;
+    cp->runs++;
     d->stats.kernel_launches = ex.launches_;
     d->stats.gemm_launches = ex.gemms_;
     d->stats.tc_gemm_launches = ex.tc_;

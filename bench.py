@@ -262,13 +262,26 @@ def bench_c2(adb, dev, pk, args):
     bias = torch.rand(cols, device="cuda", generator=g) * 2 - 1
     DP = adb.ir.DevicePayload
     inp = {"a": DP(a.data_ptr(), a.numel(), a), "b": DP(b.data_ptr(), b.numel(), b), "bias": DP(bias.data_ptr(), bias.numel(), bias)}
+    # whole-program time on a handle without per-kernel events (cached plan -> one CUDA-graph replay);
+    # per-kernel figures from the profiling handle
+    plain = adb.devices.B200(0)
     best = None
-    for it in range(6):
+    for it in range(7):
+        cfg.c2_fused_elementwise(plain, rows=rows, cols=cols, inputs=inp, execute=False)
+        adb.autodiff.execute()
+        st = plain.stats()
+        if it >= 3 and (best is None or st["device_ms"] < best["device_ms"]):
+            best = st
+    plain.close()
+    prof = None
+    for it in range(3):
         cfg.c2_fused_elementwise(dev, rows=rows, cols=cols, inputs=inp, execute=False)
         adb.autodiff.execute()
         st = dev.stats()
-        if it >= 3 and (best is None or st["device_ms"] < best["device_ms"]):
-            best = st
+        if prof is None or st["top_ms"] < prof["top_ms"]:
+            prof = st
+    for k in ("top_ms", "top_bytes", "top_name", "top_launches"):
+        best[k] = prof[k]
     n = rows * cols
     algorithmic = 4.0 * n * 4  # read a, b once; write a.grad, b.grad once
     achieved = algorithmic / (best["device_ms"] / 1e3) / 1e9
@@ -327,7 +340,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--c2-size", type=int, default=8192)
-    ap.add_argument("--cpu-sample-batch", type=int, default=128)
+    ap.add_argument("--cpu-sample-batch", type=int, default=512)
     ap.add_argument("--skip-extras", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":

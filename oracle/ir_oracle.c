@@ -245,12 +245,55 @@ static void propagate_alias(Oracle *o, Proc *p) {
     }
 }
 
+/* ------------------------------------------------------------------ buffer pool
+ * Large arrays come and go with every command; recycling them avoids the page-fault cost of fresh
+ * mappings (this only affects speed of the CPU baseline, never values). */
+#define POOL_SLOTS 96
+static struct { float *p; size_t cap; } g_pool[POOL_SLOTS];
+static size_t g_pool_bytes = 0;
+
+static float *pool_alloc(size_t n) {
+    if (n == 0) n = 1;
+    int best = -1;
+#pragma omp critical(adb_pool)
+    {
+        for (int i = 0; i < POOL_SLOTS; i++)
+            if (g_pool[i].p && g_pool[i].cap >= n && g_pool[i].cap <= 2 * n + 1024 && (best < 0 || g_pool[i].cap < g_pool[best].cap)) best = i;
+    }
+    if (best >= 0) {
+        float *p = g_pool[best].p;
+        g_pool_bytes -= g_pool[best].cap * sizeof(float);
+        g_pool[best].p = NULL;
+        /* remember the capacity in a header word in front of the array */
+        return p;
+    }
+    size_t *raw = malloc(sizeof(float) * n + 64);
+    raw[0] = n;
+    return (float *)((char *)raw + 64);
+}
+
+static void pool_free(float *p) {
+    if (!p) return;
+    size_t *raw = (size_t *)((char *)p - 64);
+    size_t cap = raw[0];
+    if (cap >= (1u << 16) && g_pool_bytes + cap * sizeof(float) < ((size_t)12 << 30)) {
+        for (int i = 0; i < POOL_SLOTS; i++)
+            if (!g_pool[i].p) {
+                g_pool[i].p = p;
+                g_pool[i].cap = cap;
+                g_pool_bytes += cap * sizeof(float);
+                return;
+            }
+    }
+    free(raw);
+}
+
 /* ------------------------------------------------------------------ helpers */
 static uint64_t numel(const Var *v) { uint64_t n = 1; for (int i = 0; i < v->nd; i++) n *= v->dims[i]; return n; }
 static uint64_t numel_d(const uint64_t *d, int nd) { uint64_t n = 1; for (int i = 0; i < nd; i++) n *= d[i]; return n; }
 
 static void var_release(Var *v) {
-    if (v->kind == K_BUF && v->data && !v->borrowed) free(v->data);
+    if (v->kind == K_BUF && v->data && !v->borrowed) pool_free(v->data);
     v->data = NULL; v->borrowed = 0;
 }
 
@@ -305,13 +348,37 @@ static float *materialize(const Oracle *o, uint32_t id, int *owned) {
     const Var *v = &o->vars[id];
     uint64_t n = numel(v);
     if (v->kind == K_BUF) { *owned = 0; return v->data; }
-    float *out = malloc(sizeof(float) * (size_t)(n ? n : 1));
+    float *out = pool_alloc((size_t)n);
     *owned = 1;
     if (v->kind == K_CONST) {
         float c = v->cval;
 #pragma omp parallel for schedule(static) if (n > 65536)
         for (uint64_t i = 0; i < n; i++) out[i] = c;
         return out;
+    }
+    /* common aliases get direct loops (same values as the generic path below, only faster) */
+    if (v->kind == K_ALIAS && v->acmd == A_PERMUTE && v->nd == 2 && v->perm[0] == 1 && v->perm[1] == 0 &&
+        o->vars[v->parent].kind == K_BUF) {
+        const float *src = o->vars[v->parent].data;
+        const uint64_t R = v->dims[0], C = v->dims[1]; /* out[r][c] = src[c][r], src is [C][R] */
+#pragma omp parallel for schedule(static) collapse(2) if (n > 16384)
+        for (uint64_t rb = 0; rb < R; rb += 32)
+            for (uint64_t cb = 0; cb < C; cb += 32)
+                for (uint64_t r = rb; r < rb + 32 && r < R; r++)
+                    for (uint64_t c = cb; c < cb + 32 && c < C; c++) out[r * C + c] = src[c * R + r];
+        return out;
+    }
+    if (v->kind == K_ALIAS && v->acmd == A_BROADCAST && v->nd == 2 && v->adim == 0) {
+        const Var *p = &o->vars[v->parent];
+        const float *row = NULL;
+        if (p->kind == K_BUF) row = p->data;
+        else if (p->kind == K_ALIAS && p->acmd == A_VIEW && o->vars[p->parent].kind == K_BUF) row = o->vars[p->parent].data;
+        if (row) {
+            const uint64_t R = v->dims[0], C = v->dims[1];
+#pragma omp parallel for schedule(static) if (n > 16384)
+            for (uint64_t r = 0; r < R; r++) memcpy(out + r * C, row, sizeof(float) * (size_t)C);
+            return out;
+        }
     }
     int nd = v->nd;
 #pragma omp parallel for schedule(static) if (n > 16384)
@@ -351,7 +418,7 @@ static int exec_cmd(Oracle *o, Cmd *c) {
     case 1: { /* CreateMat: (re)upload every time it is executed (alloc.rs:5-12) */
         uint64_t n = numel_d(c->dims, c->nd);
         if (n != c->count) { snprintf(o->err, sizeof o->err, "oracle: CreateMat '%s' size mismatch", o->names[c->res]); return -1; }
-        float *d = malloc(sizeof(float) * (size_t)(n ? n : 1));
+        float *d = pool_alloc((size_t)n);
         memcpy(d, c->payload, sizeof(float) * (size_t)n);
         bind_buf(o, c->res, d, c->dims, c->nd);
         return 0;
@@ -372,19 +439,36 @@ static int exec_cmd(Oracle *o, Cmd *c) {
         if (numel(&V[c->b]) != n && V[c->b].kind != K_CONST) {
             snprintf(o->err, sizeof o->err, "oracle: elementwise size mismatch %s vs %s", o->names[c->a], o->names[c->b]); return -1;
         }
-        int oa, ob;
-        float *a = materialize(o, c->a, &oa);
-        float *b = materialize(o, c->b, &ob);
-        float *out = malloc(sizeof(float) * (size_t)(n ? n : 1));
-        if (c->op == 3 || c->op == 5) {
+        int oa = 0, ob = 0;
+        /* a scalar constant is applied directly instead of being expanded to an array first */
+        const int ca = V[c->a].kind == K_CONST, cb = V[c->b].kind == K_CONST;
+        const float sa = V[c->a].cval, sb = V[c->b].cval;
+        float *a = ca ? NULL : materialize(o, c->a, &oa);
+        float *b = cb ? NULL : materialize(o, c->b, &ob);
+        float *out = pool_alloc((size_t)n);
+        const int mul = (c->op == 3 || c->op == 5);
+        if (ca && cb) {
+            const float r = mul ? sa * sb : sa + sb;
+            for (uint64_t i = 0; i < n; i++) out[i] = r;
+        } else if (ca || cb) {
+            const float *x = ca ? b : a;
+            const float k = ca ? sa : sb;
+            if (mul) {
+#pragma omp parallel for schedule(static) if (n > 65536)
+                for (uint64_t i = 0; i < n; i++) out[i] = ca ? k * x[i] : x[i] * k;
+            } else {
+#pragma omp parallel for schedule(static) if (n > 65536)
+                for (uint64_t i = 0; i < n; i++) out[i] = ca ? k + x[i] : x[i] + k;
+            }
+        } else if (mul) {
 #pragma omp parallel for schedule(static) if (n > 65536)
             for (uint64_t i = 0; i < n; i++) out[i] = a[i] * b[i];
         } else {
 #pragma omp parallel for schedule(static) if (n > 65536)
             for (uint64_t i = 0; i < n; i++) out[i] = a[i] + b[i];
         }
-        if (oa) free(a);
-        if (ob) free(b);
+        if (oa) pool_free(a);
+        if (ob) pool_free(b);
         bind_buf(o, c->res, out, dims, nd);
         return 0;
     }
@@ -396,7 +480,7 @@ static int exec_cmd(Oracle *o, Cmd *c) {
         memcpy(dims, va->dims, sizeof dims);
         int oa;
         float *a = materialize(o, c->a, &oa);
-        float *out = malloc(sizeof(float) * (size_t)(n ? n : 1));
+        float *out = pool_alloc((size_t)n);
         switch (c->op) {
 #define LOOP(expr) _Pragma("omp parallel for schedule(static) if (n > 32768)") for (uint64_t i = 0; i < n; i++) { float x = a[i]; out[i] = (expr); }
         case 7: LOOP(x == 0.0f ? 1.0f : 0.0f) break;
@@ -410,7 +494,7 @@ static int exec_cmd(Oracle *o, Cmd *c) {
         case 22: LOOP(sqrtf(fabsf(x))) break;
 #undef LOOP
         }
-        if (oa) free(a);
+        if (oa) pool_free(a);
         bind_buf(o, c->res, out, dims, nd);
         return 0;
     }
@@ -421,7 +505,7 @@ static int exec_cmd(Oracle *o, Cmd *c) {
         uint64_t vs = va->dims[0], rs = va->dims[1];
         int oa;
         float *a = materialize(o, c->a, &oa);
-        float *out = malloc(sizeof(float) * (size_t)(vs ? vs : 1));
+        float *out = pool_alloc((size_t)vs);
         int f64 = o->f64_acc;
 #pragma omp parallel for schedule(static) if (vs * rs > 65536)
         for (uint64_t x = 0; x < vs; x++) {
@@ -429,7 +513,7 @@ static int exec_cmd(Oracle *o, Cmd *c) {
             if (f64) { double s = 0; for (uint64_t y = 0; y < rs; y++) s += row[y]; out[x] = (float)s; }
             else { float s = 0; for (uint64_t y = 0; y < rs; y++) s += row[y]; out[x] = s; }
         }
-        if (oa) free(a);
+        if (oa) pool_free(a);
         uint64_t dims[1] = { vs };
         bind_buf(o, c->res, out, dims, 1);
         return 0;
@@ -444,7 +528,9 @@ static int exec_cmd(Oracle *o, Cmd *c) {
         int oa, ob;
         float *a = materialize(o, c->a, &oa);
         float *b = materialize(o, c->b, &ob);
-        float *out = calloc((size_t)((M * N) != 0 ? M * N : 1), sizeof(float));
+        float *out = pool_alloc((size_t)(M * N));
+#pragma omp parallel for schedule(static) if (M * N > 65536)
+        for (uint64_t i = 0; i < M * N; i++) out[i] = 0.0f;
         int f64 = o->f64_acc;
         if (f64) {
 #pragma omp parallel for schedule(static)
@@ -455,19 +541,28 @@ static int exec_cmd(Oracle *o, Cmd *c) {
                 free(acc);
             }
         } else {
-            /* i-k-j order: every out[i][j] still accumulates in ascending k */
-#pragma omp parallel for schedule(static)
-            for (uint64_t i = 0; i < M; i++) {
-                float *cr = out + i * N;
-                for (uint64_t k = 0; k < K; k++) {
-                    float av = a[i * K + k];
-                    const float *br = b + k * N;
-                    for (uint64_t j = 0; j < N; j++) cr[j] += av * br[j];
+            /* tiles of 8 rows x 512 columns; inside a tile k runs outermost, so every out[i][j] still
+             * accumulates its products in ascending k (the reference's order), while a row of B is
+             * reused by the 8 rows of the tile instead of being streamed from memory for each of them */
+            const uint64_t TI = 8, TJ = 512;
+            const uint64_t nti = (M + TI - 1) / TI, ntj = (N + TJ - 1) / TJ;
+#pragma omp parallel for schedule(dynamic, 1) collapse(2)
+            for (uint64_t ti = 0; ti < nti; ti++)
+                for (uint64_t tj = 0; tj < ntj; tj++) {
+                    const uint64_t i0 = ti * TI, i1 = i0 + TI < M ? i0 + TI : M;
+                    const uint64_t j0 = tj * TJ, j1 = j0 + TJ < N ? j0 + TJ : N;
+                    for (uint64_t k = 0; k < K; k++) {
+                        const float *br = b + k * N;
+                        for (uint64_t i = i0; i < i1; i++) {
+                            const float av = a[i * K + k];
+                            float *cr = out + i * N;
+                            for (uint64_t j = j0; j < j1; j++) cr[j] += av * br[j];
+                        }
+                    }
                 }
-            }
         }
-        if (oa) free(a);
-        if (ob) free(b);
+        if (oa) pool_free(a);
+        if (ob) pool_free(b);
         uint64_t dims[2] = { M, N };
         bind_buf(o, c->res, out, dims, 2);
         return 0;
@@ -648,7 +743,7 @@ int oracle_execute(void *h, const uint8_t *blob, size_t nbytes) {
         uint64_t n = numel(v);
         float *copy = malloc(sizeof(float) * (size_t)(n ? n : 1));
         memcpy(copy, d, sizeof(float) * (size_t)n);
-        if (owned) free(d);
+        if (owned) pool_free(d);
         uint32_t k = o->n_res++;
         o->res_names[k] = strdup(o->names[id]);
         o->res_data[k] = copy;
