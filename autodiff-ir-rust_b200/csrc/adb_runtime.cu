@@ -93,8 +93,19 @@ struct GraphSeg {
     uint64_t launches = 0, gemms = 0, tc = 0;
 };
 
+// Double-buffered staging for a host payload that a loop body uploads every iteration: the copy for
+// the next iteration runs on the copy stream while the current iteration computes.
+struct Prefetch {
+    void* stage[2] = {nullptr, nullptr};
+    cudaEvent_t ready[2] = {nullptr, nullptr};  // H2D into stage[b] finished
+    cudaEvent_t freed[2] = {nullptr, nullptr};  // the compute stream has consumed stage[b]
+    bool freed_valid[2] = {false, false};
+    size_t bytes = 0;
+};
+
 struct CompiledPlan {
     Plan plan;
+    std::map<const Step*, Prefetch> prefetch;
     std::vector<int> kernel_slot;  // plan kernel -> device kernel cache slot
     std::map<const StepBlock*, std::vector<GraphSeg>> graphs;
     uint64_t graph_epoch = 0;      // arena generation + external addresses the graphs were captured with
@@ -114,6 +125,7 @@ struct adb_device {
     uint64_t shard_batch = 0;
     int sm_count = 148;
     cudaStream_t stream = nullptr;
+    cudaStream_t copy_stream = nullptr;  // host->device prefetch of in-loop payloads
     std::string err;
     // kernels compiled so far, by entry name
     std::unordered_map<std::string, int> kernel_index;
@@ -310,7 +322,21 @@ class Executor {
             const PayloadSlot& p = plan_.payloads[s.payload];
             cudaEvent_t e0 = event(), e1 = event();
             ck(cudaEventRecord(e0, d_->stream), "event");
-            if (p.kind == PAYLOAD_DEVICE) {
+            auto pf = cp_->prefetch.find(&s);
+            if (pf != cp_->prefetch.end() && loop_depth_ > 0) {
+                // the batch for this iteration was copied ahead of time; start the copy for the next one
+                Prefetch& f = pf->second;
+                const int b = int(loop_iter_ & 1);
+                const void* src = reinterpret_cast<const void*>(uintptr_t(p.addr));
+                ck(cudaStreamWaitEvent(d_->stream, f.ready[b], 0), "wait prefetch");
+                ck(cudaMemcpyAsync(buf_ptr(s.buf), f.stage[b], f.bytes, cudaMemcpyDeviceToDevice, d_->stream), "upload (staged)");
+                ck(cudaEventRecord(f.freed[b], d_->stream), "event");
+                f.freed_valid[b] = true;
+                if (f.freed_valid[b ^ 1]) ck(cudaStreamWaitEvent(d_->copy_stream, f.freed[b ^ 1], 0), "wait stage free");
+                ck(cudaMemcpyAsync(f.stage[b ^ 1], src, f.bytes, cudaMemcpyHostToDevice, d_->copy_stream), "prefetch (host)");
+                ck(cudaEventRecord(f.ready[b ^ 1], d_->copy_stream), "event");
+                d_->stats.h2d_bytes += f.bytes;
+            } else if (p.kind == PAYLOAD_DEVICE) {
                 ck(cudaMemcpyAsync(buf_ptr(s.buf), reinterpret_cast<const void*>(uintptr_t(p.addr)), size_t(s.nelem) * 4,
                                    cudaMemcpyDeviceToDevice, d_->stream), "upload (device)");
             } else {
@@ -333,6 +359,55 @@ class Executor {
         }
         default: break;
         }
+    }
+
+    // Pinned host payloads (>= 1 MiB) that the body of an outermost loop uploads on every iteration get
+    // two staging buffers; the first copy is issued here, before the first iteration.
+    std::vector<Prefetch*> start_prefetch(const StepBlock& body) {
+        std::vector<Prefetch*> active;
+        for (auto& st : body.steps) {
+            if (st.kind != Step::UPLOAD) continue;
+            const PayloadSlot& p = plan_.payloads[st.payload];
+            const size_t bytes = size_t(st.nelem) * 4;
+            if (p.kind == PAYLOAD_DEVICE || bytes < (size_t(1) << 20)) continue;
+            cudaPointerAttributes attr;
+            if (cudaPointerGetAttributes(&attr, reinterpret_cast<const void*>(uintptr_t(p.addr))) != cudaSuccess ||
+                attr.type != cudaMemoryTypeHost) {
+                cudaGetLastError();
+                cp_->prefetch.erase(&st);  // pageable memory cannot be copied asynchronously
+                continue;
+            }
+            Prefetch& f = cp_->prefetch[&st];
+            if (f.bytes != bytes) {
+                for (int b = 0; b < 2; b++) {
+                    if (f.stage[b]) cudaFree(f.stage[b]);
+                    f.stage[b] = nullptr;
+                    if (cudaMalloc(&f.stage[b], bytes) != cudaSuccess) {
+                        cudaGetLastError();
+                        if (b == 1) cudaFree(f.stage[0]);
+                        cp_->prefetch.erase(&st);
+                        goto next;
+                    }
+                    if (!f.ready[b]) ck(cudaEventCreateWithFlags(&f.ready[b], cudaEventDisableTiming), "event create");
+                    if (!f.freed[b]) ck(cudaEventCreateWithFlags(&f.freed[b], cudaEventDisableTiming), "event create");
+                }
+                f.bytes = bytes;
+            }
+            {
+                // copies of an earlier execute may still own the staging buffers: order behind the compute stream
+                cudaEvent_t here = event();
+                ck(cudaEventRecord(here, d_->stream), "event");
+                ck(cudaStreamWaitEvent(d_->copy_stream, here, 0), "order copy stream");
+                f.freed_valid[0] = f.freed_valid[1] = false;
+                ck(cudaMemcpyAsync(f.stage[0], reinterpret_cast<const void*>(uintptr_t(p.addr)), bytes, cudaMemcpyHostToDevice,
+                                   d_->copy_stream), "prefetch (host)");
+                ck(cudaEventRecord(f.ready[0], d_->copy_stream), "event");
+                d_->stats.h2d_bytes += bytes;
+                active.push_back(&f);
+            }
+        next:;
+        }
+        return active;
     }
 
     float read_cond(int buf, int64_t off) {
@@ -427,14 +502,26 @@ class Executor {
 
     void run_one(const Step& s, bool in_loop) {
         switch (s.kind) {
-        case Step::WHILE:
+        case Step::WHILE: {
             // `while (cond[0] != 0.0)`: src/devices/opencl/device.rs:132-137
-            while (read_cond(s.cond_buf, s.cond_off) != 0.0f) {
+            if (read_cond(s.cond_buf, s.cond_off) == 0.0f) break;
+            std::vector<Prefetch*> active;
+            if (loop_depth_ == 0) active = start_prefetch(*s.body);
+            const uint64_t saved_iter = loop_iter_;
+            loop_depth_++;
+            loop_iter_ = 0;
+            do {
                 run_block(*s.body, true);
                 d_->stats.while_iterations++;
-                if (d_->exit_requested) return;
-            }
+                loop_iter_++;
+                if (d_->exit_requested) break;
+            } while (read_cond(s.cond_buf, s.cond_off) != 0.0f);
+            loop_depth_--;
+            // the copy issued for the iteration that never came must land before its buffers are reused
+            for (auto* f : active) ck(cudaStreamWaitEvent(d_->stream, f->ready[loop_iter_ & 1], 0), "drain prefetch");
+            loop_iter_ = saved_iter;
             break;
+        }
         case Step::IF: {
             // first condition equal to 1.0 wins, else the else-block: src/devices/opencl/device.rs:118-131
             bool taken = false;
@@ -470,6 +557,8 @@ class Executor {
 
     uint64_t launches_ = 0, gemms_ = 0, tc_ = 0;
     bool capturing_ = false;
+    int loop_depth_ = 0;
+    uint64_t loop_iter_ = 0;
 
   private:
     adb_device* d_;
@@ -477,6 +566,16 @@ class Executor {
     Plan& plan_;
     std::vector<cudaEvent_t> used_events_;
 };
+
+void destroy_prefetch(CompiledPlan& cp) {
+    for (auto& kv : cp.prefetch)
+        for (int b = 0; b < 2; b++) {
+            if (kv.second.stage[b]) cudaFree(kv.second.stage[b]);
+            if (kv.second.ready[b]) cudaEventDestroy(kv.second.ready[b]);
+            if (kv.second.freed[b]) cudaEventDestroy(kv.second.freed[b]);
+        }
+    cp.prefetch.clear();
+}
 
 void destroy_graphs(CompiledPlan& cp) {
     for (auto& kv : cp.graphs)
@@ -551,6 +650,7 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
         }
         if (!ok) {
             destroy_graphs(*cp);
+            destroy_prefetch(*cp);
             d->plans.erase(it);
             cp = nullptr;
         }
@@ -727,6 +827,7 @@ adb_status adb_create(const adb_config* cfg, adb_device** out) {
             return ADB_ERR_UNSUPPORTED;
         }
         ck(cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking), "cudaStreamCreate");
+        ck(cudaStreamCreateWithFlags(&d->copy_stream, cudaStreamNonBlocking), "cudaStreamCreate");
         ck(cudaMallocHost(&d->cond_host, 64), "cudaMallocHost");
         std::string gerr;
         if (!gemm_init(d->gemm, d->sm_count, gerr)) throw CudaFail{gerr};
@@ -751,7 +852,8 @@ void adb_destroy(adb_device* d) {
     if (!d) return;
     cudaSetDevice(d->ordinal);
     if (d->stream) cudaStreamSynchronize(d->stream);
-    for (auto& kv : d->plans) destroy_graphs(*kv.second);
+    if (d->copy_stream) cudaStreamSynchronize(d->copy_stream);
+    for (auto& kv : d->plans) { destroy_graphs(*kv.second); destroy_prefetch(*kv.second); }
     d->plans.clear();
     for (auto& k : d->kernels)
         if (k.lib) cudaLibraryUnload(k.lib);
@@ -763,6 +865,7 @@ void adb_destroy(adb_device* d) {
     if (d->nccl_comm && g_nccl.CommDestroy) g_nccl.CommDestroy(d->nccl_comm);
     if (d->arena) cudaFree(d->arena);
     if (d->cond_host) cudaFreeHost(d->cond_host);
+    if (d->copy_stream) cudaStreamDestroy(d->copy_stream);
     if (d->stream) cudaStreamDestroy(d->stream);
     delete d;
 }

@@ -245,3 +245,29 @@ def test_malformed_blob_is_rejected_without_killing_the_context():
     y.val().keep()
     ad.execute()
     np.testing.assert_array_equal(y.val().get().data, [2.0, 3.0])
+
+
+def test_pinned_payload_uploaded_inside_a_loop_is_prefetched_correctly():
+    """A CreateMat inside a loop body re-uploads on every iteration (src/devices/opencl/kernels/alloc.rs:5-12);
+    from pinned memory the backend double-buffers that copy on a second stream."""
+    import torch
+    n = 512 * 1024                      # 2 MiB: above the prefetch threshold
+    host = torch.empty(n, pin_memory=True)
+    host.copy_(torch.from_numpy(rnd(n)))
+    data = host.numpy()
+
+    def prog(dev):
+        ad.set_device(dev)
+        acc = ad.tensor(np.zeros(n, np.float32), [512, 1024])
+
+        def body(i):
+            nonlocal acc
+            x = ad.tensor(data, [512, 1024])
+            acc += x * (i.clone() + 1.0).broadcast(0, 512 * 1024).view([512, 1024])
+            acc.forward()
+        ad.ir_for(range(0, 5), body)
+        ad.execute()
+        return {"acc": acc.val().get()}
+    want, got = run_both(prog)
+    assert_exact("acc", got["acc"], want["acc"])
+    assert b200().stats()["h2d_bytes"] >= 5 * n * 4
