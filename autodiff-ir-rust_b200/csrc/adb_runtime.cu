@@ -103,9 +103,26 @@ struct Prefetch {
     size_t bytes = 0;
 };
 
+// Where a step of a straight-line range runs and what it has to wait for.  Collectives and the
+// element-wise kernel that produces their operand run on the communication stream so that they overlap
+// with the dot products that follow them in program order.
+struct StepSched {
+    bool on_comm = false;
+    int wait_main = -1;   // (comm step) index of the last earlier main-stream step touching one of its buffers
+    int wait_comm = -1;   // (main step) index of the last earlier comm-stream step touching one of its buffers
+    bool record_after = false;
+    cudaEvent_t done = nullptr;
+};
+struct RangeSched {
+    std::vector<StepSched> steps;
+    bool any_comm = false;
+    cudaEvent_t fork = nullptr;
+};
+
 struct CompiledPlan {
     Plan plan;
     std::map<const Step*, Prefetch> prefetch;
+    std::map<std::pair<const StepBlock*, size_t>, RangeSched> sched;  // keyed by (block, first step of the range)
     std::vector<int> kernel_slot;  // plan kernel -> device kernel cache slot
     std::map<const StepBlock*, std::vector<GraphSeg>> graphs;
     uint64_t graph_epoch = 0;      // arena generation + external addresses the graphs were captured with
@@ -126,6 +143,7 @@ struct adb_device {
     int sm_count = 148;
     cudaStream_t stream = nullptr;
     cudaStream_t copy_stream = nullptr;  // host->device prefetch of in-loop payloads
+    cudaStream_t comm_stream = nullptr;  // collectives (and the small kernels that feed them), high priority
     std::string err;
     // kernels compiled so far, by entry name
     std::unordered_map<std::string, int> kernel_index;
@@ -229,7 +247,7 @@ bool payload_uniform(const float* p, int64_t n, float v) {
 
 class Executor {
   public:
-    Executor(adb_device* d, CompiledPlan* cp) : d_(d), cp_(cp), plan_(cp->plan) {}
+    Executor(adb_device* d, CompiledPlan* cp) : d_(d), cp_(cp), plan_(cp->plan) { cur_stream_ = d->stream; }
 
     float* buf_ptr(int buf, int64_t elem_off = 0) {
         const BufferInfo& b = plan_.bufs[buf];
@@ -261,7 +279,7 @@ class Executor {
             grid.y = unsigned(k.split);
         }
         void* params[1] = {args.data()};
-        ck(cudaLaunchKernel((const void*)d_->kernels[slot].fn, grid, block, params, 0, d_->stream), k.entry.c_str());
+        ck(cudaLaunchKernel((const void*)d_->kernels[slot].fn, grid, block, params, 0, cur_stream_), k.entry.c_str());
         launches_++;
     }
 
@@ -291,9 +309,9 @@ class Executor {
         r.work = s.kind == Step::GEMM ? 2.0 * double(s.gemm.M) * double(s.gemm.N) * double(s.gemm.K)
                : s.kind == Step::ALLREDUCE ? 4.0 * double(s.nelem)
                : kernel_bytes(plan_.kernels[s.kernel]);
-        ck(cudaEventRecord(r.e0, d_->stream), "event");
+        ck(cudaEventRecord(r.e0, cur_stream_), "event");
         run_step_impl(s);
-        ck(cudaEventRecord(r.e1, d_->stream), "event");
+        ck(cudaEventRecord(r.e1, cur_stream_), "event");
         d_->prof.push_back(r);
     }
 
@@ -311,7 +329,7 @@ class Executor {
             a.force_simt = (d_->flags & ADB_FLAG_SIMT_DOT) != 0;
             std::string e;
             const unsigned long long tc0 = d_->gemm.tc_total;
-            int n = gemm_launch(d_->gemm, a, d_->stream, e);
+            int n = gemm_launch(d_->gemm, a, cur_stream_, e);
             if (n < 0) throw CudaFail{"gemm: " + e};
             launches_ += uint64_t(n);
             gemms_++;
@@ -351,7 +369,7 @@ class Executor {
         case Step::ALLREDUCE: {
             if (d_->world > 1) {
                 float* p = buf_ptr(s.buf, s.off);
-                ncclResult_t rc = g_nccl.AllReduce(p, p, size_t(s.nelem), ncclFloat32, ncclSum, d_->nccl_comm, d_->stream);
+                ncclResult_t rc = g_nccl.AllReduce(p, p, size_t(s.nelem), ncclFloat32, ncclSum, d_->nccl_comm, cur_stream_);
                 if (rc != ncclSuccess) throw CudaFail{std::string("ncclAllReduce: ") + (g_nccl.GetErrorString ? g_nccl.GetErrorString(rc) : "error")};
                 launches_++;
             }
@@ -417,6 +435,102 @@ class Executor {
         return *d_->cond_host;
     }
 
+    void step_buffers(const Step& s, std::vector<int>& bufs) const {
+        bufs.clear();
+        switch (s.kind) {
+        case Step::ELW: case Step::REDUCE: {
+            const KernelSpec& k = plan_.kernels[s.kernel];
+            for (auto& in : k.ins) bufs.push_back(in.buf);
+            for (auto& o : k.outs) bufs.push_back(o.dst.buf);
+            break;
+        }
+        case Step::GEMM: bufs = {s.gemm.a, s.gemm.b, s.gemm.c}; break;
+        case Step::UPLOAD: case Step::ALLREDUCE: bufs = {s.buf}; break;
+        default: break;
+        }
+    }
+
+    RangeSched& schedule(const StepBlock& blk, size_t begin, size_t end) {
+        auto key = std::make_pair(&blk, begin);
+        auto it = cp_->sched.find(key);
+        if (it != cp_->sched.end() && it->second.steps.size() == end - begin) return it->second;
+        RangeSched rs;
+        rs.steps.resize(end - begin);
+        // dependencies are tracked on memory ranges, not buffer ids: buffers with disjoint lifetimes share
+        // arena space, and a step that runs early on the other stream must not touch memory that steps
+        // before it in program order still use (nor the other way round)
+        struct Touch { uintptr_t lo, hi; int idx; };
+        std::vector<Touch> main_touch, comm_touch;
+        std::vector<int> bufs;
+        auto range_of = [&](int b) {
+            const BufferInfo& bi = plan_.bufs[size_t(b)];
+            uintptr_t lo = reinterpret_cast<uintptr_t>(buf_ptr(b));
+            return std::make_pair(lo, lo + uintptr_t(bi.numel) * 4);
+        };
+        for (size_t t = begin; t < end; t++) {
+            const Step& s = blk.steps[t];
+            StepSched& sc = rs.steps[t - begin];
+            if (d_->world > 1 && !(d_->flags & ADB_FLAG_NO_OVERLAP)) {
+                if (s.kind == Step::ALLREDUCE) sc.on_comm = true;
+                // the small kernel that writes the operand of the collective right before it
+                if (s.kind == Step::ELW && t + 1 < end && blk.steps[t + 1].kind == Step::ALLREDUCE) {
+                    const KernelSpec& k = plan_.kernels[s.kernel];
+                    if (k.outs.size() == 1 && k.outs[0].dst.buf == blk.steps[t + 1].buf) sc.on_comm = true;
+                }
+            }
+            step_buffers(s, bufs);
+            for (int b : bufs) {
+                auto r = range_of(b);
+                for (auto& o : (sc.on_comm ? main_touch : comm_touch))
+                    if (o.lo < r.second && r.first < o.hi) {
+                        if (sc.on_comm) sc.wait_main = std::max(sc.wait_main, o.idx);
+                        else sc.wait_comm = std::max(sc.wait_comm, o.idx);
+                    }
+            }
+            for (int b : bufs) {
+                auto r = range_of(b);
+                (sc.on_comm ? comm_touch : main_touch).push_back({r.first, r.second, int(t - begin)});
+            }
+            if (sc.on_comm) {
+                rs.any_comm = true;
+                if (sc.wait_main >= 0) rs.steps[size_t(sc.wait_main)].record_after = true;
+            }
+        }
+        for (auto& sc : rs.steps)
+            if (sc.on_comm || sc.record_after) ck(cudaEventCreateWithFlags(&sc.done, cudaEventDisableTiming), "event create");
+        if (rs.any_comm) ck(cudaEventCreateWithFlags(&rs.fork, cudaEventDisableTiming), "event create");
+        return cp_->sched[key] = std::move(rs);
+    }
+
+    // runs steps [begin, end) of a block: main-stream steps in order, collectives forked onto the
+    // communication stream and joined again before the range ends
+    void run_range(const StepBlock& blk, size_t begin, size_t end) {
+        RangeSched& rs = schedule(blk, begin, end);
+        if (!rs.any_comm) {
+            for (size_t t = begin; t < end; t++) run_step(blk.steps[t]);
+            return;
+        }
+        ck(cudaEventRecord(rs.fork, d_->stream), "fork");
+        ck(cudaStreamWaitEvent(d_->comm_stream, rs.fork, 0), "fork");
+        int last_comm = -1;
+        for (size_t t = begin; t < end; t++) {
+            StepSched& sc = rs.steps[t - begin];
+            if (sc.on_comm) {
+                if (sc.wait_main >= 0) ck(cudaStreamWaitEvent(d_->comm_stream, rs.steps[size_t(sc.wait_main)].done, 0), "comm waits");
+                cur_stream_ = d_->comm_stream;
+                run_step(blk.steps[t]);
+                cur_stream_ = d_->stream;
+                ck(cudaEventRecord(sc.done, d_->comm_stream), "event");
+                last_comm = int(t - begin);
+            } else {
+                if (sc.wait_comm >= 0) ck(cudaStreamWaitEvent(d_->stream, rs.steps[size_t(sc.wait_comm)].done, 0), "main waits");
+                run_step(blk.steps[t]);
+                if (sc.record_after) ck(cudaEventRecord(sc.done, d_->stream), "event");
+            }
+        }
+        if (last_comm >= 0) ck(cudaStreamWaitEvent(d_->stream, rs.steps[size_t(last_comm)].done, 0), "join");
+    }
+
     static bool capturable(const Step& s, const Plan& plan) {
         switch (s.kind) {
         case Step::ELW: case Step::REDUCE: case Step::GEMM: case Step::ALLREDUCE: return true;
@@ -443,7 +557,7 @@ class Executor {
                 ck(cudaStreamBeginCapture(d_->stream, cudaStreamCaptureModeThreadLocal), "begin capture");
                 capturing_ = true;
                 try {
-                    for (size_t t = i; t < j; t++) run_step(blk.steps[t]);
+                    run_range(blk, i, j);
                 } catch (...) {
                     capturing_ = false;
                     cudaStreamEndCapture(d_->stream, &graph);
@@ -486,17 +600,26 @@ class Executor {
                     tc_ += g.tc;
                     d_->stats.graph_replays++;
                 } else {
-                    for (size_t t = g.begin; t < g.end; t++) {
-                        run_one(blk.steps[t], in_loop);
-                        if (d_->exit_requested) return;
-                    }
+                    run_plain(blk, g.begin, g.end, in_loop);
+                    if (d_->exit_requested) return;
                 }
             }
             return;
         }
-        for (auto& s : blk.steps) {
-            run_one(s, false);
+        run_plain(blk, 0, blk.steps.size(), false);
+    }
+
+    // steps launched one by one: maximal runs of kernels / collectives go through run_range (so that
+    // collectives overlap), everything else (control flow, host uploads) is handled on its own
+    void run_plain(const StepBlock& blk, size_t begin, size_t end, bool in_loop) {
+        size_t t = begin;
+        while (t < end) {
+            size_t u = t;
+            while (u < end && capturable(blk.steps[u], plan_)) u++;
+            if (u > t) { run_range(blk, t, u); t = u; continue; }
+            run_one(blk.steps[t], in_loop);
             if (d_->exit_requested) return;
+            t++;
         }
     }
 
@@ -559,6 +682,7 @@ class Executor {
     bool capturing_ = false;
     int loop_depth_ = 0;
     uint64_t loop_iter_ = 0;
+    cudaStream_t cur_stream_ = nullptr;
 
   private:
     adb_device* d_;
@@ -575,6 +699,15 @@ void destroy_prefetch(CompiledPlan& cp) {
             if (kv.second.freed[b]) cudaEventDestroy(kv.second.freed[b]);
         }
     cp.prefetch.clear();
+}
+
+void destroy_sched(CompiledPlan& cp) {
+    for (auto& kv : cp.sched) {
+        for (auto& sc : kv.second.steps)
+            if (sc.done) cudaEventDestroy(sc.done);
+        if (kv.second.fork) cudaEventDestroy(kv.second.fork);
+    }
+    cp.sched.clear();
 }
 
 void destroy_graphs(CompiledPlan& cp) {
@@ -651,6 +784,7 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
         if (!ok) {
             destroy_graphs(*cp);
             destroy_prefetch(*cp);
+            destroy_sched(*cp);
             d->plans.erase(it);
             cp = nullptr;
         }
@@ -828,6 +962,11 @@ adb_status adb_create(const adb_config* cfg, adb_device** out) {
         }
         ck(cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking), "cudaStreamCreate");
         ck(cudaStreamCreateWithFlags(&d->copy_stream, cudaStreamNonBlocking), "cudaStreamCreate");
+        {
+            int lo = 0, hi = 0;
+            ck(cudaDeviceGetStreamPriorityRange(&lo, &hi), "priority range");
+            ck(cudaStreamCreateWithPriority(&d->comm_stream, cudaStreamNonBlocking, hi), "cudaStreamCreate");
+        }
         ck(cudaMallocHost(&d->cond_host, 64), "cudaMallocHost");
         std::string gerr;
         if (!gemm_init(d->gemm, d->sm_count, gerr)) throw CudaFail{gerr};
@@ -853,7 +992,8 @@ void adb_destroy(adb_device* d) {
     cudaSetDevice(d->ordinal);
     if (d->stream) cudaStreamSynchronize(d->stream);
     if (d->copy_stream) cudaStreamSynchronize(d->copy_stream);
-    for (auto& kv : d->plans) { destroy_graphs(*kv.second); destroy_prefetch(*kv.second); }
+    if (d->comm_stream) cudaStreamSynchronize(d->comm_stream);
+    for (auto& kv : d->plans) { destroy_graphs(*kv.second); destroy_prefetch(*kv.second); destroy_sched(*kv.second); }
     d->plans.clear();
     for (auto& k : d->kernels)
         if (k.lib) cudaLibraryUnload(k.lib);
@@ -866,6 +1006,7 @@ void adb_destroy(adb_device* d) {
     if (d->arena) cudaFree(d->arena);
     if (d->cond_host) cudaFreeHost(d->cond_host);
     if (d->copy_stream) cudaStreamDestroy(d->copy_stream);
+    if (d->comm_stream) cudaStreamDestroy(d->comm_stream);
     if (d->stream) cudaStreamDestroy(d->stream);
     delete d;
 }
