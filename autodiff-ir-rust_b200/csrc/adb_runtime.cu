@@ -338,8 +338,6 @@ class Executor {
         }
         case Step::UPLOAD: {
             const PayloadSlot& p = plan_.payloads[s.payload];
-            cudaEvent_t e0 = event(), e1 = event();
-            ck(cudaEventRecord(e0, d_->stream), "event");
             auto pf = cp_->prefetch.find(&s);
             if (pf != cp_->prefetch.end() && loop_depth_ > 0) {
                 // the batch for this iteration was copied ahead of time; start the copy for the next one
@@ -358,12 +356,16 @@ class Executor {
                 ck(cudaMemcpyAsync(buf_ptr(s.buf), reinterpret_cast<const void*>(uintptr_t(p.addr)), size_t(s.nelem) * 4,
                                    cudaMemcpyDeviceToDevice, d_->stream), "upload (device)");
             } else {
+                // host -> device copies on the compute stream are timed apart from the kernels (never inside a
+                // stream capture: host payloads are not capturable)
+                cudaEvent_t e0 = event(), e1 = event();
+                ck(cudaEventRecord(e0, d_->stream), "event");
                 ck(cudaMemcpyAsync(buf_ptr(s.buf), reinterpret_cast<const void*>(uintptr_t(p.addr)), size_t(s.nelem) * 4,
                                    cudaMemcpyHostToDevice, d_->stream), "upload (host)");
+                ck(cudaEventRecord(e1, d_->stream), "event");
+                d_->upload_events.push_back({e0, e1});
                 d_->stats.h2d_bytes += uint64_t(s.nelem) * 4;
             }
-            ck(cudaEventRecord(e1, d_->stream), "event");
-            d_->upload_events.push_back({e0, e1});
             break;
         }
         case Step::ALLREDUCE: {
@@ -470,7 +472,7 @@ class Executor {
         for (size_t t = begin; t < end; t++) {
             const Step& s = blk.steps[t];
             StepSched& sc = rs.steps[t - begin];
-            if (d_->world > 1 && !(d_->flags & ADB_FLAG_NO_OVERLAP)) {
+            if (d_->world > 1 && (d_->flags & ADB_FLAG_COMM_STREAM)) {
                 if (s.kind == Step::ALLREDUCE) sc.on_comm = true;
                 // the small kernel that writes the operand of the collective right before it
                 if (s.kind == Step::ELW && t + 1 < end && blk.steps[t + 1].kind == Step::ALLREDUCE) {
@@ -878,12 +880,12 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
         return ADB_ERR_CUDA;
     }
     float ms_run = 0, ms_rb = 0;
-    cudaEventElapsedTime(&ms_run, ev0, ev1);
-    cudaEventElapsedTime(&ms_rb, ev1, ev2);
+    ck(cudaEventElapsedTime(&ms_run, ev0, ev1), "elapsed time");
+    ck(cudaEventElapsedTime(&ms_rb, ev1, ev2), "elapsed time");
     double up = 0;
     for (auto& pr : d->upload_events) {
         float m = 0;
-        cudaEventElapsedTime(&m, pr.first, pr.second);
+        ck(cudaEventElapsedTime(&m, pr.first, pr.second), "elapsed time");
         up += m;
     }
     d->stats.upload_ms = up;
@@ -897,7 +899,7 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
         std::map<int, std::pair<double, std::pair<double, uint64_t>>> per_kernel;  // kernel -> (ms, (bytes, launches))
         for (auto& r : d->prof) {
             float m = 0;
-            cudaEventElapsedTime(&m, r.e0, r.e1);
+            ck(cudaEventElapsedTime(&m, r.e0, r.e1), "elapsed time");
             switch (r.kind) {
             case Step::ELW: d->stats.elw_ms += m; d->stats.elw_bytes += r.work; d->stats.elw_launches++; break;
             case Step::REDUCE: d->stats.reduce_ms += m; d->stats.reduce_bytes += r.work; d->stats.reduce_launches++; break;
@@ -1016,6 +1018,7 @@ adb_status adb_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
     d->err.clear();
     try {
         if (cudaSetDevice(d->ordinal) != cudaSuccess) { d->err = "cudaSetDevice failed"; return ADB_ERR_CUDA; }
+        cudaGetLastError();  // an error left behind by the caller's own CUDA calls is not ours to report
         return do_execute(d, blob, nbytes);
     } catch (IrError& e) {
         d->err = std::string("invalid program: ") + e.what();

@@ -153,7 +153,7 @@ def run_ours(args):
     widths = cfg.C4_WIDTHS
     batch = args.batch
     lb = batch // world
-    flags = adb.devices.FLAG_PROFILE
+    flags = adb.devices.FLAG_PROFILE if args.dev_flags is None else args.dev_flags
     dev = adb.devices.B200(local, rank=rank, world_size=world, nccl_unique_id=uid, flags=flags, shard_batch=batch if world > 1 else 0)
 
     # synthetic data: weights from the documented counter-based generator, the batch from torch's
@@ -342,6 +342,7 @@ def main():
     ap.add_argument("--c2-size", type=int, default=8192)
     ap.add_argument("--cpu-sample-batch", type=int, default=512)
     ap.add_argument("--skip-extras", action="store_true")
+    ap.add_argument("--dev-flags", type=int, default=None, help="ADB_FLAG_* bits of the handle (default: per-kernel profiling events)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

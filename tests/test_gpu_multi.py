@@ -12,7 +12,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 KW = dict(batch=256, widths=(64, 128, 128, 64, 16), steps=4, lr=1e-2)
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, flags):
     sys.path.insert(0, ROOT)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     import torch
@@ -24,7 +24,7 @@ def _worker(rank, world, port, out_dir):
     adb = importlib.import_module("autodiff-ir-rust_b200")
     box = [adb.devices.nccl_unique_id() if rank == 0 else None]
     dist.broadcast_object_list(box, src=0)
-    dev = adb.devices.B200(rank, rank=rank, world_size=world, nccl_unique_id=box[0], shard_batch=KW["batch"])
+    dev = adb.devices.B200(rank, rank=rank, world_size=world, nccl_unique_id=box[0], shard_batch=KW["batch"], flags=flags)
     inputs = adb.configs.c4_inputs(batch=KW["batch"], widths=KW["widths"])     # full tensors: the device takes its rows
     out = adb.configs.c4_mlp_train(dev, inputs=inputs, **KW)
     np.savez(os.path.join(out_dir, f"rank{rank}.npz"), **{k: v.numpy() for k, v in out.items()})
@@ -32,14 +32,16 @@ def _worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
-def test_two_gpus_match_one_gpu(tmp_path):
+@pytest.mark.parametrize("flags", [0, 16], ids=["compute-stream", "comm-stream"])
+def test_two_gpus_match_one_gpu(tmp_path, flags):
+    """flags 16 = ADB_FLAG_COMM_STREAM: collectives on their own stream, ordered against the compute stream by events."""
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     adb = importlib.import_module("autodiff-ir-rust_b200")
-    port = 29600 + (os.getpid() % 2000)
-    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    port = 29600 + (os.getpid() % 2000) + flags
+    mp.spawn(_worker, args=(2, port, str(tmp_path), flags), nprocs=2, join=True)
     dev = adb.devices.B200(0)
     want = adb.configs.c4_mlp_train(dev, inputs=adb.configs.c4_inputs(batch=KW["batch"], widths=KW["widths"]), **KW)
     dev.close()

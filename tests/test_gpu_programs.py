@@ -3,7 +3,7 @@ dot products with folded transposes, control flow -- B200 against the CPU oracle
 import numpy as np
 import pytest
 
-from helpers import ad, nn, run_both, assert_exact, assert_rel, assert_ulp, b200
+from helpers import ad, adb, nn, oracle, run_both, assert_exact, assert_rel, assert_ulp, b200
 
 pytestmark = pytest.mark.gpu
 RNG = np.random.default_rng(11)
@@ -271,3 +271,41 @@ def test_pinned_payload_uploaded_inside_a_loop_is_prefetched_correctly():
     want, got = run_both(prog)
     assert_exact("acc", got["acc"], want["acc"])
     assert b200().stats()["h2d_bytes"] >= 5 * n * 4
+
+
+def test_device_payload_in_a_captured_loop_then_a_new_program_with_a_dot():
+    """A device-resident CreateMat inside a loop body is copied inside the replayed CUDA graph; the next
+    execute (a different program, launched kernel by kernel) must not see any error left behind by it."""
+    import torch
+    n = 256 * 512
+    x_dev = torch.from_numpy(rnd(n)).cuda()
+    x_host = x_dev.cpu().numpy()
+
+    def loop_prog(dev, payload):
+        ad.set_device(dev)
+        acc = ad.tensor(np.zeros(n, np.float32), [256, 512])
+
+        def body(i):
+            nonlocal acc
+            x = ad.tensor(payload, [256, 512])
+            acc += x * 0.5
+            acc.forward()
+        ad.ir_for(range(0, 4), body)
+        ad.execute()
+        return {"acc": acc.val().get()}
+
+    def dot_prog(dev):
+        ad.set_device(dev)
+        a = ad.tensor(x_host[:128 * 256].copy(), [128, 256])
+        b = ad.tensor(x_host[128 * 256:128 * 256 + 256 * 64].copy(), [256, 64])
+        y = ad.dot(a, b).forward()
+        y.keep()
+        ad.execute()
+        return {"y": y.get()}
+
+    want = loop_prog(oracle(), x_host)
+    for _ in range(2):
+        got = loop_prog(b200(), adb.ir.DevicePayload(x_dev.data_ptr(), n, x_dev))
+        assert_exact("acc", got["acc"], want["acc"])
+        want_y, got_y = dot_prog(oracle()), dot_prog(b200())
+        assert_rel("y", got_y["y"], want_y["y"], 1e-4)
