@@ -326,7 +326,7 @@ adb_dot_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
             }
         }
     } else if (warp < 6) {
-        // ------------------------------------------------------------------ split: raw fp32 -> tf32 hi (in place) + tf32 lo
+        // ------------------------------------------------------------------ split: raw fp32 -> tf32 lo beside it
         const int t = threadIdx.x - 64;  // 0..127
         uint32_t it = 0;
         bool ok = true;
@@ -335,18 +335,19 @@ adb_dot_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                 const int s = it % STAGES;
                 const uint32_t ph = (it / STAGES) & 1;
                 if (!mbar_wait_warp(bar_raw(s), ph, stop, p.status, TIMEOUT_RAW)) { ok = false; break; }
-                uint4* hi = reinterpret_cast<uint4*>(gen_base + s * STAGE_BYTES);
+                // kind::tf32 reads the upper 19 bits of each fp32 word, so the raw tile already serves as
+                // hi = trunc_tf32(x); only lo = x - hi (exact in fp32, truncated again by the MMA) is written.
+                // Every byte less through shared memory counts: the MMAs' own operand reads take 3/4 of its bandwidth.
+                const uint4* raw = reinterpret_cast<const uint4*>(gen_base + s * STAGE_BYTES);
                 uint4* lo = reinterpret_cast<uint4*>(gen_base + s * STAGE_BYTES + A_BYTES + B_BYTES);
 #pragma unroll 4
                 for (int i = t; i < (A_BYTES + B_BYTES) / 16; i += 128) {
-                    uint4 v = hi[i];
-                    uint4 h, l;
-                    h.x = v.x & 0xffffe000u; h.y = v.y & 0xffffe000u; h.z = v.z & 0xffffe000u; h.w = v.w & 0xffffe000u;
-                    l.x = __float_as_uint(__uint_as_float(v.x) - __uint_as_float(h.x)) & 0xffffe000u;
-                    l.y = __float_as_uint(__uint_as_float(v.y) - __uint_as_float(h.y)) & 0xffffe000u;
-                    l.z = __float_as_uint(__uint_as_float(v.z) - __uint_as_float(h.z)) & 0xffffe000u;
-                    l.w = __float_as_uint(__uint_as_float(v.w) - __uint_as_float(h.w)) & 0xffffe000u;
-                    hi[i] = h;
+                    const uint4 v = raw[i];
+                    uint4 l;
+                    l.x = __float_as_uint(__uint_as_float(v.x) - __uint_as_float(v.x & 0xffffe000u));
+                    l.y = __float_as_uint(__uint_as_float(v.y) - __uint_as_float(v.y & 0xffffe000u));
+                    l.z = __float_as_uint(__uint_as_float(v.z) - __uint_as_float(v.z & 0xffffe000u));
+                    l.w = __float_as_uint(__uint_as_float(v.w) - __uint_as_float(v.w & 0xffffe000u));
                     lo[i] = l;
                 }
                 // make the generic-proxy writes visible to the tensor core (async proxy) before signalling
