@@ -422,6 +422,297 @@ adb_dot_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     }
 }
 
+// ====================================================================================================
+// Paired-CTA variant (cta_group::2)
+// ====================================================================================================
+// Two CTAs of a cluster (two SMs) work on one 256 x 256 tile of C.  Each CTA holds 128 rows of A, one half
+// (128 columns) of the B tile and the 128 x 256 accumulator of its own rows in its own tensor memory; one
+// thread of the leader CTA issues M = 256 instructions that run on both SMs and read each B half only once.
+// Per SM and k-block that is 24 KiB of operand reads per pass instead of 36 and 32 KiB of raw tile instead
+// of 48, which is what matters here: shared-memory bandwidth, not the tensor pipe, bounds the 3xTF32 loop.
+//
+// Hand-shakes (all waits bounded, as in the single-CTA kernel):
+//   raw[s]        local   TMA of this CTA landed
+//   split[s]      leader  8 arrivals: the four split warps of both CTAs wrote their lo tiles
+//   empty[s]      both    the leader's MMAs that read stage s finished (one commit per CTA)
+//   acc_full[a]   both    accumulator a holds a finished chunk (one commit per CTA)
+//   acc_empty[a]  leader  8 arrivals: the epilogue warps of both CTAs drained accumulator a
+namespace pair {
+
+using namespace tc;
+
+constexpr int BNH = BN / 2;                             // columns of the B tile held by one CTA
+constexpr int PSTAGES = 3;
+constexpr int BH_BYTES = BNH * BK * 4;                  // 16 KiB
+constexpr int RAW_BYTES = A_BYTES + BH_BYTES;           // 32 KiB
+constexpr int PSTAGE_BYTES = 2 * RAW_BYTES;             // raw + lo: 64 KiB
+constexpr int PSMEM_BYTES = PSTAGES * PSTAGE_BYTES + 1024 + 256;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// bounded wait on a barrier that threads of the other CTA arrive on
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* stop, int* status, int code) {
+    for (uint32_t it = 0; it < SPIN_LIMIT; it++) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if (*stop) return false;
+        if (it > 64) __nanosleep(64);
+    }
+    *stop = 1;
+    atomicCAS(status, 0, code);
+    return false;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ void umma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// `cluster_addr` may name a barrier of either CTA of the pair
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+adb_dot_tc_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+    // per stage: [A raw][B-half raw][A lo][B-half lo]
+    auto a_raw = [&](int s) { return base + s * PSTAGE_BYTES; };
+    auto b_raw = [&](int s) { return base + s * PSTAGE_BYTES + A_BYTES; };
+    const uint32_t bars = base + PSTAGES * PSTAGE_BYTES;
+    auto bar_raw = [&](int s) { return bars + 8u * s; };
+    auto bar_split = [&](int s) { return bars + 8u * (PSTAGES + s); };
+    auto bar_empty = [&](int s) { return bars + 8u * (2 * PSTAGES + s); };
+    auto bar_acc_full = [&](int a) { return bars + 8u * (3 * PSTAGES + a); };
+    auto bar_acc_empty = [&](int a) { return bars + 8u * (3 * PSTAGES + 2 + a); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen_base + PSTAGES * PSTAGE_BYTES + 8 * (3 * PSTAGES + 4));
+    volatile int* stop = reinterpret_cast<volatile int*>(gen_base + PSTAGES * PSTAGE_BYTES + 8 * (3 * PSTAGES + 4) + 8);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();       // 0 = leader
+    const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+    const int total_tiles = p.tiles_m * p.tiles_n;  // tiles_m counts 256-row tiles here
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PSTAGES; s++) {
+            mbar_init(bar_raw(s), 1);
+            mbar_init(bar_split(s), 8);
+            mbar_init(bar_empty(s), 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(bar_acc_full(a), 1);
+            mbar_init(bar_acc_empty(a), 8);
+        }
+        *stop = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();  // the peer's barriers are initialised and its tensor memory is allocated
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (both CTAs, own halves)
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < total_tiles && ok; tile += num_clusters) {
+                const int m0 = (tile / p.tiles_n) * (2 * BM) + (int)rank * BM;
+                const int n0 = (tile % p.tiles_n) * BN + (int)rank * BNH;
+                for (int kb = 0; kb < p.k_blocks; kb++, it++) {
+                    const int s = it % PSTAGES;
+                    const uint32_t ph = (it / PSTAGES) & 1;
+                    if (!mbar_wait(bar_empty(s), ph ^ 1, stop, p.status, TIMEOUT_EMPTY)) { ok = false; break; }
+                    mbar_expect_tx(bar_raw(s), RAW_BYTES);
+                    const int k0 = kb * BK;
+                    if (A_MN) {
+#pragma unroll
+                        for (int c = 0; c < BM / 32; c++) tma_load_2d(a_raw(s) + c * (BK * 128), &map_a, bar_raw(s), m0 + 32 * c, k0);
+                    } else {
+                        tma_load_2d(a_raw(s), &map_a, bar_raw(s), k0, m0);
+                    }
+                    if (B_MN) {
+#pragma unroll
+                        for (int c = 0; c < BNH / 32; c++) tma_load_2d(b_raw(s) + c * (BK * 128), &map_b, bar_raw(s), n0 + 32 * c, k0);
+                    } else {
+                        tma_load_2d(b_raw(s), &map_b, bar_raw(s), k0, n0);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+                                   ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+            const uint32_t a_lbo = p.a_lbo, a_sbo = p.a_sbo, a_kstep = p.a_kstep;
+            const uint32_t b_lbo = p.b_lbo, b_sbo = p.b_sbo, b_kstep = p.b_kstep;
+            uint32_t it = 0, chunk_no = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < total_tiles && ok; tile += num_clusters) {
+                for (int kb0 = 0; kb0 < p.k_blocks && ok; kb0 += CHUNK_KB, chunk_no++) {
+                    const int acc = chunk_no & 1;
+                    const uint32_t acc_ph = (chunk_no >> 1) & 1;
+                    if (!mbar_wait_cluster(bar_acc_empty(acc), acc_ph ^ 1, stop, p.status, TIMEOUT_ACC_EMPTY)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t d_tmem = tmem_base + acc * BN;
+                    const int kb_end = min(kb0 + CHUNK_KB, p.k_blocks);
+                    for (int kb = kb0; kb < kb_end; kb++, it++) {
+                        const int s = it % PSTAGES;
+                        const uint32_t ph = (it / PSTAGES) & 1;
+                        if (!mbar_wait_cluster(bar_split(s), ph, stop, p.status, TIMEOUT_SPLIT)) { ok = false; break; }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                        for (int j = 0; j < BK / UMMA_K; j++) {
+                            const uint64_t ah = make_desc(a_raw(s) + j * a_kstep, a_lbo, a_sbo, p.a_layout);
+                            const uint64_t bh = make_desc(b_raw(s) + j * b_kstep, b_lbo, b_sbo, p.b_layout);
+                            const uint64_t al = make_desc(a_raw(s) + RAW_BYTES + j * a_kstep, a_lbo, a_sbo, p.a_layout);
+                            const uint64_t bl = make_desc(b_raw(s) + RAW_BYTES + j * b_kstep, b_lbo, b_sbo, p.b_layout);
+                            umma_tf32_pair(d_tmem, al, bh, idesc, ((kb - kb0) | j) != 0);
+                            umma_tf32_pair(d_tmem, ah, bl, idesc, 1);
+                            umma_tf32_pair(d_tmem, ah, bh, idesc, 1);
+                        }
+                        umma_commit_pair(bar_empty(s));
+                        umma_commit_pair(map_to_cta(bar_empty(s), 1));
+                    }
+                    if (ok) {
+                        umma_commit_pair(bar_acc_full(acc));
+                        umma_commit_pair(map_to_cta(bar_acc_full(acc), 1));
+                    }
+                }
+            }
+        }
+    } else if (warp < 6) {
+        // ------------------------------------------------------------------ split: lo tiles beside the raw ones
+        const int t = threadIdx.x - 64;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = cluster_id; tile < total_tiles && ok; tile += num_clusters) {
+            for (int kb = 0; kb < p.k_blocks; kb++, it++) {
+                const int s = it % PSTAGES;
+                const uint32_t ph = (it / PSTAGES) & 1;
+                if (!mbar_wait_warp(bar_raw(s), ph, stop, p.status, TIMEOUT_RAW)) { ok = false; break; }
+                const uint4* raw = reinterpret_cast<const uint4*>(gen_base + s * PSTAGE_BYTES);
+                uint4* lo = reinterpret_cast<uint4*>(gen_base + s * PSTAGE_BYTES + RAW_BYTES);
+#pragma unroll 4
+                for (int i = t; i < RAW_BYTES / 16; i += 128) {
+                    const uint4 v = raw[i];
+                    uint4 l;
+                    l.x = __float_as_uint(__uint_as_float(v.x) - __uint_as_float(v.x & 0xffffe000u));
+                    l.y = __float_as_uint(__uint_as_float(v.y) - __uint_as_float(v.y & 0xffffe000u));
+                    l.z = __float_as_uint(__uint_as_float(v.z) - __uint_as_float(v.z & 0xffffe000u));
+                    l.w = __float_as_uint(__uint_as_float(v.w) - __uint_as_float(v.w & 0xffffe000u));
+                    lo[i] = l;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(map_to_cta(bar_split(s), 0));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue: own rows, all 256 columns
+        const int q = warp & 3;
+        uint32_t chunk_no = 0;
+        bool ok = true;
+        const bool vec_ok = (p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+        for (int tile = cluster_id; tile < total_tiles && ok; tile += num_clusters) {
+            const int m0 = (tile / p.tiles_n) * (2 * BM) + (int)rank * BM, n0 = (tile % p.tiles_n) * BN;
+            const int row = m0 + q * 32 + lane;
+            float* crow = p.C + (size_t)row * p.N;
+            for (int kb0 = 0; kb0 < p.k_blocks && ok; kb0 += CHUNK_KB, chunk_no++) {
+                const int acc = chunk_no & 1;
+                const uint32_t acc_ph = (chunk_no >> 1) & 1;
+                const bool first = kb0 == 0;
+                if (!mbar_wait_warp(bar_acc_full(acc), acc_ph, stop, p.status, TIMEOUT_ACC_FULL)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; c++) {
+                    float v[32];
+                    tmem_load_32cols(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, v);
+                    const int col0 = n0 + c * 32;
+                    if (row < p.M && col0 < p.N) {
+                        if (vec_ok && col0 + 32 <= p.N) {
+                            float4* dst = reinterpret_cast<float4*>(crow + col0);
+                            if (first) {
+#pragma unroll
+                                for (int j = 0; j < 8; j++) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 8; j++)
+                                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "f"(v[4 * j]),
+                                                 "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3]) : "memory");
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
+                                if (col0 + j < p.N) {
+                                    if (first) crow[col0 + j] = v[j];
+                                    else atomicAdd(crow + col0 + j, v[j]);
+                                }
+                        }
+                    }
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(map_to_cta(bar_acc_empty(acc), 0));
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    __syncthreads();
+    if (*stop && threadIdx.x == 0) {
+        for (int i = 0; i < 256; i++) __nanosleep(1000);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    // neither CTA may free tensor memory or leave while the other can still signal its barriers or while
+    // instructions issued by the leader still read its shared memory
+    cluster_sync_all();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+}  // namespace pair
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -466,6 +757,27 @@ bool gemm_init(GemmContext& ctx, int sm_count, std::string& err) {
     if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::adb_dot_tc<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
     if (e != cudaSuccess) { err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e); return false; }
     ctx.tc_ready = true;
+    // paired-CTA variant: clusters of two CTAs; how many fit at once depends on how the SMs are grouped
+    e = cudaFuncSetAttribute(tc::pair::adb_dot_tc_pair<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::pair::PSMEM_BYTES);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::pair::adb_dot_tc_pair<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::pair::PSMEM_BYTES);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::pair::adb_dot_tc_pair<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::pair::PSMEM_BYTES);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::pair::adb_dot_tc_pair<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::pair::PSMEM_BYTES);
+    if (e == cudaSuccess) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(sm_count & ~1));
+        cfg.blockDim = dim3(tc::NUM_THREADS);
+        cfg.dynamicSmemBytes = tc::pair::PSMEM_BYTES;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        e = cudaOccupancyMaxActiveClusters(&clusters, tc::pair::adb_dot_tc_pair<false, false>, &cfg);
+        if (e == cudaSuccess && clusters > 0) ctx.pair_clusters = clusters;
+    }
+    if (e != cudaSuccess) cudaGetLastError();  // the single-CTA kernel remains available
+    if (const char* v = getenv("ADB_DOT_PAIR")) { if (v[0] == '0') ctx.pair_clusters = 0; }
     return true;
 }
 
@@ -497,8 +809,11 @@ int gemm_launch(GemmContext& ctx, const GemmArgs& a, cudaStream_t stream, std::s
         auto enc = reinterpret_cast<EncodeTiledFn>(ctx.encode_tiled);
         CUtensorMap ma, mb;
         const bool A_MN = !a_k, B_MN = !b_k;
+        // two SMs per 256-row tile when there are at least two 128-row tiles to pair up
+        const bool paired = ctx.pair_clusters > 0 && !a.no_pair && a.M > BM;
         bool ok = A_MN ? encode(enc, &ma, a.A, a.M, a.K, a.a_cs, BK, true) : encode(enc, &ma, a.A, a.K, a.M, a.a_rs, BM, false);
-        ok = ok && (B_MN ? encode(enc, &mb, a.B, a.N, a.K, a.b_rs, BK, true) : encode(enc, &mb, a.B, a.K, a.N, a.b_cs, BN, false));
+        ok = ok && (B_MN ? encode(enc, &mb, a.B, a.N, a.K, a.b_rs, BK, true)
+                         : encode(enc, &mb, a.B, a.K, a.N, a.b_cs, paired ? pair::BNH : BN, false));
         if (ok) {
             Params p;
             p.C = a.C;
@@ -515,6 +830,22 @@ int gemm_launch(GemmContext& ctx, const GemmArgs& a, cudaStream_t stream, std::s
                     if (A_MN) { p.a_lbo = l; p.a_sbo = sb; p.a_kstep = ks; }
                     if (B_MN) { p.b_lbo = l; p.b_sbo = sb; p.b_kstep = ks; }
                 }
+            }
+            if (paired) {
+                p.tiles_m = (int)((a.M + 2 * BM - 1) / (2 * BM));
+                long long clusters = (long long)p.tiles_m * p.tiles_n;
+                if (clusters > ctx.pair_clusters) clusters = ctx.pair_clusters;
+                const int grid = int(2 * clusters);
+                using namespace pair;
+                if (A_MN && B_MN) adb_dot_tc_pair<true, true><<<grid, NUM_THREADS, PSMEM_BYTES, stream>>>(ma, mb, p);
+                else if (A_MN) adb_dot_tc_pair<true, false><<<grid, NUM_THREADS, PSMEM_BYTES, stream>>>(ma, mb, p);
+                else if (B_MN) adb_dot_tc_pair<false, true><<<grid, NUM_THREADS, PSMEM_BYTES, stream>>>(ma, mb, p);
+                else adb_dot_tc_pair<false, false><<<grid, NUM_THREADS, PSMEM_BYTES, stream>>>(ma, mb, p);
+                cudaError_t e = cudaGetLastError();
+                if (e != cudaSuccess) { err = std::string("adb_dot_tc_pair launch: ") + cudaGetErrorString(e); return -1; }
+                ctx.tc_launches++;
+                ctx.tc_total++;
+                return 1;
             }
             int grid = p.tiles_m * p.tiles_n;
             if (grid > ctx.sm_count) grid = ctx.sm_count;

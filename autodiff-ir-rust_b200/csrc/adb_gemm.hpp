@@ -15,12 +15,14 @@ struct GemmArgs {
     int64_t M = 0, N = 0, K = 0;
     int64_t a_rs = 0, a_cs = 0, b_rs = 0, b_cs = 0;  // element strides of A[m,k] and B[k,n]
     bool force_simt = false;
+    bool no_pair = false;  // keep the tensor-core kernel on one SM per tile
 };
 
 struct GemmContext {
     int sm_count = 148;
     void* encode_tiled = nullptr;  // cuTensorMapEncodeTiled, fetched through the runtime (no libcuda link)
     bool tc_ready = false;
+    int pair_clusters = 0;         // two-CTA clusters of the paired kernel that can be resident at once (0 = unavailable)
     int* status = nullptr;         // device word the tensor-core kernel sets when a bounded wait runs out
     int* status_host = nullptr;
     unsigned long long tc_launches = 0;  // tensor-core launches since the last status check

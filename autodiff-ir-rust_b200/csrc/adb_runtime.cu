@@ -327,6 +327,7 @@ class Executor {
             a.M = g.M; a.N = g.N; a.K = g.K;
             a.a_rs = g.a_rs; a.a_cs = g.a_cs; a.b_rs = g.b_rs; a.b_cs = g.b_cs;
             a.force_simt = (d_->flags & ADB_FLAG_SIMT_DOT) != 0;
+            a.no_pair = (d_->flags & ADB_FLAG_SINGLE_SM_DOT) != 0;
             std::string e;
             const unsigned long long tc0 = d_->gemm.tc_total;
             int n = gemm_launch(d_->gemm, a, cur_stream_, e);

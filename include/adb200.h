@@ -79,6 +79,8 @@ typedef struct adb_config {
                                       they touch) instead of the compute stream; off by default: the persistent dot-product
                                       kernel holds every SM, so the collective only starts when it ends and then delays the
                                       next one (measured 2 % slower on 2 GPUs) */
+#define ADB_FLAG_SINGLE_SM_DOT 32u  /* keep the tcgen05 dot kernel on one SM per 128 x 256 tile instead of pairing two SMs
+                                      (cta_group::2) on a 256 x 256 tile */
 #define ADB_FLAG_PROFILE 8u        /* CUDA events around every kernel (fills the per-kind times of adb_stats);
                                       loop bodies are then launched kernel by kernel, not as graphs */
 

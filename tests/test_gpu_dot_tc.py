@@ -2,10 +2,21 @@
 import numpy as np
 import pytest
 
-from helpers import ad, b200, oracle, assert_rel
+from helpers import ad, adb, b200, oracle, assert_rel
 
 pytestmark = pytest.mark.gpu
 RNG = np.random.default_rng(23)
+_single = None
+
+
+def _device(kernel):
+    """"pair": the default handle (two SMs per 256 x 256 tile whenever M > 128); "single": one SM per 128 x 256 tile."""
+    global _single
+    if kernel == "pair":
+        return b200()
+    if _single is None:
+        _single = adb.devices.B200(0, flags=adb.devices.FLAG_SINGLE_SM_DOT)
+    return _single
 
 
 def _dot(dev, a, b, ta, tb, M, K, N):
@@ -20,12 +31,14 @@ def _dot(dev, a, b, ta, tb, M, K, N):
     return y.val().get()
 
 
+@pytest.mark.parametrize("kernel", ["pair", "single"])
 @pytest.mark.parametrize("ta,tb", [(False, False), (True, False), (False, True), (True, True)])
-@pytest.mark.parametrize("M,K,N", [(128, 64, 256), (256, 32, 512), (200, 100, 300), (384, 1024, 520), (96, 4096, 1000)])
-def test_tc_dot_matches_float64(M, K, N, ta, tb):
+@pytest.mark.parametrize("M,K,N", [(128, 64, 256), (256, 32, 512), (200, 100, 300), (384, 1024, 520), (96, 4096, 1000),
+                                   (260, 96, 136), (1024, 3200, 392), (640, 2048, 1000)])
+def test_tc_dot_matches_float64(M, K, N, ta, tb, kernel):
     a = RNG.standard_normal(M * K).astype(np.float32)
     b = RNG.standard_normal(K * N).astype(np.float32)
-    dev = b200()
+    dev = _device(kernel)
     got = _dot(dev, a, b, ta, tb, M, K, N)
     assert dev.stats()["tc_gemm_launches"] == 1, "expected the tensor-core kernel for this shape"
     A = a.reshape(K, M).T if ta else a.reshape(M, K)
@@ -38,11 +51,12 @@ def test_tc_dot_matches_float64(M, K, N, ta, tb):
     assert err < 1.5e-5, f"relative error {err:.3e} (3xTF32 should be at fp32 level)"
 
 
-@pytest.mark.parametrize("M,K,N,ta,tb", [(256, 16384, 256, False, False), (128, 65536, 256, True, False)])
-def test_tc_dot_error_does_not_grow_with_k(M, K, N, ta, tb):
+@pytest.mark.parametrize("kernel", ["pair", "single"])
+@pytest.mark.parametrize("M,K,N,ta,tb", [(256, 16384, 256, False, False), (128, 65536, 256, True, False), (512, 65536, 128, True, False)])
+def test_tc_dot_error_does_not_grow_with_k(M, K, N, ta, tb, kernel):
     a = RNG.standard_normal(M * K).astype(np.float32)
     b = RNG.standard_normal(K * N).astype(np.float32)
-    dev = b200()
+    dev = _device(kernel)
     got = _dot(dev, a, b, ta, tb, M, K, N)
     assert dev.stats()["tc_gemm_launches"] == 1
     A = a.reshape(K, M).T if ta else a.reshape(M, K)
@@ -70,11 +84,12 @@ def test_tc_dot_matches_oracle_and_simt():
     assert_rel("tc vs simt", got, ref, 1e-5)
 
 
-def test_tc_dot_exact_on_small_integers():
+@pytest.mark.parametrize("M,kernel", [(128, "single"), (768, "single"), (768, "pair")])
+def test_tc_dot_exact_on_small_integers(M, kernel):
     """Products of small integers are exact in every term of the split: the result must be exact."""
-    M, K, N = 128, 256, 256
+    K, N = 256, 512
     a = RNG.integers(-8, 9, M * K).astype(np.float32)
     b = RNG.integers(-8, 9, K * N).astype(np.float32)
-    got = _dot(b200(), a, b, False, False, M, K, N)
+    got = _dot(_device(kernel), a, b, False, False, M, K, N)
     ref = a.reshape(M, K).astype(np.int64) @ b.reshape(K, N).astype(np.int64)
     np.testing.assert_array_equal(np.asarray(got.data).reshape(M, N), ref.astype(np.float32))
