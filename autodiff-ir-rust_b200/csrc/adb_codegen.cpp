@@ -9,8 +9,9 @@
 // straight-line SSA body between load and store is spliced in from the plan.
 //
 // Arithmetic contract (matches the CPU restatement of the reference semantics):
-//   + and * are __fadd_rn / __fmul_rn (never contracted into FMA), 1/x is __frcp_rn,
-//   sqrt is __fsqrt_rn(fabsf(x)), comparisons give 1.0f / 0.0f against 0.0f
+//   + and * are __fadd_rn / __fmul_rn (never contracted into FMA), 1/x and sqrt(fabsf(x)) are the
+//   <= 1 ulp rcp.approx / sqrt.approx (or __frcp_rn / __fsqrt_rn when the plan asks for correctly rounded
+//   division), comparisons give 1.0f / 0.0f against 0.0f
 //   (src/devices/opencl/kernels/unary.rs:3-17), exp2f / log2f / sinf are CUDA's (<= 2 ulp).
 #include <algorithm>
 #include <cstdio>
@@ -27,6 +28,18 @@ struct Access {
     enum Mode { SCALAR, VEC4, GATHER } mode = SCALAR;
     int64_t lane_stride = 0;  // GATHER: element stride between the 4 lanes
 };
+
+// set for the duration of generate_kernels
+thread_local bool g_exact_div = false;
+
+// 1/x and sqrt(x) through the special-function unit: rcp.approx.f32 / sqrt.approx.f32 keep subnormal inputs and
+// results and are within 1 ulp, inside the 2-ulp bound the element-wise primitives are held to; the correctly
+// rounded forms cost 10 and 11 issue slots per element in kernels that are issue-bound
+const char* helpers() {
+    if (g_exact_div) return "";
+    return "__device__ __forceinline__ float adb_rcp(float x) { float r; asm(\"rcp.approx.f32 %0, %1;\" : \"=f\"(r) : \"f\"(x)); return r; }\n"
+           "__device__ __forceinline__ float adb_sqrt(float x) { float r; asm(\"sqrt.approx.f32 %0, %1;\" : \"=f\"(r) : \"f\"(x)); return r; }\n";
+}
 
 std::string hexf(float v) {
     uint32_t bits;
@@ -116,8 +129,8 @@ void emit_ssa(std::ostringstream& o, const KernelSpec& k, int vec, const std::ve
                 case E_EXP2: o << "exp2f(" << a << ")"; break;
                 case E_LOG2: o << "log2f(" << a << ")"; break;
                 case E_SIN: o << "sinf(" << a << ")"; break;
-                case E_RECIP: o << "__frcp_rn(" << a << ")"; break;
-                case E_SQRT: o << "__fsqrt_rn(fabsf(" << a << "))"; break;
+                case E_RECIP: o << (g_exact_div ? "__frcp_rn(" : "adb_rcp(") << a << ")"; break;
+                case E_SQRT: o << (g_exact_div ? "__fsqrt_rn(fabsf(" : "adb_sqrt(fabsf(") << a << "))"; break;
                 case E_EQZ: o << "(" << a << " == 0.0f ? 1.0f : 0.0f)"; break;
                 case E_GTZ: o << "(" << a << " > 0.0f ? 1.0f : 0.0f)"; break;
                 case E_LTZ: o << "(" << a << " < 0.0f ? 1.0f : 0.0f)"; break;
@@ -182,7 +195,7 @@ void gen_elw(KernelSpec& k) {
     for (size_t i = 0; i < k.outs.size(); i++) out_acc[i] = classify(k.outs[i].dst.subs, k.outs[i].dst.offset, vec, true);
 
     std::ostringstream o;
-    o << "struct Args { const float* in[" << std::max<size_t>(1, k.ins.size()) << "]; float* out[" << k.outs.size()
+    o << helpers() << "struct Args { const float* in[" << std::max<size_t>(1, k.ins.size()) << "]; float* out[" << k.outs.size()
       << "]; long long n; };\n";
     o << "extern \"C\" __global__ void __launch_bounds__(256) @ENTRY@(const __grid_constant__ Args a) {\n";
     o << "  const " << idx_t << " nv = (" << idx_t << ")(a.n / " << vec << ");\n";
@@ -247,7 +260,7 @@ void gen_reduce(KernelSpec& k) {
     const int64_t R = k.r, S = k.split;
     const int64_t chunk = k.chunk > 0 ? k.chunk : (R + S - 1) / S;  // summed elements per partial
     std::ostringstream o;
-    o << "struct Args { const float* in[" << std::max<size_t>(1, k.ins.size()) << "]; float* out[1]; long long n; };\n";
+    o << helpers() << "struct Args { const float* in[" << std::max<size_t>(1, k.ins.size()) << "]; float* out[1]; long long n; };\n";
 
     if (k.mode == 0) {
         // lanes along the summed axis: TPR threads cooperate on one row, 256/TPR rows per block
@@ -470,6 +483,7 @@ void plan_reduce(KernelSpec& k, int sm_count) {
 }
 
 void generate_kernels(Plan& plan) {
+    g_exact_div = plan.exact_div;
     for (auto& k : plan.kernels) {
         if (!k.source.empty()) continue;
         if (k.type == KernelSpec::ELW) gen_elw(k);

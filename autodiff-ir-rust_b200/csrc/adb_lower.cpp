@@ -83,6 +83,7 @@ class Lowerer {
 
     void run() {
         plan_.ir_commands = prog_.n_cmds;
+        plan_.exact_div = opt_.exact_div;
         is_dep_.assign(prog_.ids.size(), 0);
         for (auto d : prog_.dep) { info_[d].cross = true; is_dep_[d] = 1; }
         int seg = 0;

@@ -129,10 +129,12 @@ struct Plan {
     int n_steps = 0;
     size_t ir_commands = 0;
     uint64_t key = 0;
+    bool exact_div = false;  // 1/x and sqrt correctly rounded instead of the <= 1 ulp hardware approximations
 };
 
 struct LowerOptions {
     bool no_fusion = false;
+    bool exact_div = false;
     int64_t fuse_limit = 768;  // largest expression DAG fused into one kernel
     int rank = 0, world = 1;
     int sm_count = 148;        // B200: 148 SMs; reduce kernels split rows until every SM has work

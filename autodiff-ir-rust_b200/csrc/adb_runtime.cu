@@ -797,6 +797,7 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
         auto fresh = std::make_unique<CompiledPlan>();
         LowerOptions opt;
         opt.no_fusion = (d->flags & ADB_FLAG_NO_FUSION) != 0;
+        opt.exact_div = (d->flags & ADB_FLAG_EXACT_DIV) != 0;
         opt.rank = d->rank;
         opt.world = d->world;
         opt.sm_count = d->sm_count;
@@ -1104,6 +1105,7 @@ adb_status adb_lower_check(const uint8_t* blob, size_t nbytes, const adb_config*
         LowerOptions opt;
         if (cfg) {
             opt.no_fusion = (cfg->flags & ADB_FLAG_NO_FUSION) != 0;
+            opt.exact_div = (cfg->flags & ADB_FLAG_EXACT_DIV) != 0;
             opt.rank = cfg->rank;
             opt.world = cfg->world_size > 0 ? cfg->world_size : 1;
             if (opt.world > 1 && cfg->shard_batch) shard_program(prog, opt.rank, opt.world, int64_t(cfg->shard_batch));

@@ -81,6 +81,8 @@ typedef struct adb_config {
                                       next one (measured 2 % slower on 2 GPUs) */
 #define ADB_FLAG_SINGLE_SM_DOT 32u  /* keep the tcgen05 dot kernel on one SM per 128 x 256 tile instead of pairing two SMs
                                       (cta_group::2) on a 256 x 256 tile */
+#define ADB_FLAG_EXACT_DIV 64u      /* Recip and Sqrt correctly rounded (bit-identical to IEEE 1.0f/x and sqrtf) instead of the
+                                      special-function-unit forms (<= 1 ulp); costs ~10 issue slots per use */
 #define ADB_FLAG_PROFILE 8u        /* CUDA events around every kernel (fills the per-kind times of adb_stats);
                                       loop bodies are then launched kernel by kernel, not as graphs */
 

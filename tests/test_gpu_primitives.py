@@ -1,12 +1,13 @@
 """Every element-wise primitive on its own, against the CPU oracle.
 
-Tolerances: + * compare recip sqrt are bit-exact; exp2 / log2 / sin within 2 ulp (fp32), which is the
-bound stated for element-wise ops.
+Tolerances: + * compare are bit-exact; exp2 / log2 / sin within 2 ulp (fp32), which is the bound stated
+for element-wise ops; recip / sqrt within 1 ulp by default (special-function unit) and bit-exact on a handle
+created with FLAG_EXACT_DIV.
 """
 import numpy as np
 import pytest
 
-from helpers import ad, run_both, assert_exact, assert_ulp
+from helpers import ad, adb, oracle, run_both, assert_exact, assert_ulp
 
 pytestmark = pytest.mark.gpu
 
@@ -49,7 +50,7 @@ def _unary(method, x):
 
 @pytest.mark.parametrize("method,kind,ulp", [
     ("exp2", "exp", 2), ("log2", "positive", 2), ("sin", "angle", 2), ("sin", "normal", 2),
-    ("recip", "wide", 0), ("sqrt", "wide", 0),
+    ("recip", "wide", 1), ("sqrt", "wide", 1), ("recip", "positive", 1), ("sqrt", "positive", 1),
 ])
 def test_unary(method, kind, ulp):
     x = _data(kind)
@@ -59,6 +60,18 @@ def test_unary(method, kind, ulp):
         assert_exact(method, got["y"], want["y"])
     else:
         assert_ulp(method, got["y"], want["y"], ulp)
+
+
+@pytest.mark.parametrize("method,kind", [("recip", "wide"), ("sqrt", "wide"), ("recip", "positive")])
+def test_division_is_correctly_rounded_on_request(method, kind):
+    x = _data(kind)
+    dev = adb.devices.B200(0, flags=adb.devices.FLAG_EXACT_DIV)
+    try:
+        with np.errstate(all="ignore"):
+            want, got = _unary(method, x)(oracle()), _unary(method, x)(dev)
+    finally:
+        dev.close()
+    assert_exact(method, got["y"], want["y"])
 
 
 @pytest.mark.parametrize("op", ["add", "mul"])
