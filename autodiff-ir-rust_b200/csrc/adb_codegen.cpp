@@ -175,18 +175,29 @@ void finish(KernelSpec& k, const std::string& body, const char* prefix) {
 }
 
 // -------------------------------------------------------------------------------- element-wise
+int elw_vec_impl(const KernelSpec& k) {
+    int vec = 4;
+    if (k.n % 4) vec = 1;
+    for (auto& i : k.ins)
+        if (!lanes_ok(i.subs)) vec = 1;
+    for (auto& o : k.outs) {
+        if (!lanes_ok(o.dst.subs)) vec = 1;
+        if (o.dst.subs.empty() || o.dst.subs.back().stride == 0) vec = 1;
+    }
+    if (!k.reds.empty() && k.q2 % 4) vec = 1;
+    return vec;
+}
+
+void gen_elw_red(KernelSpec& k);
+
 void gen_elw(KernelSpec& k) {
+    if (!k.reds.empty()) { gen_elw_red(k); return; }
     std::vector<const Operand*> ops;
     for (auto& i : k.ins) ops.push_back(&i);
     for (auto& o : k.outs) ops.push_back(&o.dst);
     k.wide_index = needs_wide(k.n, ops);
     const char* idx_t = k.wide_index ? "long long" : "unsigned int";
-    int vec = 4;
-    if (k.n % 4) vec = 1;
-    for (auto* o : ops)
-        if (!lanes_ok(o->subs)) vec = 1;
-    for (auto& o : k.outs)
-        if (o.dst.subs.empty() || o.dst.subs.back().stride == 0) vec = 1;
+    const int vec = elw_vec_impl(k);
     k.vec = vec;
     k.threads = 256;
 
@@ -235,6 +246,118 @@ void gen_elw(KernelSpec& k) {
     }
     o << "  }\n}\n";
     finish(k, o.str(), "adb_elw");
+}
+
+// Element-wise pass that also sums some of its values.  The flat index space is walked as [P, Q]
+// (i = p * Q + q): a block covers 8 rows (one per warp) by 32 * vec columns per iteration and a chunk of rows
+// (blockIdx.y) in total.  Sums over q (axis 0): warp-shuffle tree, one partial per row and column tile.  Sums over
+// p (axis 1): per-thread accumulators over the rows of the chunk, combined across the 8 warps in shared memory
+// in a fixed order, one partial per column and row chunk.  The partials are added by a small reduce step.
+void gen_elw_red(KernelSpec& k) {
+    std::vector<const Operand*> ops;
+    for (auto& i : k.ins) ops.push_back(&i);
+    for (auto& o : k.outs) ops.push_back(&o.dst);
+    k.wide_index = needs_wide(k.n, ops);
+    const char* idx_t = k.wide_index ? "long long" : "unsigned int";
+    const int vec = elw_vec_impl(k);
+    k.vec = vec;
+    k.threads = 256;
+    const int64_t P = k.p2, Q = k.q2;
+    const int64_t W = 32 * vec;
+    const int64_t tiles_q = (Q + W - 1) / W;
+
+    std::vector<Access> in_acc(k.ins.size()), out_acc(k.outs.size());
+    for (size_t i = 0; i < k.ins.size(); i++) in_acc[i] = classify(k.ins[i].subs, k.ins[i].offset, vec, false);
+    for (size_t i = 0; i < k.outs.size(); i++) out_acc[i] = classify(k.outs[i].dst.subs, k.outs[i].dst.offset, vec, true);
+    bool any_col = false;
+    for (auto& r : k.reds) any_col = any_col || r.axis == 1;
+
+    std::ostringstream o;
+    o << helpers() << "struct Args { const float* in[" << std::max<size_t>(1, k.ins.size()) << "]; float* out["
+      << k.outs.size() + k.reds.size() << "]; long long n; };\n";
+    o << "extern \"C\" __global__ void __launch_bounds__(256) @ENTRY@(const __grid_constant__ Args a) {\n";
+    if (any_col) o << "  __shared__ float sm[8][" << W << "];\n";
+    o << "  const unsigned int lane = threadIdx.x & 31u, wrp = threadIdx.x >> 5;\n";
+    o << "  const " << idx_t << " c = ((" << idx_t << ")blockIdx.x * 32u + lane) * " << vec << "u;\n";
+    o << "  const bool cok = c < " << Q << ";\n";
+    o << "  const " << idx_t << " p_beg = (" << idx_t << ")blockIdx.y * " << k.row_chunk << ";\n";
+    o << "  const " << idx_t << " p_end = p_beg + " << k.row_chunk << " < " << P << " ? p_beg + " << k.row_chunk << " : " << P << ";\n";
+    for (size_t r = 0; r < k.reds.size(); r++)
+        if (k.reds[r].axis == 1)
+            for (int l = 0; l < vec; l++) o << "  float ca" << r << "_" << l << " = 0.0f;\n";
+    o << "  for (" << idx_t << " pb = p_beg; pb < p_end; pb += 8) {\n";
+    o << "    const " << idx_t << " p = pb + wrp;\n";
+    for (size_t r = 0; r < k.reds.size(); r++)
+        if (k.reds[r].axis == 0) o << "    float rs" << r << " = 0.0f;\n";
+    o << "    if (cok && p < p_end) {\n";
+    o << "      const " << idx_t << " i = p * " << Q << " + c;\n";
+    std::vector<std::pair<std::vector<Sub>, std::string>> seen;
+    auto offset_of = [&](const std::vector<Sub>& subs) {
+        for (auto& s : seen)
+            if (s.first == subs) return s.second;
+        std::ostringstream pre;
+        std::string tag = std::to_string(seen.size());
+        std::string e = offset_expr(subs, "i", pre, tag, idx_t);
+        o << pre.str();
+        std::string var = "o" + tag;
+        o << "      const " << idx_t << " " << var << " = " << e << ";\n";
+        seen.push_back({subs, var});
+        return var;
+    };
+    std::vector<std::string> in_off(k.ins.size()), out_off(k.outs.size());
+    for (size_t i = 0; i < k.ins.size(); i++) in_off[i] = offset_of(k.ins[i].subs);
+    for (size_t i = 0; i < k.outs.size(); i++) out_off[i] = offset_of(k.outs[i].dst.subs);
+    std::vector<std::string> names;
+    emit_loads(o, k, vec, in_acc, in_off, names, "      ");
+    emit_ssa(o, k, vec, names, in_acc, "      ");
+    for (size_t i = 0; i < k.outs.size(); i++) {
+        std::string p = "a.out[" + std::to_string(i) + "]";
+        std::string v = "v" + std::to_string(k.outs[i].ssa);
+        if (vec == 1)
+            o << "      " << p << "[" << out_off[i] << "] = " << v << "_0;\n";
+        else if (out_acc[i].mode == Access::VEC4)
+            o << "      *reinterpret_cast<float4*>(" << p << " + (" << out_off[i] << ")) = make_float4(" << v << "_0, " << v
+              << "_1, " << v << "_2, " << v << "_3);\n";
+        else
+            for (int l = 0; l < 4; l++)
+                o << "      " << p << "[(" << out_off[i] << ") + " << l * out_acc[i].lane_stride << "] = " << v << "_" << l << ";\n";
+    }
+    for (size_t r = 0; r < k.reds.size(); r++) {
+        std::string v = "v" + std::to_string(k.reds[r].ssa);
+        if (k.reds[r].axis == 1) {
+            for (int l = 0; l < vec; l++) o << "      ca" << r << "_" << l << " = __fadd_rn(ca" << r << "_" << l << ", " << v << "_" << l << ");\n";
+        } else if (vec == 4) {
+            o << "      rs" << r << " = __fadd_rn(__fadd_rn(" << v << "_0, " << v << "_1), __fadd_rn(" << v << "_2, " << v << "_3));\n";
+        } else {
+            o << "      rs" << r << " = " << v << "_0;\n";
+        }
+    }
+    o << "    }\n";
+    for (size_t r = 0; r < k.reds.size(); r++) {
+        if (k.reds[r].axis != 0) continue;
+        std::string q = "a.out[" + std::to_string(k.outs.size() + r) + "]";
+        o << "    for (int s = 16; s > 0; s >>= 1) rs" << r << " = __fadd_rn(rs" << r << ", __shfl_xor_sync(0xffffffffu, rs" << r << ", s));\n";
+        o << "    if (lane == 0 && p < p_end) " << q << "[(size_t)p * " << tiles_q << " + blockIdx.x] = rs" << r << ";\n";
+    }
+    o << "  }\n";
+    for (size_t r = 0; r < k.reds.size(); r++) {
+        if (k.reds[r].axis != 1) continue;
+        std::string q = "a.out[" + std::to_string(k.outs.size() + r) + "]";
+        for (int l = 0; l < vec; l++) o << "  sm[wrp][lane * " << vec << " + " << l << "] = ca" << r << "_" << l << ";\n";
+        o << "  __syncthreads();\n";
+        o << "  if (wrp == 0 && cok) {\n";
+        for (int l = 0; l < vec; l++) {
+            o << "    float t" << l << " = sm[0][lane * " << vec << " + " << l << "];\n";
+            o << "    for (int w = 1; w < 8; w++) t" << l << " = __fadd_rn(t" << l << ", sm[w][lane * " << vec << " + " << l << "]);\n";
+        }
+        o << "    float* dst = " << q << " + (size_t)blockIdx.y * " << Q << " + c;\n";
+        if (vec == 4) o << "    *reinterpret_cast<float4*>(dst) = make_float4(t0, t1, t2, t3);\n";
+        else o << "    dst[0] = t0;\n";
+        o << "  }\n";
+        o << "  __syncthreads();\n";
+    }
+    o << "}\n";
+    finish(k, o.str(), "adb_elwsum");
 }
 
 // -------------------------------------------------------------------------------- reduce
@@ -482,10 +605,12 @@ void plan_reduce(KernelSpec& k, int sm_count) {
     }
 }
 
+int elw_vec(const KernelSpec& k) { return elw_vec_impl(k); }
+
 void generate_kernels(Plan& plan) {
     g_exact_div = plan.exact_div;
     for (auto& k : plan.kernels) {
-        if (!k.source.empty()) continue;
+        if (!k.source.empty() || k.dead) continue;
         if (k.type == KernelSpec::ELW) gen_elw(k);
         else gen_reduce(k);
     }

@@ -98,6 +98,7 @@ class Lowerer {
         (void)stopped;
         finalize_results();
         plan_.n_steps = pos_;
+        fuse_reductions();
         plan_arena();
     }
 
@@ -1182,6 +1183,386 @@ class Lowerer {
         results_done_ = true;
     }
 
+    // ------------------------------------------------------------------ sums fused into element-wise passes
+    // A Sum whose summand is built from the operands an element-wise kernel streams anyway (or from a value that
+    // kernel writes) costs a second pass over the same memory when it runs as a kernel of its own: config 2's
+    // loss and bias gradient re-read both 256 MB inputs, a bias gradient re-reads the activation gradient that the
+    // kernel before it wrote.  This pass moves such a reduce step into the element-wise kernel as a side sum
+    // (KernelSpec::reds) when the two walk the same index space and no other step gets in the way.  The reference
+    // fuses in the other direction only (a reduce followed by element-wise work on its result,
+    // src/kernel/fusion/reduce_elw.rs:12-144).
+    static constexpr int POS_SCALE = 64;       // room between two original step positions for moved / added steps
+    static constexpr int64_t FUSE_MIN_ELEMS = int64_t(1) << 18;
+
+    void step_rw(const Step& s, std::vector<int>& rd, std::vector<int>& wr) const {
+        rd.clear();
+        wr.clear();
+        switch (s.kind) {
+        case Step::ELW: case Step::REDUCE: {
+            const KernelSpec& k = plan_.kernels[size_t(s.kernel)];
+            for (auto& in : k.ins) rd.push_back(in.buf);
+            for (auto& o : k.outs) wr.push_back(o.dst.buf);
+            for (auto& r : k.reds) wr.push_back(r.dst.buf);
+            break;
+        }
+        case Step::GEMM: rd = {s.gemm.a, s.gemm.b}; wr = {s.gemm.c}; break;
+        case Step::UPLOAD: wr = {s.buf}; break;
+        case Step::ALLREDUCE: rd = {s.buf}; wr = {s.buf}; break;
+        default: break;
+        }
+    }
+    static bool hits(const std::vector<int>& a, const std::vector<int>& b) {
+        for (int x : a)
+            for (int y : b)
+                if (x == y) return true;
+        return false;
+    }
+    static bool is_barrier(const Step& s) { return s.kind == Step::WHILE || s.kind == Step::IF || s.kind == Step::EXIT; }
+
+    void scale_positions(StepBlock& blk) {
+        for (auto& s : blk.steps) {
+            s.pos *= POS_SCALE;
+            if (s.body) scale_positions(*s.body);
+            for (auto& br : s.branches) scale_positions(*br.body);
+            if (s.else_body) scale_positions(*s.else_body);
+        }
+    }
+
+    void fuse_reductions() {
+        if (opt_.no_fusion || opt_.no_reduce_fusion) return;
+        if (pos_ >= INT_MAX / POS_SCALE - 1) return;
+        scale_positions(plan_.main);
+        for (auto& b : plan_.bufs) {
+            if (b.first != INT_MAX) b.first *= POS_SCALE;
+            if (b.last >= 0) b.last *= POS_SCALE;
+        }
+        for (auto& sp : loop_spans_) { sp.first *= POS_SCALE; sp.second *= POS_SCALE; }
+        pos_ *= POS_SCALE;
+        fuse_block(plan_.main);
+    }
+
+    void fuse_block(StepBlock& blk) {
+        for (auto& s : blk.steps) {
+            if (s.body) fuse_block(*s.body);
+            for (auto& br : s.branches) fuse_block(*br.body);
+            if (s.else_body) fuse_block(*s.else_body);
+        }
+        for (size_t e = 0; e < blk.steps.size(); e++) {
+            if (blk.steps[e].kind != Step::ELW) continue;
+            if (plan_.kernels[size_t(blk.steps[e].kernel)].n < FUSE_MIN_ELEMS) continue;
+            bool again = true;
+            while (again && plan_.kernels[size_t(blk.steps[e].kernel)].reds.size() < 4) {
+                again = false;
+                // straight-line neighbourhood of the kernel
+                size_t lo = e, hi = e;
+                while (lo > 0 && !is_barrier(blk.steps[lo - 1]) && e - (lo - 1) <= 48) lo--;
+                while (hi + 1 < blk.steps.size() && !is_barrier(blk.steps[hi + 1]) && (hi + 1) - e <= 48) hi++;
+                for (size_t r = lo; r <= hi && !again; r++) {
+                    if (r == e || blk.steps[r].kind != Step::REDUCE) continue;
+                    size_t e_now = e;
+                    if (try_fuse(blk, r, e_now)) {
+                        e = e_now;
+                        again = true;
+                    }
+                }
+            }
+        }
+    }
+
+    // flat digits of a reduce operand when the reduce's [V, R] space is laid over the flat index with the kept axis
+    // outermost (x_major) or innermost
+    static std::vector<Sub> flat_digits(const Operand& o, bool x_major) {
+        std::vector<Sub> d;
+        if (x_major) { d = o.xsubs; d.insert(d.end(), o.subs.begin(), o.subs.end()); }
+        else { d = o.subs; d.insert(d.end(), o.xsubs.begin(), o.xsubs.end()); }
+        canon_subs(d);
+        return d;
+    }
+
+    // tries to turn the reduce at index r into a side sum of the element-wise kernel at index e; on success the
+    // step list is rewritten and e is updated to the kernel's new index
+    bool try_fuse(StepBlock& blk, size_t r, size_t& e) {
+        auto& steps = blk.steps;
+        const KernelSpec& rk0 = plan_.kernels[size_t(steps[r].kernel)];
+        // second pass of a split reduce: handled together with its first pass
+        if (r > 0 && steps[r - 1].kind == Step::REDUCE && r - 1 != e) {
+            const KernelSpec& prev = plan_.kernels[size_t(steps[r - 1].kernel)];
+            if (prev.scratch >= 0 && rk0.ins.size() == 1 && rk0.ins[0].buf == prev.scratch) return false;
+        }
+        size_t r_end = r;  // last step of the reduce group
+        Operand final_dst = rk0.outs[0].dst;
+        int old_scratch = -1;
+        if (rk0.scratch >= 0) {
+            if (r + 1 >= steps.size() || steps[r + 1].kind != Step::REDUCE || r + 1 == e) return false;
+            const KernelSpec& k2 = plan_.kernels[size_t(steps[r + 1].kernel)];
+            if (k2.ins.size() != 1 || k2.ins[0].buf != rk0.scratch) return false;
+            r_end = r + 1;
+            final_dst = k2.outs[0].dst;
+            old_scratch = rk0.scratch;
+        }
+        if (r < e && r_end >= e) return false;
+        const bool sink = r < e;  // the reduce runs before the kernel today and moves down to it
+        KernelSpec& ek = plan_.kernels[size_t(steps[e].kernel)];
+        const int64_t V = rk0.n, R = rk0.r;
+        if (V <= 0 || R <= 0 || V * R != ek.n) return false;
+
+        // dependences
+        std::vector<int> rd, wr, e_rd, e_wr, r_rd;
+        step_rw(steps[e], e_rd, e_wr);
+        for (auto& in : rk0.ins) r_rd.push_back(in.buf);
+        const std::vector<int> r_wr = {final_dst.buf};
+        if (hits(e_rd, r_wr) && sink) return false;  // the kernel consumes the sum
+        std::vector<size_t> moved;                    // sink: steps between the reduce and the kernel that depend on the sum
+        if (sink) {
+            // (a summand input that the kernel overwrites is looked at below: allowed only as an in-place update
+            //  of the very elements the same thread reads)
+            std::vector<int> tainted = r_wr;
+            for (size_t q = r_end + 1; q < e; q++) {
+                step_rw(steps[q], rd, wr);
+                if (hits(rd, tainted)) {
+                    moved.push_back(q);
+                    tainted.insert(tainted.end(), wr.begin(), wr.end());
+                }
+            }
+            if (hits(e_rd, tainted)) return false;
+            if (moved.size() > 24) return false;
+            // a moved step must not cross a step it conflicts with; the summand's inputs must stay untouched
+            for (size_t q = r_end + 1; q <= e; q++) {
+                if (std::find(moved.begin(), moved.end(), q) != moved.end()) continue;
+                step_rw(steps[q], rd, wr);
+                if (q != e && hits(wr, r_rd)) return false;
+                if (hits(wr, r_wr)) return false;
+                for (size_t m : moved) {
+                    if (m > q) continue;
+                    std::vector<int> mrd, mwr;
+                    step_rw(steps[m], mrd, mwr);
+                    if (hits(wr, mrd) || hits(wr, mwr) || hits(rd, mwr)) return false;
+                }
+            }
+        } else {
+            for (size_t q = e + 1; q < r; q++) {
+                step_rw(steps[q], rd, wr);
+                if (hits(wr, r_rd) || hits(rd, r_wr) || hits(wr, r_wr)) return false;
+            }
+            if (hits(e_wr, r_wr)) return false;
+        }
+
+        // steps that earlier fusions parked right behind the kernel: the new ones line up after them, so they must
+        // not depend on each other in either direction; and there must be positions left
+        const int e_pos = steps[e].pos;
+        {
+            int used = 0;
+            std::vector<int> nrd = {final_dst.buf}, nwr = {final_dst.buf};
+            for (size_t m : moved) {
+                std::vector<int> mrd, mwr;
+                step_rw(steps[m], mrd, mwr);
+                nrd.insert(nrd.end(), mrd.begin(), mrd.end());
+                nwr.insert(nwr.end(), mwr.begin(), mwr.end());
+            }
+            for (size_t q = e + 1; q < steps.size() && steps[q].pos < e_pos + POS_SCALE; q++) {
+                used++;
+                step_rw(steps[q], rd, wr);
+                if (hits(rd, nwr) || hits(wr, nrd) || hits(wr, nwr)) return false;
+            }
+            if (used + 1 + int(moved.size()) >= POS_SCALE - 2) return false;
+        }
+        std::vector<int> dead_kernels;
+        for (size_t q = r; q <= r_end; q++) dead_kernels.push_back(steps[q].kernel);
+
+        // index spaces: which of the two layouts of [V, R] over the flat index matches the kernel's operands?
+        struct Match { bool ok = false; std::vector<int> in_of; std::vector<int> val_of; };
+        auto match = [&](bool x_major) {
+            Match m;
+            m.in_of.assign(rk0.ins.size(), -1);
+            m.val_of.assign(rk0.ins.size(), -1);
+            for (size_t i = 0; i < rk0.ins.size(); i++) {
+                const Operand& o = rk0.ins[i];
+                std::vector<Sub> d = flat_digits(o, x_major);
+                const bool written_by_e = std::find(e_wr.begin(), e_wr.end(), o.buf) != e_wr.end();
+                if (written_by_e && sink) {
+                    // in-place update: the summand wants the old value, which the kernel loads from the same
+                    // element before it stores the new one -- every access of the kernel to this buffer must be
+                    // this very access
+                    for (size_t j = 0; j < ek.ins.size(); j++) {
+                        std::vector<Sub> ed = ek.ins[j].subs;
+                        canon_subs(ed);
+                        if (ek.ins[j].buf == o.buf && ek.ins[j].offset == o.offset && ed == d) m.in_of[i] = int(j);
+                    }
+                    if (m.in_of[i] < 0) return m;
+                    for (auto& in2 : ek.ins)
+                        if (in2.buf == o.buf && !in2.same_access(ek.ins[size_t(m.in_of[i])])) return m;
+                    for (auto& o2 : ek.outs) {
+                        if (o2.dst.buf != o.buf) continue;
+                        std::vector<Sub> od = o2.dst.subs;
+                        canon_subs(od);
+                        if (o2.dst.offset != o.offset || od != d) return m;
+                    }
+                } else if (written_by_e) {
+                    for (size_t j = 0; j < ek.outs.size(); j++) {
+                        std::vector<Sub> ed = ek.outs[j].dst.subs;
+                        canon_subs(ed);
+                        if (ek.outs[j].dst.buf == o.buf && ek.outs[j].dst.offset == o.offset && ed == d) m.val_of[i] = ek.outs[j].ssa;
+                    }
+                    if (m.val_of[i] < 0) return m;
+                } else {
+                    for (size_t j = 0; j < ek.ins.size(); j++) {
+                        std::vector<Sub> ed = ek.ins[j].subs;
+                        canon_subs(ed);
+                        if (ek.ins[j].buf == o.buf && ek.ins[j].offset == o.offset && ed == d) m.in_of[i] = int(j);
+                    }
+                    if (m.in_of[i] < 0) return m;
+                }
+            }
+            m.ok = true;
+            return m;
+        };
+        int axis = -1;
+        int64_t P = 0, Q = 0;
+        Match mt;
+        for (int t = 0; t < 2 && axis < 0; t++) {
+            const bool x_major = t == 0;
+            const int64_t p = x_major ? V : R, q = x_major ? R : V;
+            if (!ek.reds.empty() && (p != ek.p2 || q != ek.q2)) continue;
+            if (q < 128 || p < 8) continue;
+            Match m = match(x_major);
+            if (!m.ok) continue;
+            mt = std::move(m);
+            axis = x_major ? 0 : 1;
+            P = p;
+            Q = q;
+        }
+        if (axis < 0) return false;
+        // the kernel must keep its vector width
+        {
+            KernelSpec probe;
+            probe.n = ek.n;
+            probe.ins = ek.ins;
+            probe.outs = ek.outs;
+            if (elw_vec(probe) == 4 && Q % 4) return false;
+        }
+
+        // splice the summand into the kernel's SSA
+        std::map<std::tuple<int, int, uint32_t, int, int, int>, int> known;
+        auto key_of = [](const Ssa& s) {
+            uint32_t bits;
+            std::memcpy(&bits, &s.c, 4);
+            // + and * commute exactly: the two kernels may have ordered the same operands differently
+            int a = s.kind == Ssa::OP ? s.a : -1, b = s.kind == Ssa::OP ? s.b : -1;
+            if (s.kind == Ssa::OP && b >= 0 && a > b) std::swap(a, b);
+            return std::make_tuple(int(s.kind), s.kind == Ssa::LOAD ? s.operand : -1, s.kind == Ssa::CONST ? bits : 0u,
+                                   s.kind == Ssa::OP ? int(s.op) : -1, a, b);
+        };
+        for (size_t i = 0; i < ek.ssa.size(); i++) known.emplace(key_of(ek.ssa[i]), int(i));
+        std::vector<int> remap(rk0.ssa.size(), -1);
+        for (size_t i = 0; i < rk0.ssa.size(); i++) {
+            Ssa s = rk0.ssa[i];
+            if (s.kind == Ssa::LOAD) {
+                if (mt.val_of[size_t(s.operand)] >= 0) { remap[i] = mt.val_of[size_t(s.operand)]; continue; }
+                s.operand = mt.in_of[size_t(s.operand)];
+            } else if (s.kind == Ssa::OP) {
+                s.a = remap[size_t(s.a)];
+                if (s.b >= 0) s.b = remap[size_t(s.b)];
+            }
+            auto it = known.find(key_of(s));
+            if (it != known.end()) { remap[i] = it->second; continue; }
+            ek.ssa.push_back(s);
+            remap[i] = int(ek.ssa.size()) - 1;
+            known.emplace(key_of(s), remap[i]);
+        }
+
+        // launch geometry and the partial-sum buffer
+        if (ek.reds.empty()) {
+            ek.p2 = P;
+            ek.q2 = Q;
+            const int vec = elw_vec(ek) == 4 && Q % 4 == 0 ? 4 : 1;
+            const int64_t tiles_q = (Q + 32 * vec - 1) / (32 * vec);
+            // at least 32 rows per block so that the cross-warp combine and the partial store are amortised
+            int64_t chunks = std::max<int64_t>(1, std::min<int64_t>((int64_t(opt_.sm_count) * 16 + tiles_q - 1) / tiles_q, (P + 31) / 32));
+            int64_t rows = (P + chunks - 1) / chunks;
+            ek.row_chunk = (rows + 7) / 8 * 8;
+        }
+        KernelSpec::Red red;
+        red.ssa = remap[size_t(rk0.outs[0].ssa)];
+        red.axis = axis;
+        ek.reds.push_back(red);  // (elw_vec looks at q2 only once a side sum exists)
+        const int vec = elw_vec(ek);
+        const int64_t tiles_q = (Q + 32 * vec - 1) / (32 * vec);
+        const int64_t chunks_p = (P + ek.row_chunk - 1) / ek.row_chunk;
+        const int64_t parts = axis == 0 ? tiles_q : chunks_p;
+        const int64_t kept = axis == 0 ? P : Q;
+        const int scratch = temp_buffer(kept * parts);
+        KernelSpec& ek2 = plan_.kernels[size_t(steps[e].kernel)];  // (temp_buffer does not move kernels; kept for clarity)
+        ek2.reds.back().dst.buf = scratch;
+        ek2.reds.back().dst.subs = {{kept * parts, 1}};
+
+        // second pass: partials -> the reduce's own destination
+        KernelSpec k2;
+        k2.type = KernelSpec::REDUCE;
+        k2.n = kept;
+        k2.r = parts;
+        Operand in;
+        in.buf = scratch;
+        if (axis == 0) {
+            if (kept > 1) in.xsubs = {{kept, parts}};
+            if (parts > 1) in.subs = {{parts, 1}};
+        } else {
+            if (kept > 1) in.xsubs = {{kept, 1}};
+            if (parts > 1) in.subs = {{parts, kept}};
+        }
+        k2.ins.push_back(in);
+        Ssa ld;
+        ld.kind = Ssa::LOAD;
+        ld.operand = 0;
+        k2.ssa.push_back(ld);
+        KernelSpec::Out fo;
+        fo.ssa = 0;
+        fo.dst = final_dst;
+        k2.outs.push_back(fo);
+        plan_reduce(k2, opt_.sm_count);
+        k2.split = 1;
+        k2.chunk = k2.r;
+        plan_.kernels.push_back(std::move(k2));
+        const int k2_index = int(plan_.kernels.size()) - 1;
+
+        // rewrite the step list: [.. reduce group .. moved .. E ..] -> [.. E, (earlier tails), second pass, moved ..]
+        std::vector<Step> tail;
+        {
+            Step s2;
+            s2.kind = Step::REDUCE;
+            s2.kernel = k2_index;
+            tail.push_back(std::move(s2));
+        }
+        for (size_t m : moved) tail.push_back(std::move(steps[m]));
+        std::vector<size_t> drop = moved;
+        for (size_t q = r; q <= r_end; q++) drop.push_back(q);
+        std::sort(drop.begin(), drop.end());
+        std::vector<Step> out;
+        out.reserve(steps.size() + 1);
+        size_t new_e = 0;
+        for (size_t q = 0; q < steps.size(); q++) {
+            if (std::binary_search(drop.begin(), drop.end(), q)) continue;
+            if (q == e) new_e = out.size();
+            out.push_back(std::move(steps[q]));
+        }
+        size_t ins_at = new_e + 1;
+        int next_pos = e_pos + 1;
+        while (ins_at < out.size() && out[ins_at].pos < e_pos + POS_SCALE) { next_pos = out[ins_at].pos + 1; ins_at++; }
+        for (auto& t : tail) {
+            t.pos = next_pos++;
+            std::vector<int> trd, twr;
+            step_rw(t, trd, twr);
+            for (int b : trd) touch(b, t.pos);
+            for (int b : twr) touch(b, t.pos);
+        }
+        touch(scratch, e_pos);
+        out.insert(out.begin() + long(ins_at), std::make_move_iterator(tail.begin()), std::make_move_iterator(tail.end()));
+        steps = std::move(out);
+        for (size_t q = 0; q < dead_kernels.size(); q++) plan_.kernels[size_t(dead_kernels[q])].dead = true;
+        if (old_scratch >= 0) { plan_.bufs[size_t(old_scratch)].first = INT_MAX; plan_.bufs[size_t(old_scratch)].last = -1; }
+        e = new_e;
+        return true;
+    }
+
     // ------------------------------------------------------------------ arena
     void plan_arena() {
         auto& bufs = plan_.bufs;
@@ -1277,6 +1658,9 @@ static void dump_block(const Plan& p, const StepBlock& b, int ind, bool src, std
                 o << pad << "    in  " << p.bufs[in.buf].name << "+" << in.offset << " " << (s.kind == Step::REDUCE ? subs_str(in.xsubs) + "," : "") << subs_str(in.subs) << "\n";
             for (auto& out : k.outs)
                 o << pad << "    out " << p.bufs[out.dst.buf].name << "+" << out.dst.offset << " " << (s.kind == Step::REDUCE ? subs_str(out.dst.xsubs) : subs_str(out.dst.subs)) << "\n";
+            for (auto& rd : k.reds)
+                o << pad << "    sum v" << rd.ssa << " over " << (rd.axis == 0 ? "columns" : "rows") << " of [" << k.p2 << "," << k.q2
+                  << "] -> " << p.bufs[rd.dst.buf].name << " " << subs_str(rd.dst.subs) << " (rows per block " << k.row_chunk << ")\n";
             if (src) {
                 for (size_t i = 0; i < k.ssa.size(); i++) {
                     auto& x = k.ssa[i];
@@ -1325,7 +1709,9 @@ static void dump_block(const Plan& p, const StepBlock& b, int ind, bool src, std
 
 std::string dump_plan(const Plan& plan, bool with_source) {
     std::ostringstream o;
-    o << "plan: " << plan.ir_commands << " IR commands -> " << plan.n_steps << " steps, " << plan.kernels.size()
+    size_t live = 0;
+    for (auto& k : plan.kernels) live += !k.dead;
+    o << "plan: " << plan.ir_commands << " IR commands -> " << plan.n_steps << " steps, " << live
       << " kernels, arena " << plan.arena_bytes << " B, " << plan.bufs.size() << " buffers\n";
     dump_block(plan, plan.main, 0, with_source, o);
     o << "results:";

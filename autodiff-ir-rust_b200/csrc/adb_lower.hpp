@@ -17,6 +17,10 @@ void lower_program(Program& prog, Plan& plan, const LowerOptions& opt);
 // width, split factor); needed while lowering because a split adds a scratch buffer and a second pass.
 void plan_reduce(KernelSpec& k, int sm_count);
 
+// Elements per thread an element-wise kernel will use (4 when every operand's innermost digit can hold
+// four consecutive lanes, else 1); the lowering needs it to size the partial-sum buffers of fused sums.
+int elw_vec(const KernelSpec& k);
+
 // Fills KernelSpec::source / entry / launch shape for every kernel of the plan.
 void generate_kernels(Plan& plan);
 

@@ -56,6 +56,19 @@ struct KernelSpec {
         Operand dst;
     };
     std::vector<Out> outs;  // REDUCE: one entry; `ssa` is the summand, dst is indexed by x
+    // ELW only: sums computed in the same pass.  The index space is then walked as [p2, q2] (i = p * q2 + q) by
+    // blocks of 8 rows x 32*vec columns; axis 0 = sum over q (one partial per row and column tile, dst holds
+    // [p2][tiles_q]), axis 1 = sum over p (one partial per column and row chunk, dst holds [chunks_p][q2]).
+    // A small REDUCE step after the kernel adds the partials up.
+    struct Red {
+        int ssa = -1;
+        int axis = 0;
+        Operand dst;  // scratch buffer of the partial sums (contiguous)
+    };
+    std::vector<Red> reds;
+    int64_t p2 = 0, q2 = 0;
+    int64_t row_chunk = 0;  // rows per blockIdx.y (a multiple of 8)
+    bool dead = false;      // no step refers to this kernel any more (its work moved into another kernel)
     // filled in by the code generator
     std::string source, entry;
     int vec = 1;            // elements per thread along the innermost digit
@@ -134,6 +147,7 @@ struct Plan {
 
 struct LowerOptions {
     bool no_fusion = false;
+    bool no_reduce_fusion = false;  // keep every Sum in a kernel of its own
     bool exact_div = false;
     int64_t fuse_limit = 768;  // largest expression DAG fused into one kernel
     int rank = 0, world = 1;

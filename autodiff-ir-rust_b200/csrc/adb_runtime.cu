@@ -257,17 +257,24 @@ class Executor {
     }
 
     void launch_kernel(const KernelSpec& k, int slot) {
-        // Args { const float* in[max(1,NI)]; float* out[NO]; long long n; }
+        // Args { const float* in[max(1,NI)]; float* out[NO + sums]; long long n; }
         std::vector<uint64_t> args;
         size_t ni = std::max<size_t>(1, k.ins.size());
-        args.resize(ni + k.outs.size() + 1, 0);
+        const size_t no = k.outs.size() + k.reds.size();
+        args.resize(ni + no + 1, 0);
         for (size_t i = 0; i < k.ins.size(); i++) args[i] = uint64_t(uintptr_t(buf_ptr(k.ins[i].buf, k.ins[i].offset)));
         for (size_t i = 0; i < k.outs.size(); i++)
             args[ni + i] = uint64_t(uintptr_t(buf_ptr(k.outs[i].dst.buf, k.outs[i].dst.offset)));
-        args[ni + k.outs.size()] = uint64_t(k.n);
+        for (size_t i = 0; i < k.reds.size(); i++)
+            args[ni + k.outs.size() + i] = uint64_t(uintptr_t(buf_ptr(k.reds[i].dst.buf, k.reds[i].dst.offset)));
+        args[ni + no] = uint64_t(k.n);
         dim3 grid(1, 1, 1), block(256, 1, 1);
         const int64_t cap = int64_t(d_->sm_count) * 16;
-        if (k.type == KernelSpec::ELW) {
+        if (k.type == KernelSpec::ELW && !k.reds.empty()) {
+            // element-wise pass with side sums: 2-d launch over [p2, q2]
+            grid.x = unsigned((k.q2 + 32 * k.vec - 1) / (32 * k.vec));
+            grid.y = unsigned((k.p2 + k.row_chunk - 1) / k.row_chunk);
+        } else if (k.type == KernelSpec::ELW) {
             int64_t nv = k.n / k.vec;
             grid.x = unsigned(std::max<int64_t>(1, std::min<int64_t>((nv + 255) / 256, cap)));
         } else if (k.mode == 0) {
@@ -294,6 +301,7 @@ class Executor {
         double b = 0;
         for (auto& in : k.ins) b += operand_bytes(in);
         for (auto& o : k.outs) b += k.type == KernelSpec::REDUCE ? 4.0 * double(k.n) * double(k.split) : operand_bytes(o.dst);
+        for (auto& r : k.reds) b += operand_bytes(r.dst);
         return b;
     }
 
@@ -804,7 +812,8 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
         lower_program(prog, fresh->plan, opt);
         generate_kernels(fresh->plan);
         fresh->kernel_slot.resize(fresh->plan.kernels.size());
-        for (size_t i = 0; i < fresh->plan.kernels.size(); i++) fresh->kernel_slot[i] = ensure_kernel(d, fresh->plan.kernels[i]);
+        for (size_t i = 0; i < fresh->plan.kernels.size(); i++)
+            fresh->kernel_slot[i] = fresh->plan.kernels[i].dead ? -1 : ensure_kernel(d, fresh->plan.kernels[i]);
         fresh->plan.key = key;
         fresh->lower_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
         d->stats.lower_ms = fresh->lower_ms;
@@ -1115,7 +1124,7 @@ adb_status adb_lower_check(const uint8_t* blob, size_t nbytes, const adb_config*
         generate_kernels(plan);
         std::unordered_map<std::string, bool> done;
         for (auto& k : plan.kernels) {
-            if (done.count(k.entry)) continue;
+            if (k.dead || done.count(k.entry)) continue;
             done[k.entry] = true;
             std::vector<char> cubin;
             std::string log;

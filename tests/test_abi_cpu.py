@@ -92,6 +92,27 @@ def test_fusion_shapes_of_the_benchmark_programs():
     assert sum(" gemm " in l for l in dev.plan.splitlines()) == 11   # 4 forward, 4 dW, 3 dX (dX of layer 1 is dead)
 
 
+def test_sums_ride_along_with_the_element_wise_pass_over_the_same_memory():
+    """Config 2 above 2^18 elements: the loss and the bias gradient become side sums of the one kernel that streams
+    a and b (plus two tiny second passes); the training loop fuses its loss and every bias gradient; the generated
+    kernels compile for sm_100a."""
+    cfg = adb.configs
+    dev = _LowerOnly(with_source=True)
+    cfg.c2_fused_elementwise(dev, rows=512, cols=1024)
+    steps = [l for l in dev.plan.splitlines() if l.startswith("#")]
+    big = [l for l in steps if " elw n=524288" in l or "rows=512 len=1024" in l or "rows=1024 len=512" in l]
+    assert len(big) == 1 and "adb_elwsum_" in big[0], steps
+    assert dev.plan.count("    sum v") == 2
+    assert "__shfl_xor_sync" in dev.plan and "__shared__ float sm[8][128]" in dev.plan
+    small = _LowerOnly()
+    cfg.c2_fused_elementwise(small, rows=64, cols=128)
+    assert "adb_elwsum_" not in small.plan
+    loop = _LowerOnly()
+    cfg.c4_mlp_train(loop, batch=2048, widths=(256, 512, 512, 256, 128), steps=2)
+    assert loop.plan.count("    sum v") == 5          # loss + four bias gradients
+    assert sum(" reduce " in l and "len=2048" in l and "rows=1 " not in l for l in loop.plan.splitlines()) == 0
+
+
 def test_no_fusion_flag_gives_one_kernel_per_command():
     dev = _LowerOnly(flags=adb.devices.FLAG_NO_FUSION)
     ref_programs.ct(dev)
