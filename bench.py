@@ -294,7 +294,7 @@ def bench_c2(adb, dev, pk, args):
                          "frac": top / pk["hbm_gbs"],
                          # dram__bytes_read + dram__bytes_write of this kernel at this size, from the ncu capture summarised in
                          # profiles/c2_fused_elementwise_8192.md (one launch)
-                         "traffic": 1030936832 if rows == 8192 else None, "launches": int(best["top_launches"]),
+                         "traffic": 1034001664 if rows == 8192 else None, "launches": int(best["top_launches"]),
                          "peak_note": "copy bandwidth of " + pk["source"]}}
 
 
