@@ -1249,7 +1249,7 @@ class Lowerer {
         }
         for (size_t e = 0; e < blk.steps.size(); e++) {
             if (blk.steps[e].kind != Step::ELW) continue;
-            if (plan_.kernels[size_t(blk.steps[e].kernel)].n < FUSE_MIN_ELEMS) continue;
+            if (plan_.kernels[size_t(blk.steps[e].kernel)].n < (opt_.fuse_small_sums ? 1 : FUSE_MIN_ELEMS)) continue;
             bool again = true;
             while (again && plan_.kernels[size_t(blk.steps[e].kernel)].reds.size() < 4) {
                 again = false;
@@ -1423,7 +1423,7 @@ class Lowerer {
             const bool x_major = t == 0;
             const int64_t p = x_major ? V : R, q = x_major ? R : V;
             if (!ek.reds.empty() && (p != ek.p2 || q != ek.q2)) continue;
-            if (q < 128 || p < 8) continue;
+            if (!opt_.fuse_small_sums && (q < 128 || p < 8)) continue;
             Match m = match(x_major);
             if (!m.ok) continue;
             mt = std::move(m);

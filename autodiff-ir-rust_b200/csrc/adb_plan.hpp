@@ -148,6 +148,7 @@ struct Plan {
 struct LowerOptions {
     bool no_fusion = false;
     bool no_reduce_fusion = false;  // keep every Sum in a kernel of its own
+    bool fuse_small_sums = false;   // fold sums into element-wise kernels of any size (the thresholds only exist for speed)
     bool exact_div = false;
     int64_t fuse_limit = 768;  // largest expression DAG fused into one kernel
     int rank = 0, world = 1;

@@ -806,6 +806,7 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
         LowerOptions opt;
         opt.no_fusion = (d->flags & ADB_FLAG_NO_FUSION) != 0;
         opt.exact_div = (d->flags & ADB_FLAG_EXACT_DIV) != 0;
+        opt.fuse_small_sums = (d->flags & ADB_FLAG_FUSE_SMALL_SUMS) != 0;
         opt.rank = d->rank;
         opt.world = d->world;
         opt.sm_count = d->sm_count;
@@ -1115,6 +1116,7 @@ adb_status adb_lower_check(const uint8_t* blob, size_t nbytes, const adb_config*
         if (cfg) {
             opt.no_fusion = (cfg->flags & ADB_FLAG_NO_FUSION) != 0;
             opt.exact_div = (cfg->flags & ADB_FLAG_EXACT_DIV) != 0;
+            opt.fuse_small_sums = (cfg->flags & ADB_FLAG_FUSE_SMALL_SUMS) != 0;
             opt.rank = cfg->rank;
             opt.world = cfg->world_size > 0 ? cfg->world_size : 1;
             if (opt.world > 1 && cfg->shard_batch) shard_program(prog, opt.rank, opt.world, int64_t(cfg->shard_batch));

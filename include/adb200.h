@@ -83,6 +83,8 @@ typedef struct adb_config {
                                       (cta_group::2) on a 256 x 256 tile */
 #define ADB_FLAG_EXACT_DIV 64u      /* Recip and Sqrt correctly rounded (bit-identical to IEEE 1.0f/x and sqrtf) instead of the
                                       special-function-unit forms (<= 1 ulp); costs ~10 issue slots per use */
+#define ADB_FLAG_FUSE_SMALL_SUMS 128u /* fold sums into neighbouring element-wise kernels whatever their size (by default only
+                                      above 2^18 elements and 128 columns, where it pays); lets small tests reach that path */
 #define ADB_FLAG_PROFILE 8u        /* CUDA events around every kernel (fills the per-kind times of adb_stats);
                                       loop bodies are then launched kernel by kernel, not as graphs */
 

@@ -11,8 +11,13 @@ adb = importlib.import_module("autodiff-ir-rust_b200")
 
 
 class _Both(OracleDevice):
+    fused_sums = 0
+
     def execute(self, proc, dep):
         adb.devices.lower_check(proc, dep)
+        # the same program with sums folded into element-wise kernels whatever their size
+        plan = adb.devices.lower_check(proc, dep, flags=adb.devices.FLAG_FUSE_SMALL_SUMS)
+        _Both.fused_sums += plan.count("    sum v")
         super().execute(proc, dep)
 
 
@@ -21,3 +26,8 @@ def test_random_program_lowers(seed):
     out = fuzz_programs.build(seed, exact=seed % 2 == 0)(_Both())
     for v in out.values():
         assert not v.is_none
+
+
+def test_some_random_programs_reach_the_sum_fusion():
+    """Runs after the parametrised cases above (same module, collected in order)."""
+    assert _Both.fused_sums >= 5
