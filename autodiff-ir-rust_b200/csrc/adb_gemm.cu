@@ -777,7 +777,6 @@ bool gemm_init(GemmContext& ctx, int sm_count, std::string& err) {
         if (e == cudaSuccess && clusters > 0) ctx.pair_clusters = clusters;
     }
     if (e != cudaSuccess) cudaGetLastError();  // the single-CTA kernel remains available
-    if (const char* v = getenv("ADB_DOT_PAIR")) { if (v[0] == '0') ctx.pair_clusters = 0; }
     return true;
 }
 
@@ -824,13 +823,6 @@ int gemm_launch(GemmContext& ctx, const GemmArgs& a, cudaStream_t stream, std::s
             p.status = ctx.status;
             p.a_lbo = A_MN ? BK * 128 : 16; p.a_sbo = A_MN ? 512 : 1024; p.a_kstep = A_MN ? 1024 : UMMA_K * 4; p.a_layout = A_MN ? 1 : 2;
             p.b_lbo = B_MN ? BK * 128 : 16; p.b_sbo = B_MN ? 512 : 1024; p.b_kstep = B_MN ? 1024 : UMMA_K * 4; p.b_layout = B_MN ? 1 : 2;
-            if (const char* dbg = getenv("ADB_TC_DESC")) {
-                unsigned l, sb, ks;
-                if (sscanf(dbg, "%u,%u,%u", &l, &sb, &ks) == 3) {
-                    if (A_MN) { p.a_lbo = l; p.a_sbo = sb; p.a_kstep = ks; }
-                    if (B_MN) { p.b_lbo = l; p.b_sbo = sb; p.b_kstep = ks; }
-                }
-            }
             if (paired) {
                 p.tiles_m = (int)((a.M + 2 * BM - 1) / (2 * BM));
                 long long clusters = (long long)p.tiles_m * p.tiles_n;

@@ -1484,16 +1484,15 @@ class Lowerer {
         KernelSpec::Red red;
         red.ssa = remap[size_t(rk0.outs[0].ssa)];
         red.axis = axis;
-        ek.reds.push_back(red);  // (elw_vec looks at q2 only once a side sum exists)
+        ek.reds.push_back(red);  // from here on elw_vec() also requires q2 % 4 == 0 for 128-bit lanes
         const int vec = elw_vec(ek);
         const int64_t tiles_q = (Q + 32 * vec - 1) / (32 * vec);
         const int64_t chunks_p = (P + ek.row_chunk - 1) / ek.row_chunk;
         const int64_t parts = axis == 0 ? tiles_q : chunks_p;
         const int64_t kept = axis == 0 ? P : Q;
         const int scratch = temp_buffer(kept * parts);
-        KernelSpec& ek2 = plan_.kernels[size_t(steps[e].kernel)];  // (temp_buffer does not move kernels; kept for clarity)
-        ek2.reds.back().dst.buf = scratch;
-        ek2.reds.back().dst.subs = {{kept * parts, 1}};
+        ek.reds.back().dst.buf = scratch;
+        ek.reds.back().dst.subs = {{kept * parts, 1}};
 
         // second pass: partials -> the reduce's own destination
         KernelSpec k2;
