@@ -68,3 +68,51 @@ def test_c5_mid_size_against_float64():
     err = np.abs(np.asarray(got["x"].data).reshape(n, n) - x).max() / np.abs(x).max()
     assert err < 1e-4, err
     assert b200().stats()["tc_gemm_launches"] == 3 * iters + 1
+
+
+@pytest.mark.parametrize("flags", [0, adb.devices.FLAG_NO_FUSION], ids=["fused", "one-kernel-per-command"])
+def test_more_than_2_31_elements_use_64_bit_indices(flags):
+    """Flat indices beyond 2^31 (the reference's i32 index math, src/kernel/kernel_decl.rs:5, stops there): an in-place
+    element-wise update with its column sums inside a loop, then row sums, over 2^31 + 16384 elements, checked
+    against torch on the same GPU."""
+    import torch
+    P, Q = (1 << 20) + 8, 2048
+    n = P * Q
+    assert n > 1 << 31
+    g = torch.Generator(device="cuda").manual_seed(5)
+    a = torch.randn(n, device="cuda", generator=g)
+    b = torch.randn(n, device="cuda", generator=g)
+    DP = adb.ir.DevicePayload
+    ad = adb.autodiff
+    dev = adb.devices.B200(0, flags=flags)
+    try:
+        ad.set_device(dev)
+        ad.eager_dep_opt()          # read back only what is kept: the [P, Q] tensors stay on the device
+        acc = ad.tensor(DP(a.data_ptr(), n, a), [P, Q])
+        x = ad.tensor(DP(b.data_ptr(), n, b), [P, Q])
+        tot = ad.tensor(np.zeros(Q, np.float32), [Q])
+
+        def body(i):
+            nonlocal acc, tot
+            acc += x * 0.5
+            acc.forward()
+            tot += acc.sum(0)
+            tot.forward()
+        ad.ir_for(range(0, 2), body)
+        rows = acc.sum(1).forward()
+        rows.keep()
+        tot.val().keep()
+        ad.execute()
+        got_rows = np.asarray(rows.get().data, np.float64)
+        got_tot = np.asarray(tot.val().get().data, np.float64)
+        fused = dev.dump_plan().count("adb_elwsum_")
+    finally:
+        dev.close()
+    assert fused == (1 if flags == 0 else 0)
+    want_rows = (a + b).view(P, Q).sum(1, dtype=torch.float64).cpu().numpy()
+    want_tot = ((a + b * 0.5).view(P, Q).sum(0, dtype=torch.float64) + (a + b).view(P, Q).sum(0, dtype=torch.float64)).cpu().numpy()
+    assert got_rows.shape == (P,) and got_tot.shape == (Q,)
+    # the last rows only come out right when no index wrapped at 2^31 or 2^32
+    assert np.abs(got_rows - want_rows).max() / np.abs(want_rows).max() < 1e-4
+    assert np.abs(got_rows[-8:] - want_rows[-8:]).max() < 1e-2
+    assert np.abs(got_tot - want_tot).max() / np.abs(want_tot).max() < 1e-4
