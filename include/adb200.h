@@ -72,21 +72,22 @@ typedef struct adb_config {
     uint64_t shard_batch;      /* world_size > 1: CreateMat tensors whose dim 0 equals this are split by rank */
 } adb_config;
 
-#define ADB_FLAG_NO_GRAPHS 1u      /* launch loop bodies kernel by kernel instead of replaying CUDA graphs */
-#define ADB_FLAG_NO_FUSION 2u      /* one kernel per IR command (debug aid, like the reference's unfused path) */
-#define ADB_FLAG_SIMT_DOT 4u       /* force the plain fp32 dot kernel instead of the tcgen05 3xTF32 kernel */
-#define ADB_FLAG_COMM_STREAM 16u   /* issue collectives on a second, high-priority stream (ordered by events on the memory
-                                      they touch) instead of the compute stream; off by default: the persistent dot-product
-                                      kernel holds every SM, so the collective only starts when it ends and then delays the
-                                      next one (measured 2 % slower on 2 GPUs) */
-#define ADB_FLAG_SINGLE_SM_DOT 32u  /* keep the tcgen05 dot kernel on one SM per 128 x 256 tile instead of pairing two SMs
-                                      (cta_group::2) on a 256 x 256 tile */
-#define ADB_FLAG_EXACT_DIV 64u      /* Recip and Sqrt correctly rounded (bit-identical to IEEE 1.0f/x and sqrtf) instead of the
-                                      special-function-unit forms (<= 1 ulp); costs ~10 issue slots per use */
-#define ADB_FLAG_FUSE_SMALL_SUMS 128u /* fold sums into neighbouring element-wise kernels whatever their size (by default only
-                                      above 2^18 elements and 128 columns, where it pays); lets small tests reach that path */
-#define ADB_FLAG_PROFILE 8u        /* CUDA events around every kernel (fills the per-kind times of adb_stats);
-                                      loop bodies are then launched kernel by kernel, not as graphs */
+#define ADB_FLAG_NO_GRAPHS 1u         /* launch loop bodies kernel by kernel instead of replaying CUDA graphs */
+#define ADB_FLAG_NO_FUSION 2u         /* one kernel per IR command (debug aid, like the reference's unfused path) */
+#define ADB_FLAG_SIMT_DOT 4u          /* force the plain fp32 dot kernel instead of the tcgen05 3xTF32 kernels */
+#define ADB_FLAG_PROFILE 8u           /* CUDA events around every kernel (fills the per-kind times of adb_stats);
+                                         loop bodies are then launched kernel by kernel, not as graphs */
+#define ADB_FLAG_COMM_STREAM 16u      /* issue collectives on a second, high-priority stream (ordered by events on the
+                                         memory they touch) instead of the compute stream; off by default: the persistent
+                                         dot-product kernel holds every SM, so the collective only starts when it ends and
+                                         then delays the next one (measured 2 % slower on 2 GPUs) */
+#define ADB_FLAG_SINGLE_SM_DOT 32u    /* keep the tcgen05 dot kernel on one SM per 128 x 256 tile instead of pairing two
+                                         SMs (cta_group::2) on a 256 x 256 tile */
+#define ADB_FLAG_EXACT_DIV 64u        /* Recip and Sqrt correctly rounded (bit-identical to IEEE 1.0f/x and sqrtf) instead
+                                         of the special-function-unit forms (<= 1 ulp); costs ~10 issue slots per use */
+#define ADB_FLAG_FUSE_SMALL_SUMS 128u /* fold sums into neighbouring element-wise kernels whatever their size (by default
+                                         only above 2^18 elements and 128 columns, where it pays); lets small tests reach
+                                         that path */
 
 /* Replaces OpenCL::new (src/devices/opencl/device.rs:41-58) + autodiff::set_device's device slot
  * (src/core/autodiff.rs:82-97).  Fails with ADB_ERR_NO_DEVICE when no GPU is present. */
