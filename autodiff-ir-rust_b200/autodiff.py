@@ -332,6 +332,12 @@ class Tensor:
     def pow2(self):
         return self * self
 
+    def abs(self):
+        """|x| composed from existing primitives (upstream lists abs as missing, TODO.md:47): the device's Sqrt is
+        sqrt(fabs(.)) (src/devices/opencl/kernels/unary.rs:11), so sqrt(x*x) is exact up to the rounding of x*x;
+        the gradient x / |x| comes out of the pow2 / sqrt backward rules."""
+        return self.pow2().sqrt()
+
     def pow3(self):
         return self.pow2() * self
 

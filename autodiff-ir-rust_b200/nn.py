@@ -1,7 +1,7 @@
 """Mirror of the reference's `nn` helpers that the configs and known-answer tests use:
 Linear / LinearWithWeights (src/nn/linear.rs:5-49), Sequential (src/nn/sequential.rs),
 Sigmoid / ReLU / Softmax (src/nn/activations), RMS / LayerNorm (src/nn/norm) and SGD
-(src/nn/optimizers/sgd.rs:3-28).  Each `f` composes Tensor ops exactly as upstream does,
+(src/nn/optimizers/sgd.rs:3-28), plus the two helpers upstream lists as missing (mse_loss, Tensor.abs).  Each `f` composes Tensor ops exactly as upstream does,
 so the IR reaching the device has the same shape.
 """
 from __future__ import annotations
@@ -89,6 +89,23 @@ class LayerNorm(Module):
         eps = f32(1e-9)
         y = (x - x.mean(-1).unsqueeze(-1)) / (x.var(-1, 0) + eps).sqrt().unsqueeze(-1)
         return y * self.scale + self.bias
+
+
+def mse_loss(y: Tensor, target: Tensor) -> Tensor:
+    """mean((y - target)^2) over every element, as a [1]-shaped tensor: the composition the reference's examples
+    spell out by hand (`MSE` is on its to-do list, TODO.md:12): square, sum the axes from the last to the first,
+    scale by the host-computed 1 / count."""
+    d = y - target
+    count = int(np.prod(d.dim()))
+    s = d.pow2()
+    while len(s.dim()) > 1:
+        s = s.sum(len(s.dim()) - 1)
+    return s.sum(0) * f32(1.0 / count)
+
+
+class MSELoss(Module):
+    def f(self, x: Tensor, target: Tensor = None) -> Tensor:
+        return mse_loss(x, target)
 
 
 class Sequential(Module):

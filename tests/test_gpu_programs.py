@@ -309,3 +309,25 @@ def test_device_payload_in_a_captured_loop_then_a_new_program_with_a_dot():
         assert_exact("acc", got["acc"], want["acc"])
         want_y, got_y = dot_prog(oracle()), dot_prog(b200())
         assert_rel("y", got_y["y"], want_y["y"], 1e-4)
+
+
+@pytest.mark.parametrize("shape", [[4096], [64, 48], [8, 16, 32]])
+def test_mse_loss_and_abs_helpers(shape):
+    n = int(np.prod(shape))
+    y, t = rnd(n), rnd(n)
+
+    def prog(dev):
+        ad.set_device(dev)
+        ty, tt = ad.tensor(y, shape), ad.tensor(t, shape)
+        loss = nn.mse_loss(ty, tt)
+        loss.forward()
+        loss.backward()
+        a = ty.abs().forward()
+        a.keep()
+        loss.val().keep()
+        ad.execute()
+        return {"loss": loss.val().get(), "y_grad": ty.grad().get(), "abs": a.get()}
+    want, got = run_both(prog)
+    assert_rel("loss", got["loss"], want["loss"], 1e-4)
+    assert_ulp("y_grad", got["y_grad"], want["y_grad"], 2)
+    assert_ulp("abs", got["abs"], want["abs"], 1)
