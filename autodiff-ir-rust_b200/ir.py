@@ -118,6 +118,7 @@ class _Writer:
         self.body = bytearray()
         self.inline: list[tuple[int, np.ndarray]] = []  # (patch position in body, data)
         self.keepalive: list = []
+        self.inline_limit = INLINE_LIMIT
 
     def idx(self, s: str) -> int:
         i = self.ids.get(s)
@@ -165,7 +166,7 @@ class _Writer:
                 self.keepalive.append(contents)
                 return
             arr = np.ascontiguousarray(contents, dtype=np.float32).reshape(-1)
-            if arr.nbytes <= INLINE_LIMIT:
+            if arr.nbytes <= self.inline_limit:
                 self.u8(PAYLOAD_INLINE)
                 self.inline.append((len(self.body), arr))
                 self.u64(0)
@@ -225,14 +226,18 @@ class _Writer:
             raise ValueError(f"unknown IR command {k}")
 
 
-def serialize(proc: IRProcedure, dep_list) -> tuple[bytes, list]:
+def serialize(proc: IRProcedure, dep_list, inline_limit: int | None = None) -> tuple[bytes, list]:
     """Flatten (procedure, dep list) into the wire blob.
 
     Returns (blob, keepalive): `keepalive` holds the arrays whose addresses the
     blob references (PAYLOAD_HOST / PAYLOAD_DEVICE); the caller keeps it alive
-    until `adb_execute` has returned.
+    until `adb_execute` has returned.  `inline_limit` (bytes) overrides the size up to which
+    host payloads are copied into the blob instead of being passed by address; a very large value
+    gives a self-contained blob that can be written to a file.
     """
     w = _Writer()
+    if inline_limit is not None:
+        w.inline_limit = inline_limit
     w.proc(proc)
     dep = sorted(dep_list)
     dep_idx = [w.idx(d) for d in dep]
