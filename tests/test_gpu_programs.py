@@ -331,3 +331,30 @@ def test_mse_loss_and_abs_helpers(shape):
     assert_rel("loss", got["loss"], want["loss"], 1e-4)
     assert_ulp("y_grad", got["y_grad"], want["y_grad"], 2)
     assert_ulp("abs", got["abs"], want["abs"], 1)
+
+
+def test_arena_that_does_not_fit_is_refused_and_the_handle_stays_usable():
+    """A program whose buffers need more memory than the GPU has: `adb_execute` reports ADB_ERR_OOM before anything
+    runs (the arena size is known after lowering); the next program on the same handle works."""
+    n = 1 << 18
+    x = rnd(n)
+    dev = b200()
+    ad.set_device(dev)
+    ad.eager_dep_opt()
+    t = ad.tensor(x, [1, n])
+    big = (t.broadcast(0, n) * 2.0 + 1.0).forward()       # 2^36 elements = 256 GiB
+    big.keep()
+    with pytest.raises(adb.devices.AdbError) as e:
+        ad.execute()
+    assert "does not fit" in str(e.value)
+    want, got = run_both(lambda d: _tiny(d, x))
+    assert_exact("y", got["y"], want["y"])
+
+
+def _tiny(dev, x):
+    ad.set_device(dev)
+    ad.eager_dep_opt()
+    y = (ad.tensor(x[:1024].copy(), [1024]) * 3.0).forward()
+    y.keep()
+    ad.execute()
+    return {"y": y.get()}
