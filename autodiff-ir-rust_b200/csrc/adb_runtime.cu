@@ -129,6 +129,8 @@ struct CompiledPlan {
     uint64_t runs = 0;             // completed executions of this plan
     bool top_level_graphs = false; // straight-line top-level code is replayed as graphs (addresses were stable)
     double lower_ms = 0;
+    std::vector<uint8_t> structure;  // the program without payload addresses: compared on every cache hit
+    uint64_t last_used = 0;
 };
 
 }  // namespace adb
@@ -155,6 +157,7 @@ struct adb_device {
     char* arena = nullptr;
     size_t arena_cap = 0;
     uint64_t arena_gen = 1;
+    uint64_t use_counter = 0;      // orders plans by last use (cache eviction)
     // condition read-back
     float* cond_host = nullptr;
     // results of the last execute
@@ -197,7 +200,7 @@ uint64_t fnv_bytes(const void* p, size_t n, uint64_t h = 1469598103934665603ull)
 }
 
 // hash of everything in the program except payload addresses and payload data
-uint64_t structure_key(Program& prog, uint32_t flags, int rank, int world, uint64_t shard_batch) {
+uint64_t structure_key(Program& prog, uint32_t flags, int rank, int world, uint64_t shard_batch, std::vector<uint8_t>& structure) {
     struct Saved { Cmd* c; uint64_t payload; uint8_t kind; };
     std::vector<Saved> saved;
     std::function<void(Block&)> strip = [&](Block& b) {
@@ -217,11 +220,13 @@ uint64_t structure_key(Program& prog, uint32_t flags, int rank, int world, uint6
     strip(prog.main);
     std::vector<uint8_t> bytes = serialize_program(prog);
     for (auto& s : saved) { s.c->payload = s.payload; s.c->payload_kind = s.kind; }
-    uint64_t h = fnv_bytes(bytes.data(), bytes.size());
     // the device-vs-host distinction changes the plan (resident payloads are read in place)
-    for (auto& s : saved) { uint8_t k = s.kind == PAYLOAD_DEVICE ? 1 : 0; h = fnv_bytes(&k, 1, h); }
+    for (auto& s : saved) bytes.push_back(s.kind == PAYLOAD_DEVICE ? 1 : 0);
     uint64_t extra[4] = {flags, uint64_t(rank), uint64_t(world), shard_batch};
-    return fnv_bytes(extra, sizeof extra, h);
+    const uint8_t* e = reinterpret_cast<const uint8_t*>(extra);
+    bytes.insert(bytes.end(), e, e + sizeof extra);
+    structure.swap(bytes);
+    return fnv_bytes(structure.data(), structure.size());
 }
 
 void collect_payload_cmds(Block& b, std::vector<Cmd*>& out, const std::vector<char>* live) {
@@ -764,7 +769,8 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
     d->stats = adb_stats{};
     d->stats.ir_commands = prog.n_cmds;
     if (d->world > 1 && d->shard_batch) shard_program(prog, d->rank, d->world, int64_t(d->shard_batch));
-    uint64_t key = structure_key(prog, d->flags, d->rank, d->world, d->shard_batch);
+    std::vector<uint8_t> structure;
+    uint64_t key = structure_key(prog, d->flags, d->rank, d->world, d->shard_batch, structure);
 
     std::vector<Cmd*> mats;
     collect_payload_cmds(prog.main, mats, nullptr);
@@ -773,8 +779,9 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
     auto it = d->plans.find(key);
     if (it != d->plans.end()) {
         cp = it->second.get();
-        // a cached plan may have folded a constant-filled payload; that must still hold
-        bool ok = cp->plan.payloads.size() <= mats.size();
+        // equal hashes are not proof of equal programs; and a cached plan may have folded a constant-filled payload,
+        // which must still hold
+        bool ok = cp->structure == structure && cp->plan.payloads.size() <= mats.size();
         if (ok) {
             // payload slots are recorded in program order together with the command index
             for (size_t s = 0; s < cp->plan.payloads.size() && ok; s++) {
@@ -818,10 +825,22 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
         fresh->plan.key = key;
         fresh->lower_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
         d->stats.lower_ms = fresh->lower_ms;
+        fresh->structure = std::move(structure);
         cp = fresh.get();
+        // bounded cache: a process that keeps producing new programs drops the plan it used longest ago
+        if (d->plans.size() >= 256) {
+            auto old = d->plans.begin();
+            for (auto p = d->plans.begin(); p != d->plans.end(); ++p)
+                if (p->second->last_used < old->second->last_used) old = p;
+            destroy_graphs(*old->second);
+            destroy_prefetch(*old->second);
+            destroy_sched(*old->second);
+            d->plans.erase(old);
+        }
         d->plans[key] = std::move(fresh);
     }
     d->last = cp;
+    cp->last_used = ++d->use_counter;
     Plan& plan = cp->plan;
     d->stats.plan_steps = uint64_t(plan.n_steps);
     d->stats.arena_bytes = uint64_t(plan.arena_bytes);
