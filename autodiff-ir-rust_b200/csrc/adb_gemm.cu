@@ -114,6 +114,9 @@ struct Params {
     // shared-memory descriptor geometry of the two operands (bytes)
     uint32_t a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep;
     uint32_t a_layout, b_layout;  // descriptor swizzle mode: 2 = 128B (K-major), 1 = 128B with 32B atoms (MN-major tf32)
+    // paired kernel only: the k loop of every tile is cut into k_splits ranges of kb_per_split k-blocks that different
+    // clusters work on (few tiles, long K); all of them then add into a zeroed C
+    int k_splits = 1, kb_per_split = 0;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -522,7 +525,8 @@ adb_dot_tc_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();       // 0 = leader
     const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
-    const int total_tiles = p.tiles_m * p.tiles_n;  // tiles_m counts 256-row tiles here
+    // a unit of work is one k range of one tile (tiles_m counts 256-row tiles here)
+    const int total_units = p.tiles_m * p.tiles_n * p.k_splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < PSTAGES; s++) {
@@ -552,10 +556,12 @@ adb_dot_tc_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = cluster_id; tile < total_tiles && ok; tile += num_clusters) {
+            for (int unit = cluster_id; unit < total_units && ok; unit += num_clusters) {
+                const int tile = unit / p.k_splits;
+                const int kb_begin = (unit % p.k_splits) * p.kb_per_split, kb_stop = min(kb_begin + p.kb_per_split, p.k_blocks);
                 const int m0 = (tile / p.tiles_n) * (2 * BM) + (int)rank * BM;
                 const int n0 = (tile % p.tiles_n) * BN + (int)rank * BNH;
-                for (int kb = 0; kb < p.k_blocks; kb++, it++) {
+                for (int kb = kb_begin; kb < kb_stop; kb++, it++) {
                     const int s = it % PSTAGES;
                     const uint32_t ph = (it / PSTAGES) & 1;
                     if (!mbar_wait(bar_empty(s), ph ^ 1, stop, p.status, TIMEOUT_EMPTY)) { ok = false; break; }
@@ -585,14 +591,15 @@ adb_dot_tc_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const uint32_t b_lbo = p.b_lbo, b_sbo = p.b_sbo, b_kstep = p.b_kstep;
             uint32_t it = 0, chunk_no = 0;
             bool ok = true;
-            for (int tile = cluster_id; tile < total_tiles && ok; tile += num_clusters) {
-                for (int kb0 = 0; kb0 < p.k_blocks && ok; kb0 += CHUNK_KB, chunk_no++) {
+            for (int unit = cluster_id; unit < total_units && ok; unit += num_clusters) {
+                const int kb_begin = (unit % p.k_splits) * p.kb_per_split, kb_stop = min(kb_begin + p.kb_per_split, p.k_blocks);
+                for (int kb0 = kb_begin; kb0 < kb_stop && ok; kb0 += CHUNK_KB, chunk_no++) {
                     const int acc = chunk_no & 1;
                     const uint32_t acc_ph = (chunk_no >> 1) & 1;
                     if (!mbar_wait_cluster(bar_acc_empty(acc), acc_ph ^ 1, stop, p.status, TIMEOUT_ACC_EMPTY)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t d_tmem = tmem_base + acc * BN;
-                    const int kb_end = min(kb0 + CHUNK_KB, p.k_blocks);
+                    const int kb_end = min(kb0 + CHUNK_KB, kb_stop);
                     for (int kb = kb0; kb < kb_end; kb++, it++) {
                         const int s = it % PSTAGES;
                         const uint32_t ph = (it / PSTAGES) & 1;
@@ -623,8 +630,9 @@ adb_dot_tc_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int t = threadIdx.x - 64;
         uint32_t it = 0;
         bool ok = true;
-        for (int tile = cluster_id; tile < total_tiles && ok; tile += num_clusters) {
-            for (int kb = 0; kb < p.k_blocks; kb++, it++) {
+        for (int unit = cluster_id; unit < total_units && ok; unit += num_clusters) {
+            const int kb_begin = (unit % p.k_splits) * p.kb_per_split, kb_stop = min(kb_begin + p.kb_per_split, p.k_blocks);
+            for (int kb = kb_begin; kb < kb_stop; kb++, it++) {
                 const int s = it % PSTAGES;
                 const uint32_t ph = (it / PSTAGES) & 1;
                 if (!mbar_wait_warp(bar_raw(s), ph, stop, p.status, TIMEOUT_RAW)) { ok = false; break; }
@@ -651,14 +659,18 @@ adb_dot_tc_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         uint32_t chunk_no = 0;
         bool ok = true;
         const bool vec_ok = (p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
-        for (int tile = cluster_id; tile < total_tiles && ok; tile += num_clusters) {
+        for (int unit = cluster_id; unit < total_units && ok; unit += num_clusters) {
+            const int tile = unit / p.k_splits;
+            const int kb_begin = (unit % p.k_splits) * p.kb_per_split, kb_stop = min(kb_begin + p.kb_per_split, p.k_blocks);
             const int m0 = (tile / p.tiles_n) * (2 * BM) + (int)rank * BM, n0 = (tile % p.tiles_n) * BN;
             const int row = m0 + q * 32 + lane;
             float* crow = p.C + (size_t)row * p.N;
-            for (int kb0 = 0; kb0 < p.k_blocks && ok; kb0 += CHUNK_KB, chunk_no++) {
+            for (int kb0 = kb_begin; kb0 < kb_stop && ok; kb0 += CHUNK_KB, chunk_no++) {
                 const int acc = chunk_no & 1;
                 const uint32_t acc_ph = (chunk_no >> 1) & 1;
-                const bool first = kb0 == 0;
+                // the first chunk of a tile overwrites C, later ones add to it; with split k ranges nobody knows who
+                // is first, so C was zeroed and everybody adds
+                const bool first = kb0 == 0 && p.k_splits == 1;
                 if (!mbar_wait_warp(bar_acc_full(acc), acc_ph, stop, p.status, TIMEOUT_ACC_FULL)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
@@ -825,7 +837,24 @@ int gemm_launch(GemmContext& ctx, const GemmArgs& a, cudaStream_t stream, std::s
             p.b_lbo = B_MN ? BK * 128 : 16; p.b_sbo = B_MN ? 512 : 1024; p.b_kstep = B_MN ? 1024 : UMMA_K * 4; p.b_layout = B_MN ? 1 : 2;
             if (paired) {
                 p.tiles_m = (int)((a.M + 2 * BM - 1) / (2 * BM));
-                long long clusters = (long long)p.tiles_m * p.tiles_n;
+                const long long tiles = (long long)p.tiles_m * p.tiles_n;
+                // few tiles and a long k loop: cut k so that every cluster has work (ranges are whole 1024-element
+                // accumulation chunks); the partial products meet in C through the adds the epilogue performs anyway
+                p.k_splits = 1;
+                p.kb_per_split = p.k_blocks;
+                if (tiles * 2 <= ctx.pair_clusters && p.k_blocks >= 2 * CHUNK_KB) {
+                    const long long want = ctx.pair_clusters / tiles;
+                    long long per = (p.k_blocks + want - 1) / want;
+                    per = (per + CHUNK_KB - 1) / CHUNK_KB * CHUNK_KB;
+                    p.kb_per_split = (int)per;
+                    p.k_splits = (int)((p.k_blocks + per - 1) / per);
+                    if (p.k_splits > 1 &&
+                        cudaMemsetAsync(a.C, 0, size_t(a.M) * size_t(a.N) * sizeof(float), stream) != cudaSuccess) {
+                        err = "cudaMemsetAsync(C)";
+                        return -1;
+                    }
+                }
+                long long clusters = tiles * p.k_splits;
                 if (clusters > ctx.pair_clusters) clusters = ctx.pair_clusters;
                 const int grid = int(2 * clusters);
                 using namespace pair;

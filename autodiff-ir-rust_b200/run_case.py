@@ -34,13 +34,14 @@ def main():
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--no-profile-flag", action="store_true")
+    ap.add_argument("--flags", type=int, default=0, help="extra ADB_FLAG_* bits for the handle (e.g. 32 = single-SM dot kernel)")
     args = ap.parse_args()
 
     import torch
     adb = importlib.import_module("autodiff-ir-rust_b200")
     ad, cfg, DP = adb.autodiff, adb.configs, adb.ir.DevicePayload
     torch.cuda.set_device(0)
-    dev = adb.devices.B200(0, flags=0 if args.no_profile_flag else adb.devices.FLAG_PROFILE)
+    dev = adb.devices.B200(0, flags=args.flags | (0 if args.no_profile_flag else adb.devices.FLAG_PROFILE))
     g = torch.Generator(device="cuda").manual_seed(1)
 
     def resident(n, scale=1.0):

@@ -93,3 +93,20 @@ def test_tc_dot_exact_on_small_integers(M, kernel):
     got = _dot(_device(kernel), a, b, False, False, M, K, N)
     ref = a.reshape(M, K).astype(np.int64) @ b.reshape(K, N).astype(np.int64)
     np.testing.assert_array_equal(np.asarray(got.data).reshape(M, N), ref.astype(np.float32))
+
+
+@pytest.mark.parametrize("M,K,N,ta,tb", [(512, 8192, 512, False, False), (300, 5000, 200, False, False), (256, 4096, 256, True, True),
+                                         (384, 20000, 136, True, False)])
+def test_few_tiles_long_k_is_split_across_clusters(M, K, N, ta, tb):
+    """Fewer tiles than half the SM pairs and K >= 2048: the paired kernel cuts k into ranges that different
+    clusters accumulate into a zeroed C.  Same accuracy bar; the single-SM kernel (no split) must agree."""
+    a = RNG.standard_normal(M * K).astype(np.float32)
+    b = RNG.standard_normal(K * N).astype(np.float32)
+    got = _dot(_device("pair"), a, b, ta, tb, M, K, N)
+    ref1 = _dot(_device("single"), a, b, ta, tb, M, K, N)
+    A = a.reshape(K, M).T if ta else a.reshape(M, K)
+    B = b.reshape(N, K).T if tb else b.reshape(K, N)
+    ref = A.astype(np.float64) @ B.astype(np.float64)
+    g = np.asarray(got.data, np.float64).reshape(M, N)
+    assert np.abs(g - ref).max() / np.abs(ref).max() < 2e-5
+    assert_rel("pair vs single", got, ref1, 2e-5)

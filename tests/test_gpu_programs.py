@@ -358,3 +358,25 @@ def _tiny(dev, x):
     y.keep()
     ad.execute()
     return {"y": y.get()}
+
+
+def test_plan_cache_is_bounded_and_evicted_programs_still_run():
+    """More distinct programs than the cache holds (256): every one is right, and the first one, whose plan was
+    dropped in the meantime, is lowered again and right again."""
+    dev = adb.devices.B200(0)
+    try:
+        def run(n):
+            ad.set_device(dev)
+            ad.eager_dep_opt()
+            x = np.arange(n, dtype=np.float32)
+            y = (ad.tensor(x, [n]) * 2.0 + float(n)).forward()
+            y.keep()
+            ad.execute()
+            np.testing.assert_array_equal(y.get().data, x * 2.0 + float(n))
+            return dev.stats()["lower_ms"]
+        for n in range(1, 271):
+            run(n)
+        assert run(270) == 0.0      # still cached: no lowering
+        assert run(1) > 0.0         # evicted: lowered again
+    finally:
+        dev.close()
