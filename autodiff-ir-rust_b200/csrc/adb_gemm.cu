@@ -114,8 +114,8 @@ struct Params {
     // shared-memory descriptor geometry of the two operands (bytes)
     uint32_t a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep;
     uint32_t a_layout, b_layout;  // descriptor swizzle mode: 2 = 128B (K-major), 1 = 128B with 32B atoms (MN-major tf32)
-    // paired kernel only: the k loop of every tile is cut into k_splits ranges of kb_per_split k-blocks that different
-    // clusters work on (few tiles, long K); all of them then add into a zeroed C
+    // the k loop of every tile is cut into k_splits ranges of kb_per_split k-blocks that different CTAs (clusters) work
+    // on when there are few tiles and K is long; all of them then add into a zeroed C
     int k_splits = 1, kb_per_split = 0;
 };
 
@@ -232,7 +232,7 @@ adb_dot_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     volatile int* stop = reinterpret_cast<volatile int*>(gen_base + STAGES * STAGE_BYTES + 8 * (3 * STAGES + 4) + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int total_tiles = p.tiles_m * p.tiles_n;
+    const int total_units = p.tiles_m * p.tiles_n * p.k_splits;  // a unit of work is one k range of one tile
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -261,9 +261,11 @@ adb_dot_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+                const int tile = unit / p.k_splits;
+                const int kb_begin = (unit % p.k_splits) * p.kb_per_split, kb_stop = min(kb_begin + p.kb_per_split, p.k_blocks);
                 const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
-                for (int kb = 0; kb < p.k_blocks; kb++, it++) {
+                for (int kb = kb_begin; kb < kb_stop; kb++, it++) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(bar_empty(s), ph ^ 1, stop, p.status, TIMEOUT_EMPTY)) { ok = false; break; }
@@ -298,14 +300,15 @@ adb_dot_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
             const uint32_t b_lbo = p.b_lbo, b_sbo = p.b_sbo, b_kstep = p.b_kstep;
             uint32_t it = 0, chunk_no = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                for (int kb0 = 0; kb0 < p.k_blocks && ok; kb0 += CHUNK_KB, chunk_no++) {
+            for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+                const int kb_begin = (unit % p.k_splits) * p.kb_per_split, kb_stop = min(kb_begin + p.kb_per_split, p.k_blocks);
+                for (int kb0 = kb_begin; kb0 < kb_stop && ok; kb0 += CHUNK_KB, chunk_no++) {
                     const int acc = chunk_no & 1;
                     const uint32_t acc_ph = (chunk_no >> 1) & 1;
                     if (!mbar_wait(bar_acc_empty(acc), acc_ph ^ 1, stop, p.status, TIMEOUT_ACC_EMPTY)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t d_tmem = tmem_base + acc * BN;
-                    const int kb_end = min(kb0 + CHUNK_KB, p.k_blocks);
+                    const int kb_end = min(kb0 + CHUNK_KB, kb_stop);
                     for (int kb = kb0; kb < kb_end; kb++, it++) {
                         const int s = it % STAGES;
                         const uint32_t ph = (it / STAGES) & 1;
@@ -333,8 +336,9 @@ adb_dot_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         const int t = threadIdx.x - 64;  // 0..127
         uint32_t it = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            for (int kb = 0; kb < p.k_blocks; kb++, it++) {
+        for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+            const int kb_begin = (unit % p.k_splits) * p.kb_per_split, kb_stop = min(kb_begin + p.kb_per_split, p.k_blocks);
+            for (int kb = kb_begin; kb < kb_stop; kb++, it++) {
                 const int s = it % STAGES;
                 const uint32_t ph = (it / STAGES) & 1;
                 if (!mbar_wait_warp(bar_raw(s), ph, stop, p.status, TIMEOUT_RAW)) { ok = false; break; }
@@ -365,14 +369,17 @@ adb_dot_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         uint32_t chunk_no = 0;
         bool ok = true;
         const bool vec_ok = (p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+            const int tile = unit / p.k_splits;
+            const int kb_begin = (unit % p.k_splits) * p.kb_per_split, kb_stop = min(kb_begin + p.kb_per_split, p.k_blocks);
             const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
             const int row = m0 + q * 32 + lane;
             float* crow = p.C + (size_t)row * p.N;
-            for (int kb0 = 0; kb0 < p.k_blocks && ok; kb0 += CHUNK_KB, chunk_no++) {
+            for (int kb0 = kb_begin; kb0 < kb_stop && ok; kb0 += CHUNK_KB, chunk_no++) {
                 const int acc = chunk_no & 1;
                 const uint32_t acc_ph = (chunk_no >> 1) & 1;
-                const bool first = kb0 == 0;  // first chunk of the tile overwrites C, later ones add to it
+                // first chunk of the tile overwrites C, later ones add to it (split k ranges: C is zeroed, all add)
+                const bool first = kb0 == 0 && p.k_splits == 1;
                 if (!mbar_wait_warp(bar_acc_full(acc), acc_ph, stop, p.status, TIMEOUT_ACC_FULL)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
@@ -806,6 +813,25 @@ static bool tma_ok(const float* p, long long unit_len, long long other_stride) {
     return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && other_stride % 4 == 0 && other_stride > 0;
 }
 
+// Few tiles and a long k loop: cut k so that every SM (pair) has work.  Ranges are whole 1024-element accumulation
+// chunks; the partial products meet in a zeroed C through the adds the epilogue performs anyway.
+static bool plan_k_split(tc::Params& p, long long tiles, int workers, const GemmArgs& a, cudaStream_t stream, std::string& err) {
+    using namespace tc;
+    p.k_splits = 1;
+    p.kb_per_split = p.k_blocks;
+    if (tiles * 2 > workers || p.k_blocks < 2 * CHUNK_KB) return true;
+    const long long want = workers / tiles;
+    long long per = (p.k_blocks + want - 1) / want;
+    per = (per + CHUNK_KB - 1) / CHUNK_KB * CHUNK_KB;
+    p.kb_per_split = (int)per;
+    p.k_splits = (int)((p.k_blocks + per - 1) / per);
+    if (p.k_splits > 1 && cudaMemsetAsync(a.C, 0, size_t(a.M) * size_t(a.N) * sizeof(float), stream) != cudaSuccess) {
+        err = "cudaMemsetAsync(C)";
+        return false;
+    }
+    return true;
+}
+
 int gemm_launch(GemmContext& ctx, const GemmArgs& a, cudaStream_t stream, std::string& err) {
     if (a.M <= 0 || a.N <= 0) return 0;
     bool use_tc = ctx.tc_ready && !a.force_simt && a.K >= 8 && a.M >= 32 && a.N >= 32 &&
@@ -838,22 +864,7 @@ int gemm_launch(GemmContext& ctx, const GemmArgs& a, cudaStream_t stream, std::s
             if (paired) {
                 p.tiles_m = (int)((a.M + 2 * BM - 1) / (2 * BM));
                 const long long tiles = (long long)p.tiles_m * p.tiles_n;
-                // few tiles and a long k loop: cut k so that every cluster has work (ranges are whole 1024-element
-                // accumulation chunks); the partial products meet in C through the adds the epilogue performs anyway
-                p.k_splits = 1;
-                p.kb_per_split = p.k_blocks;
-                if (tiles * 2 <= ctx.pair_clusters && p.k_blocks >= 2 * CHUNK_KB) {
-                    const long long want = ctx.pair_clusters / tiles;
-                    long long per = (p.k_blocks + want - 1) / want;
-                    per = (per + CHUNK_KB - 1) / CHUNK_KB * CHUNK_KB;
-                    p.kb_per_split = (int)per;
-                    p.k_splits = (int)((p.k_blocks + per - 1) / per);
-                    if (p.k_splits > 1 &&
-                        cudaMemsetAsync(a.C, 0, size_t(a.M) * size_t(a.N) * sizeof(float), stream) != cudaSuccess) {
-                        err = "cudaMemsetAsync(C)";
-                        return -1;
-                    }
-                }
+                if (!plan_k_split(p, tiles, ctx.pair_clusters, a, stream, err)) return -1;
                 long long clusters = tiles * p.k_splits;
                 if (clusters > ctx.pair_clusters) clusters = ctx.pair_clusters;
                 const int grid = int(2 * clusters);
@@ -868,8 +879,9 @@ int gemm_launch(GemmContext& ctx, const GemmArgs& a, cudaStream_t stream, std::s
                 ctx.tc_total++;
                 return 1;
             }
-            int grid = p.tiles_m * p.tiles_n;
-            if (grid > ctx.sm_count) grid = ctx.sm_count;
+            if (!plan_k_split(p, (long long)p.tiles_m * p.tiles_n, ctx.sm_count, a, stream, err)) return -1;
+            long long units = (long long)p.tiles_m * p.tiles_n * p.k_splits;
+            const int grid = int(units > ctx.sm_count ? ctx.sm_count : units);
             if (A_MN && B_MN) adb_dot_tc<true, true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, p);
             else if (A_MN) adb_dot_tc<true, false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, p);
             else if (B_MN) adb_dot_tc<false, true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, p);

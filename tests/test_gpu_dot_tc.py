@@ -110,3 +110,16 @@ def test_few_tiles_long_k_is_split_across_clusters(M, K, N, ta, tb):
     g = np.asarray(got.data, np.float64).reshape(M, N)
     assert np.abs(g - ref).max() / np.abs(ref).max() < 2e-5
     assert_rel("pair vs single", got, ref1, 2e-5)
+
+
+@pytest.mark.parametrize("M,K,N,ta", [(128, 16384, 512, False), (64, 8192, 1000, False), (96, 30000, 256, True)])
+def test_single_sm_kernel_splits_long_k_too(M, K, N, ta):
+    a = RNG.standard_normal(M * K).astype(np.float32)
+    b = RNG.standard_normal(K * N).astype(np.float32)
+    dev = _device("pair")      # M <= 128 runs the single-SM kernel on any handle
+    got = _dot(dev, a, b, ta, False, M, K, N)
+    assert dev.stats()["tc_gemm_launches"] == 1
+    A = a.reshape(K, M).T if ta else a.reshape(M, K)
+    ref = A.astype(np.float64) @ b.reshape(K, N).astype(np.float64)
+    g = np.asarray(got.data, np.float64).reshape(M, N)
+    assert np.abs(g - ref).max() / np.abs(ref).max() < 2e-5
