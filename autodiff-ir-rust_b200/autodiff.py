@@ -367,6 +367,22 @@ class Tensor:
         permute_to = permute_to[:dim] + permute_to[dim + 1:]
         return node.permute(permute_to)
 
+    def max(self, dim: int) -> "Tensor":
+        """Maximum along one axis: the same permute / view / reduce / view / permute sandwich as `sum`."""
+        p_dim = len(self.dim())
+        dim = p_dim + dim if dim < 0 else dim
+        permute_to = list(range(p_dim))
+        permute_to[-1] = dim
+        permute_to[dim] = p_dim - 1
+        node = self.permute(permute_to)
+        new_dim = node.dim()
+        node = node.view([-1, new_dim[-1]])
+        node = Tensor(MaxNode(node))
+        new_dim = new_dim[:-1]
+        node = node.view(list(new_dim))
+        permute_to = permute_to[:dim] + permute_to[dim + 1:]
+        return node.permute(permute_to)
+
     def mean(self, dim: int) -> "Tensor":
         p_dim = self.dim()
         d = len(p_dim) + dim if dim < 0 else dim
@@ -705,6 +721,31 @@ class SumNode(_UnaryBase):
     def backward(self, grad):
         n = self.parent.dim()[-1]
         self.parent.n.backward(grad.to_node().unsqueeze(-1).broadcast(-1, n).forward())
+
+
+class MaxNode(_UnaryBase):
+    """Row maximum of a 2-d tensor (IR extension `Max`).  Backward sends the gradient to every position that holds
+    the maximum of its row (ties share it undivided, like the comparison-based masks upstream uses for relu)."""
+
+    def forward(self):
+        v = self.val()
+        if v is not None:
+            return v
+        val = self.parent.forward()
+        assert len(self.parent.dim()) == 2, "Reduce (max) node needs dim=2"
+        id_ = self._res_id()
+        ir_b_add(("Max", val.id, id_))
+        res = Value(val.dim[:-1], id_)
+        self._val = res.clone()
+        return res
+
+    def dim(self): return self.parent.dim()[:-1]
+
+    def backward(self, grad):
+        n = self.parent.dim()[-1]
+        top = Tensor(self).unsqueeze(-1).broadcast(-1, n)
+        mask = self.parent.equal(top)
+        self.parent.n.backward((grad.to_node().unsqueeze(-1).broadcast(-1, n) * mask).forward())
 
 
 class DotProductNode(Node):

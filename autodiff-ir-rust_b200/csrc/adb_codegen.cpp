@@ -383,7 +383,14 @@ void gen_reduce(KernelSpec& k) {
     const int64_t R = k.r, S = k.split;
     const int64_t chunk = k.chunk > 0 ? k.chunk : (R + S - 1) / S;  // summed elements per partial
     std::ostringstream o;
-    o << helpers() << "struct Args { const float* in[" << std::max<size_t>(1, k.ins.size()) << "]; float* out[1]; long long n; };\n";
+    // how two partial results combine and what an empty partial is: sum (round-to-nearest adds, 0) or maximum
+    // (fmaxf: a NaN operand is ignored, -inf)
+    o << helpers()
+      << (k.red_op ? "#define ADB_IDENT __int_as_float(0xff800000)\n"
+                     "__device__ __forceinline__ float adb_comb(float a, float b) { return fmaxf(a, b); }\n"
+                   : "#define ADB_IDENT 0.0f\n"
+                     "__device__ __forceinline__ float adb_comb(float a, float b) { return __fadd_rn(a, b); }\n")
+      << "struct Args { const float* in[" << std::max<size_t>(1, k.ins.size()) << "]; float* out[1]; long long n; };\n";
 
     if (k.mode == 0) {
         // lanes along the summed axis: TPR threads cooperate on one row, 256/TPR rows per block
@@ -406,7 +413,7 @@ void gen_reduce(KernelSpec& k) {
         o << "  for (" << idx_t << " xb = (" << idx_t << ")blockIdx.x * " << RPB << "u; xb < V; xb += (" << idx_t << ")gridDim.x * " << RPB << "u) {\n";
         o << "    const " << idx_t << " x = xb + rib;\n";
         o << "    const bool valid = x < V;\n";
-        o << "    float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;\n";
+        o << "    float acc0 = ADB_IDENT, acc1 = ADB_IDENT, acc2 = ADB_IDENT, acc3 = ADB_IDENT;\n";
         o << "    if (valid) {\n";
         std::vector<std::pair<std::vector<Sub>, std::string>> seenx, seeny;
         std::vector<std::string> xo(k.ins.size());
@@ -445,18 +452,18 @@ void gen_reduce(KernelSpec& k) {
         emit_loads(o, k, vec, acc, off, names, "        ");
         emit_ssa(o, k, vec, names, acc, "        ");
         for (int l = 0; l < vec; l++)
-            o << "        acc" << l << " = __fadd_rn(acc" << l << ", v" << k.outs[0].ssa << "_" << l << ");\n";
+            o << "        acc" << l << " = adb_comb(acc" << l << ", v" << k.outs[0].ssa << "_" << l << ");\n";
         o << "      }\n    }\n";
-        o << "    float s = __fadd_rn(__fadd_rn(acc0, acc1), __fadd_rn(acc2, acc3));\n";
+        o << "    float s = adb_comb(adb_comb(acc0, acc1), adb_comb(acc2, acc3));\n";
         for (int m = std::min(TPR, 32) / 2; m >= 1; m /= 2)
-            o << "    s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, " << m << "));\n";
+            o << "    s = adb_comb(s, __shfl_xor_sync(0xffffffffu, s, " << m << "));\n";
         if (TPR > 32) {
             const int wpr = TPR / 32;
             o << "    __syncthreads();\n";
             o << "    if ((threadIdx.x & 31u) == 0u) sm[threadIdx.x >> 5] = s;\n";
             o << "    __syncthreads();\n";
             o << "    if (lane == 0u) { s = sm[rib * " << wpr << "u];";
-            for (int w = 1; w < wpr; w++) o << " s = __fadd_rn(s, sm[rib * " << wpr << "u + " << w << "u]);";
+            for (int w = 1; w < wpr; w++) o << " s = adb_comb(s, sm[rib * " << wpr << "u + " << w << "u]);";
             o << " }\n";
         }
         {
@@ -484,7 +491,7 @@ void gen_reduce(KernelSpec& k) {
         o << "  const " << idx_t << " x = ((" << idx_t << ")blockIdx.x * 32u + tx) * " << vec << "u;\n";
         o << "  const " << idx_t << " ybeg = (" << idx_t << ")blockIdx.y * " << chunk << ";\n";
         o << "  const " << idx_t << " yend = ybeg + " << chunk << " < " << R << " ? ybeg + " << chunk << " : " << R << ";\n";
-        o << "  float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;\n";
+        o << "  float acc0 = ADB_IDENT, acc1 = ADB_IDENT, acc2 = ADB_IDENT, acc3 = ADB_IDENT;\n";
         o << "  if (x < V) {\n";
         std::vector<std::pair<std::vector<Sub>, std::string>> seenx, seeny;
         std::vector<std::string> xo(k.ins.size());
@@ -523,7 +530,7 @@ void gen_reduce(KernelSpec& k) {
         emit_loads(o, k, vec, acc, off, names, "      ");
         emit_ssa(o, k, vec, names, acc, "      ");
         for (int l = 0; l < vec; l++)
-            o << "      acc" << l << " = __fadd_rn(acc" << l << ", v" << k.outs[0].ssa << "_" << l << ");\n";
+            o << "      acc" << l << " = adb_comb(acc" << l << ", v" << k.outs[0].ssa << "_" << l << ");\n";
         o << "    }\n  }\n";
         for (int l = 0; l < vec; l++) o << "  sm[ty][tx * " << vec << " + " << l << "] = acc" << l << ";\n";
         o << "  __syncthreads();\n";
@@ -537,12 +544,12 @@ void gen_reduce(KernelSpec& k) {
         int64_t out_stride = k.outs[0].dst.xsubs.empty() ? 0 : k.outs[0].dst.xsubs.back().stride;
         for (int l = 0; l < vec; l++) {
             o << "    { float s = sm[0][tx * " << vec << " + " << l << "];";
-            for (int t = 1; t < 8; t++) o << " s = __fadd_rn(s, sm[" << t << "][tx * " << vec << " + " << l << "]);";
+            for (int t = 1; t < 8; t++) o << " s = adb_comb(s, sm[" << t << "][tx * " << vec << " + " << l << "]);";
             o << " a.out[0][oo + " << l * out_stride << "] = s; }\n";
         }
         o << "  }\n}\n";
     }
-    finish(k, o.str(), k.mode ? "adb_colsum" : "adb_rowsum");
+    finish(k, o.str(), k.red_op ? (k.mode ? "adb_colmax" : "adb_rowmax") : (k.mode ? "adb_colsum" : "adb_rowsum"));
 }
 
 }  // namespace

@@ -18,6 +18,7 @@ enum Op : uint8_t {
     OP_VIEW = 12, OP_INDEX = 13, OP_CONCAT = 14, OP_PERMUTE = 15, OP_BROADCAST = 16, OP_CONTIG = 17,
     OP_EXP2 = 18, OP_LOG2 = 19, OP_SIN = 20, OP_RECIP = 21, OP_SQRT = 22,
     OP_WHILE = 23, OP_IF = 24, OP_EX = 25, OP_HEADING = 26, OP_ALLREDUCE = 27,
+    OP_MAX = 28,  // extension: row maximum of a 2-d tensor, same shape contract as OP_SUM
 };
 
 enum PayloadKind : uint8_t { PAYLOAD_INLINE = 0, PAYLOAD_HOST = 1, PAYLOAD_DEVICE = 2 };
@@ -119,7 +120,7 @@ inline void parse_cmd(Reader& r, Program& prog, Cmd& c, int depth) {
     case OP_CREATE_CONST: c.res = id(); c.cval = r.get<float>(); c.dims = read_dims(r); break;
     case OP_MUL: case OP_ADD: case OP_DOT: c.a = id(); c.b = id(); c.res = id(); break;
     case OP_MUL_EQ: case OP_ADD_EQ: c.a = id(); c.b = id(); c.res = c.a; break;
-    case OP_EQZ: case OP_GTZ: case OP_LTZ: case OP_SUM: case OP_CONTIG:
+    case OP_EQZ: case OP_GTZ: case OP_LTZ: case OP_SUM: case OP_MAX: case OP_CONTIG:
     case OP_EXP2: case OP_LOG2: case OP_SIN: case OP_RECIP: case OP_SQRT:
         c.a = id(); c.res = id(); break;
     case OP_VIEW: c.a = id(); c.res = id(); c.dims = read_dims(r); break;
@@ -220,7 +221,7 @@ inline void write_cmd(Writer& w, const Cmd& c, std::vector<std::pair<size_t, con
     case OP_CREATE_CONST: w.put<uint32_t>(c.res); w.put<float>(c.cval); w.dims(c.dims); break;
     case OP_MUL: case OP_ADD: case OP_DOT: w.put<uint32_t>(c.a); w.put<uint32_t>(c.b); w.put<uint32_t>(c.res); break;
     case OP_MUL_EQ: case OP_ADD_EQ: w.put<uint32_t>(c.a); w.put<uint32_t>(c.b); break;
-    case OP_EQZ: case OP_GTZ: case OP_LTZ: case OP_SUM: case OP_CONTIG:
+    case OP_EQZ: case OP_GTZ: case OP_LTZ: case OP_SUM: case OP_MAX: case OP_CONTIG:
     case OP_EXP2: case OP_LOG2: case OP_SIN: case OP_RECIP: case OP_SQRT:
         w.put<uint32_t>(c.a); w.put<uint32_t>(c.res); break;
     case OP_VIEW: w.put<uint32_t>(c.a); w.put<uint32_t>(c.res); w.dims(c.dims); break;

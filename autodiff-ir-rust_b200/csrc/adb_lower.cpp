@@ -60,7 +60,7 @@ void cmd_reads(const Cmd& c, uint32_t out[2], int& n) {
     switch (c.op) {
     case OP_MUL: case OP_ADD: case OP_DOT: case OP_CONCAT: case OP_MUL_EQ: case OP_ADD_EQ:
         out[n++] = c.a; out[n++] = c.b; break;
-    case OP_EQZ: case OP_GTZ: case OP_LTZ: case OP_SUM: case OP_CONTIG: case OP_EXP2: case OP_LOG2:
+    case OP_EQZ: case OP_GTZ: case OP_LTZ: case OP_SUM: case OP_MAX: case OP_CONTIG: case OP_EXP2: case OP_LOG2:
     case OP_SIN: case OP_RECIP: case OP_SQRT: case OP_VIEW: case OP_INDEX: case OP_PERMUTE:
     case OP_BROADCAST: case OP_ALLREDUCE:
         out[n++] = c.a; break;
@@ -120,6 +120,7 @@ class Lowerer {
     std::unordered_map<const Cmd*, int> mat_index_;  // CreateMat -> ordinal in program order
     std::map<std::pair<Node*, Node*>, Node*> dot_cse_;  // (A, B) -> product still in memory
     std::map<Node*, Node*> sum_cse_;                    // summand -> row sums still in memory
+    std::map<Node*, Node*> max_cse_;                    // the same for row maxima
 
     void index_mats(Block& b) {
         for (auto& c : b.cmds) {
@@ -785,7 +786,8 @@ class Lowerer {
             (void)resolve(c.res);  // shape / range checks happen at definition
             return;
         }
-        case OP_SUM: return lower_sum(c);
+        case OP_SUM: return lower_sum(c, 0);
+        case OP_MAX: return lower_sum(c, 1);
         case OP_DOT: return lower_dot(c);
         case OP_ALLREDUCE: return lower_allreduce(c);
         default: fail("internal: unexpected command in straight-line code");
@@ -860,20 +862,22 @@ class Lowerer {
         return buf;
     }
 
-    void lower_sum(const Cmd& c) {
+    // Sum (red_op 0) and Max (red_op 1) over the last axis of a 2-d value
+    void lower_sum(const Cmd& c, int red_op) {
         Node* a = resolve(c.a);
-        if (a->shape.size() != 2) fail("Reduce (sum) node needs dim=2 ('" + name(c.a) + "')");
+        if (a->shape.size() != 2) fail(std::string("Reduce (") + (red_op ? "max" : "sum") + ") node needs dim=2 ('" + name(c.a) + "')");
         int64_t V = a->shape[0], R = a->shape[1];
         consume(c.a);
-        if (a->kind == N_CONST && (a->cval == 0.0f)) {
-            after_op(c.res, g_.constant(0.0f, {V}));
+        if (a->kind == N_CONST && (red_op == 1 || a->cval == 0.0f)) {
+            after_op(c.res, g_.constant(a->cval, {V}));   // maximum of a constant row; sum of zeros
             return;
         }
         // the same reduction of the same value was computed before and is still in memory
         // (what the reference's repeat_opt does on the IR, src/ir/opts/repeat_opt.rs:5-71)
+        std::map<Node*, Node*>& cse = red_op ? max_cse_ : sum_cse_;
         {
-            auto it = sum_cse_.find(a);
-            if (it != sum_cse_.end() && g_.load_valid(it->second)) {
+            auto it = cse.find(a);
+            if (it != cse.end() && g_.load_valid(it->second)) {
                 bind_value(c.res, it->second);
                 return;
             }
@@ -901,6 +905,7 @@ class Lowerer {
             k.type = KernelSpec::REDUCE;
             k.n = p.node->shape[0];
             k.r = R;
+            k.red_op = red_op;
             if (k.n == 0) continue;
             SsaBuilder sb(*this, k, true);
             KernelSpec::Out o;
@@ -923,6 +928,7 @@ class Lowerer {
                 k2.type = KernelSpec::REDUCE;
                 k2.n = k.n;
                 k2.r = k.split;
+                k2.red_op = red_op;
                 Operand in;
                 in.buf = scratch;
                 if (k.mode == 0) {
@@ -961,8 +967,8 @@ class Lowerer {
         }
         g_.buf_version[buf]++;
         bind_own_buffer(c.res, buf, {V});
-        sum_cse_[sum_key] = bind_[c.res].node;
-        sum_cse_[g_.canon(sum_key)] = bind_[c.res].node;
+        cse[sum_key] = bind_[c.res].node;
+        cse[g_.canon(sum_key)] = bind_[c.res].node;
     }
 
     // a GEMM operand: 2-d strided read of a buffer (anything else is copied out first)
@@ -1284,6 +1290,7 @@ class Lowerer {
     bool try_fuse(StepBlock& blk, size_t r, size_t& e) {
         auto& steps = blk.steps;
         const KernelSpec& rk0 = plan_.kernels[size_t(steps[r].kernel)];
+        if (rk0.red_op != 0) return false;  // side sums only
         // second pass of a split reduce: handled together with its first pass
         if (r > 0 && steps[r - 1].kind == Step::REDUCE && r - 1 != e) {
             const KernelSpec& prev = plan_.kernels[size_t(steps[r - 1].kernel)];
@@ -1651,7 +1658,7 @@ static void dump_block(const Plan& p, const StepBlock& b, int ind, bool src, std
             int nops = 0;
             for (auto& x : k.ssa) nops += x.kind == Ssa::OP;
             if (s.kind == Step::ELW) o << pad << "#" << s.pos << " elw n=" << k.n;
-            else o << pad << "#" << s.pos << " reduce rows=" << k.n << " len=" << k.r << " mode=" << (k.mode ? "col" : "row") << " split=" << k.split;
+            else o << pad << "#" << s.pos << (k.red_op ? " reduce(max) rows=" : " reduce rows=") << k.n << " len=" << k.r << " mode=" << (k.mode ? "col" : "row") << " split=" << k.split;
             o << " ops=" << nops << " vec=" << k.vec << " ins=" << k.ins.size() << " outs=" << k.outs.size() << " " << k.entry << "\n";
             for (auto& in : k.ins)
                 o << pad << "    in  " << p.bufs[in.buf].name << "+" << in.offset << " " << (s.kind == Step::REDUCE ? subs_str(in.xsubs) + "," : "") << subs_str(in.subs) << "\n";

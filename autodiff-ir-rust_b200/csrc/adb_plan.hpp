@@ -49,6 +49,7 @@ struct KernelSpec {
     enum Type { ELW, REDUCE } type = ELW;
     int64_t n = 0;  // ELW: elements; REDUCE: rows kept (V)
     int64_t r = 0;  // REDUCE: elements summed per row (R)
+    int red_op = 0; // REDUCE: 0 = sum, 1 = maximum (fmaxf)
     std::vector<Operand> ins;
     std::vector<Ssa> ssa;
     struct Out {

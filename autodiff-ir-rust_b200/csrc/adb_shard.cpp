@@ -48,7 +48,7 @@ struct Sharder {
         n = 0;
         switch (c.op) {
         case OP_MUL: case OP_ADD: case OP_DOT: case OP_CONCAT: case OP_MUL_EQ: case OP_ADD_EQ: out[n++] = c.a; out[n++] = c.b; break;
-        case OP_EQZ: case OP_GTZ: case OP_LTZ: case OP_SUM: case OP_CONTIG: case OP_EXP2: case OP_LOG2: case OP_SIN:
+        case OP_EQZ: case OP_GTZ: case OP_LTZ: case OP_SUM: case OP_MAX: case OP_CONTIG: case OP_EXP2: case OP_LOG2: case OP_SIN:
         case OP_RECIP: case OP_SQRT: case OP_VIEW: case OP_INDEX: case OP_PERMUTE: case OP_BROADCAST: case OP_ALLREDUCE:
             out[n++] = c.a; break;
         default: break;
@@ -236,6 +236,19 @@ struct Sharder {
                 else set(c.res, T_PART, 0, g, c);
             } else if (a.tag == T_PART) set(c.res, T_PART, 0, g, c);
             else set(c.res, T_REP, 0, g, c);
+            return;
+        }
+        case OP_MAX: {
+            // not linear: a partial operand is summed over the ranks first; a maximum along the batch itself
+            // would need a max-reduction across ranks, which this rewrite does not have
+            resolve_partial(c.a, out);
+            Info a = info[c.a];
+            if (a.dims.size() != 2) fail("Max needs a 2-d operand");
+            std::vector<int64_t> g{a.dims[0]};
+            if (a.tag == T_SHARD) {
+                if (a.axis != 0) fail("Max of '" + name(c.a) + "' runs along the sharded batch axis");
+                set(c.res, T_SHARD, 0, g, c);
+            } else set(c.res, T_REP, 0, g, c);
             return;
         }
         case OP_DOT: {

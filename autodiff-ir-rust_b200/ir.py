@@ -34,6 +34,9 @@ OPC = {
     "While": 23, "If": 24, "EX": 25, "Heading": 26,
     # extension (no counterpart in the reference): in-place sum of `id` over all data-parallel ranks
     "AllReduce": 27,
+    # extension: row maximum of a 2-d tensor, same shape contract as Sum (the reference's kernel layer names
+    # `ReduceOp::Max`, src/kernel/kernel_decl.rs:77, but no IR command reaches it)
+    "Max": 28,
 }
 
 PAYLOAD_INLINE = 0   # u64 = byte offset of the data inside the blob
@@ -184,7 +187,7 @@ class _Writer:
             self.u32(self.idx(c[1])); self.u32(self.idx(c[2])); self.u32(self.idx(c[3]))
         elif k in ("ElwMultiplyEq", "ElwAddEq"):
             self.u32(self.idx(c[1])); self.u32(self.idx(c[2]))
-        elif k in ("EqualZero", "MoreZero", "LessZero", "Sum", "Contigious",
+        elif k in ("EqualZero", "MoreZero", "LessZero", "Sum", "Max", "Contigious",
                    "Exp2", "Log2", "Sin", "Recip", "Sqrt"):
             self.u32(self.idx(c[1])); self.u32(self.idx(c[2]))
         elif k == "View":

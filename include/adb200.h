@@ -58,6 +58,8 @@ typedef enum adb_status {
  *     24 If u32 n, n x { cond, procedure }, u8 has_else, [procedure]
  *     25 EX                      26 Heading u16 len, bytes
  *     27 AllReduce id   (extension, no reference counterpart: in-place sum over all ranks)
+ *     28 Max a, res     (extension: row maximum of a 2-d tensor, same shape contract as Sum; the reference's kernel
+ *                        layer names ReduceOp::Max, src/kernel/kernel_decl.rs:77, but no IR command reaches it)
  */
 #define ADB_IR_MAGIC 0x52494441u
 #define ADB_IR_VERSION 1u

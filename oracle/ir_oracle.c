@@ -144,7 +144,7 @@ static int parse_cmd(Oracle *o, Rd *r, Cmd *c, int depth) {
     case 2: c->res = r32(r); c->cval = rf32(r); rdims(r, c); break;
     case 3: case 4: case 11: c->a = r32(r); c->b = r32(r); c->res = r32(r); break;
     case 5: case 6: c->a = r32(r); c->b = r32(r); c->res = c->a; break;
-    case 7: case 8: case 9: case 10: case 17: case 18: case 19: case 20: case 21: case 22:
+    case 7: case 8: case 9: case 10: case 17: case 18: case 19: case 20: case 21: case 22: case 28:
         c->a = r32(r); c->res = r32(r); break;
     case 12: c->a = r32(r); c->res = r32(r); rdims(r, c); break;
     case 13: c->a = r32(r); c->res = r32(r); c->index = r64(r); c->dim = r32(r); break;
@@ -217,7 +217,7 @@ static void scan_uses(Oracle *o, Proc *p, int top, uint32_t outer_pos) {
         case 3: case 4: case 11: case 14: mark_use(o, c->a, pos); mark_use(o, c->b, pos); break;
         case 5: case 6: mark_use(o, c->a, pos); mark_use(o, c->b, pos); break;
         case 7: case 8: case 9: case 10: case 12: case 13: case 15: case 16: case 17:
-        case 18: case 19: case 20: case 21: case 22: case 27:
+        case 18: case 19: case 20: case 21: case 22: case 27: case 28:
             mark_use(o, c->a, pos); break;
         case 23: mark_use(o, c->a, pos); scan_uses(o, &c->block, 0, pos); break;
         case 24:
@@ -512,6 +512,26 @@ static int exec_cmd(Oracle *o, Cmd *c) {
             const float *row = a + x * rs;
             if (f64) { double s = 0; for (uint64_t y = 0; y < rs; y++) s += row[y]; out[x] = (float)s; }
             else { float s = 0; for (uint64_t y = 0; y < rs; y++) s += row[y]; out[x] = s; }
+        }
+        if (oa) pool_free(a);
+        uint64_t dims[1] = { vs };
+        bind_buf(o, c->res, out, dims, 1);
+        return 0;
+    }
+    case 28: { /* Max over the last axis of a 2-d tensor (IR extension; fmaxf semantics: a NaN operand is ignored) */
+        if (check_defined(o, c->a)) return -1;
+        const Var *va = &V[c->a];
+        if (va->nd != 2) { snprintf(o->err, sizeof o->err, "oracle: Max needs a 2-d input ('%s')", o->names[c->a]); return -1; }
+        uint64_t vs = va->dims[0], rs = va->dims[1];
+        int oa;
+        float *a = materialize(o, c->a, &oa);
+        float *out = pool_alloc((size_t)vs);
+#pragma omp parallel for schedule(static) if (vs * rs > 65536)
+        for (uint64_t x = 0; x < vs; x++) {
+            const float *row = a + x * rs;
+            float m = -INFINITY;
+            for (uint64_t y = 0; y < rs; y++) m = fmaxf(m, row[y]);
+            out[x] = m;
         }
         if (oa) pool_free(a);
         uint64_t dims[1] = { vs };

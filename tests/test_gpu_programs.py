@@ -380,3 +380,30 @@ def test_plan_cache_is_bounded_and_evicted_programs_still_run():
         assert run(1) > 0.0         # evicted: lowered again
     finally:
         dev.close()
+
+
+@pytest.mark.parametrize("shape,axis", [([4096], 0), ([300, 33], 1), ([300, 33], 0), ([2, 40000], 1), ([9000, 64], 0),
+                                        ([8, 16, 32], 1), ([257, 4096], 1)])
+def test_max_reduce_every_launch_shape(shape, axis):
+    """Row / column launch shapes and the two-pass split of the reduce kernels, with maximum instead of sum:
+    bit-exact against the oracle (a maximum involves no rounding), gradient mask included."""
+    n = int(np.prod(shape))
+    x = rnd(n)
+
+    def prog(dev):
+        ad.set_device(dev)
+        t = ad.tensor(x, shape)
+        m = (t * 1.5).max(axis)
+        total = m
+        while len(total.dim()) > 1:
+            total = total.sum(len(total.dim()) - 1)
+        total = total.sum(0)
+        total.forward()
+        total.backward()
+        mv = m.forward()
+        mv.keep()
+        ad.execute()
+        return {"max": mv.get(), "grad": t.grad().get()}
+    want, got = run_both(prog)
+    assert_exact("max", got["max"], want["max"])
+    assert_exact("grad", got["grad"], want["grad"])

@@ -74,6 +74,12 @@ def test_reference_and_benchmark_programs_under_sanitizers(hostcheck, tmp_path):
     cfg.c3_reduce_movement(cap, batch=8, n=16)
     cfg.c4_mlp_train(cap, batch=2048, widths=(64, 128, 128, 64, 16), steps=2)
     cfg.c5_dot_loop(cap, n=32, max_iters=3)
+    adb.autodiff.set_device(cap)                                # row / column maxima (IR extension)
+    t = adb.autodiff.tensor(np.arange(300 * 40, dtype=np.float32), [300, 40])
+    for axis in (0, 1):
+        m = t.max(axis).forward()
+        m.keep()
+    adb.autodiff.execute()
     files = _write(tmp_path, cap.blobs)
     for flags in (0, 1, 2, 4):
         out = _run(hostcheck, files, flags=flags)
