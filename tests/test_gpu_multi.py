@@ -12,7 +12,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 KW = dict(batch=256, widths=(64, 128, 128, 64, 16), steps=4, lr=1e-2)
 
 
-def _worker(rank, world, port, out_dir, flags):
+def _worker(rank, world, port, out_dir, flags, kw=None):
+    kw = kw or KW
     sys.path.insert(0, ROOT)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     import torch
@@ -24,9 +25,9 @@ def _worker(rank, world, port, out_dir, flags):
     adb = importlib.import_module("autodiff-ir-rust_b200")
     box = [adb.devices.nccl_unique_id() if rank == 0 else None]
     dist.broadcast_object_list(box, src=0)
-    dev = adb.devices.B200(rank, rank=rank, world_size=world, nccl_unique_id=box[0], shard_batch=KW["batch"], flags=flags)
-    inputs = adb.configs.c4_inputs(batch=KW["batch"], widths=KW["widths"])     # full tensors: the device takes its rows
-    out = adb.configs.c4_mlp_train(dev, inputs=inputs, **KW)
+    dev = adb.devices.B200(rank, rank=rank, world_size=world, nccl_unique_id=box[0], shard_batch=kw["batch"], flags=flags)
+    inputs = adb.configs.c4_inputs(batch=kw["batch"], widths=kw["widths"])     # full tensors: the device takes its rows
+    out = adb.configs.c4_mlp_train(dev, inputs=inputs, **kw)
     np.savez(os.path.join(out_dir, f"rank{rank}.npz"), **{k: v.numpy() for k, v in out.items()})
     dev.close()
     dist.destroy_process_group()
@@ -44,6 +45,29 @@ def test_two_gpus_match_one_gpu(tmp_path, flags):
     mp.spawn(_worker, args=(2, port, str(tmp_path), flags), nprocs=2, join=True)
     dev = adb.devices.B200(0)
     want = adb.configs.c4_mlp_train(dev, inputs=adb.configs.c4_inputs(batch=KW["batch"], widths=KW["widths"]), **KW)
+    dev.close()
+    for r in range(2):
+        got = np.load(tmp_path / f"rank{r}.npz")
+        for k, v in want.items():
+            ref = v.numpy()
+            err = np.abs(got[k] - ref).max() / max(np.abs(ref).max(), 1e-30)
+            assert err < 1e-4, (r, k, err)
+
+
+def test_two_gpus_match_one_gpu_at_the_benchmark_widths(tmp_path):
+    """The benchmark network (4096-8192-8192-4096-1000) at batch 8192: tensor-core dot products on CTA pairs, sums
+    fused into the element-wise passes, NCCL all-reduce of 553 MB of gradients per step; two steps, 2 GPUs against 1."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    adb = importlib.import_module("autodiff-ir-rust_b200")
+    kw = dict(batch=8192, widths=adb.configs.C4_WIDTHS, steps=2, lr=1e-3)
+    port = 29700 + (os.getpid() % 2000)
+    mp.spawn(_worker, args=(2, port, str(tmp_path), 0, kw), nprocs=2, join=True)
+    dev = adb.devices.B200(0)
+    want = adb.configs.c4_mlp_train(dev, inputs=adb.configs.c4_inputs(batch=kw["batch"], widths=kw["widths"]), **kw)
+    assert dev.stats()["tc_gemm_launches"] == 22
     dev.close()
     for r in range(2):
         got = np.load(tmp_path / f"rank{r}.npz")
