@@ -106,9 +106,10 @@ Access classify(const std::vector<Sub>& subs, int64_t offset, int vec, bool is_s
 bool lanes_ok(const std::vector<Sub>& subs) { return subs.empty() || subs.back().size % 4 == 0; }
 
 void emit_ssa(std::ostringstream& o, const KernelSpec& k, int vec, const std::vector<std::string>& load_names,
-              const std::vector<Access>& acc, const char* ind) {
+              const std::vector<Access>& acc, const char* ind, const std::vector<char>* need = nullptr) {
     static const char L[4] = {'x', 'y', 'z', 'w'};
     for (size_t i = 0; i < k.ssa.size(); i++) {
+        if (need && !(*need)[i]) continue;
         const Ssa& s = k.ssa[i];
         for (int l = 0; l < vec; l++) {
             std::string lhs = "v" + std::to_string(i) + "_" + std::to_string(l);
@@ -120,6 +121,8 @@ void emit_ssa(std::ostringstream& o, const KernelSpec& k, int vec, const std::ve
                 else o << nm << "_" << l;
             } else if (s.kind == Ssa::CONST) {
                 o << hexf(s.c);
+            } else if (s.kind == Ssa::RED) {
+                o << "red" << s.operand;
             } else {
                 std::string a = "v" + std::to_string(s.a) + "_" + std::to_string(l);
                 std::string b = s.b >= 0 ? "v" + std::to_string(s.b) + "_" + std::to_string(l) : "";
@@ -142,11 +145,13 @@ void emit_ssa(std::ostringstream& o, const KernelSpec& k, int vec, const std::ve
 }
 
 void emit_loads(std::ostringstream& o, const KernelSpec& k, int vec, const std::vector<Access>& acc,
-                const std::vector<std::string>& off, std::vector<std::string>& names, const char* ind) {
+                const std::vector<std::string>& off, std::vector<std::string>& names, const char* ind,
+                const std::vector<char>* need = nullptr) {
     names.resize(k.ins.size());
     for (size_t i = 0; i < k.ins.size(); i++) {
         std::string nm = "l" + std::to_string(i);
         names[i] = nm;
+        if (need && !(*need)[i]) continue;
         std::string p = "a.in[" + std::to_string(i) + "]";
         if (vec == 1 || acc[i].mode == Access::SCALAR)
             o << ind << "const float " << nm << " = " << p << "[" << off[i] << "];\n";
@@ -358,6 +363,132 @@ void gen_elw_red(KernelSpec& k) {
     }
     o << "}\n";
     finish(k, o.str(), "adb_elwsum");
+}
+
+// Row reductions and the element-wise work that depends on them in one kernel: one block walks one row of the
+// [P, Q] space at a time.  Phase k loops over the row, reduces its value across the block (warp shuffles, then
+// eight partials in shared memory combined in a fixed order) and leaves the result in a register every thread
+// holds; later phases and the final store loop read the row again (it was just read by the same block, so it comes
+// from L1 / L2, not from HBM) and use those registers.
+void gen_rows(KernelSpec& k) {
+    std::vector<const Operand*> ops;
+    for (auto& i : k.ins) ops.push_back(&i);
+    for (auto& o : k.outs) ops.push_back(&o.dst);
+    k.wide_index = needs_wide(k.n, ops);
+    const char* idx_t = k.wide_index ? "long long" : "unsigned int";
+    const int64_t P = k.p2, Q = k.q2;
+    int vec = 4;
+    if (Q % 4) vec = 1;
+    for (auto& i : k.ins)
+        if (!lanes_ok(i.subs)) vec = 1;
+    for (auto& o : k.outs)
+        if (!lanes_ok(o.dst.subs) || o.dst.subs.empty() || o.dst.subs.back().stride == 0) vec = 1;
+    k.vec = vec;
+    k.threads = 256;
+    std::vector<Access> in_acc(k.ins.size()), out_acc(k.outs.size());
+    for (size_t i = 0; i < k.ins.size(); i++) in_acc[i] = classify(k.ins[i].subs, k.ins[i].offset, vec, false);
+    for (size_t i = 0; i < k.outs.size(); i++) out_acc[i] = classify(k.outs[i].dst.subs, k.outs[i].dst.offset, vec, true);
+
+    // which SSA values (and loads) a set of roots needs
+    auto slice = [&](const std::vector<int>& roots, std::vector<char>& need, std::vector<char>& need_in) {
+        need.assign(k.ssa.size(), 0);
+        need_in.assign(k.ins.size(), 0);
+        for (int r : roots) need[size_t(r)] = 1;
+        for (size_t i = k.ssa.size(); i-- > 0;) {
+            if (!need[i]) continue;
+            const Ssa& s = k.ssa[i];
+            if (s.kind == Ssa::OP) {
+                need[size_t(s.a)] = 1;
+                if (s.b >= 0) need[size_t(s.b)] = 1;
+            } else if (s.kind == Ssa::LOAD) need_in[size_t(s.operand)] = 1;
+        }
+    };
+
+    std::ostringstream o;
+    o << helpers() << "struct Args { const float* in[" << std::max<size_t>(1, k.ins.size()) << "]; float* out["
+      << k.outs.size() + k.phases.size() << "]; long long n; };\n";
+    o << "extern \"C\" __global__ void __launch_bounds__(256) @ENTRY@(const __grid_constant__ Args a) {\n";
+    o << "  __shared__ float sm[8];\n";
+    o << "  const unsigned int lane = threadIdx.x & 31u, wrp = threadIdx.x >> 5;\n";
+    o << "  for (" << idx_t << " p = blockIdx.x; p < " << P << "; p += gridDim.x) {\n";
+    auto body_prefix = [&](const std::vector<char>& need_in, std::vector<std::string>& in_off, std::vector<std::string>& out_off,
+                           bool with_outs) {
+        o << "    for (" << idx_t << " q = threadIdx.x * " << vec << "u; q < " << Q << "; q += " << 256 * vec << "u) {\n";
+        o << "      const " << idx_t << " i = p * " << Q << " + q;\n";
+        std::vector<std::pair<std::vector<Sub>, std::string>> seen;
+        auto offset_of = [&](const std::vector<Sub>& subs) {
+            for (auto& s : seen)
+                if (s.first == subs) return s.second;
+            std::ostringstream pre;
+            std::string tag = std::to_string(seen.size());
+            std::string e = offset_expr(subs, "i", pre, tag, idx_t);
+            o << pre.str();
+            std::string var = "o" + tag;
+            o << "      const " << idx_t << " " << var << " = " << e << ";\n";
+            seen.push_back({subs, var});
+            return var;
+        };
+        in_off.assign(k.ins.size(), "0");
+        for (size_t i = 0; i < k.ins.size(); i++)
+            if (need_in[i]) in_off[i] = offset_of(k.ins[i].subs);
+        out_off.assign(k.outs.size(), "0");
+        if (with_outs)
+            for (size_t i = 0; i < k.outs.size(); i++) out_off[i] = offset_of(k.outs[i].dst.subs);
+    };
+    for (size_t ph = 0; ph < k.phases.size(); ph++) {
+        const auto& phs = k.phases[ph];
+        const char* ident = phs.red_op ? "__int_as_float(0xff800000)" : "0.0f";
+        auto comb = [&](const std::string& x, const std::string& y) {
+            return (phs.red_op ? "fmaxf(" : "__fadd_rn(") + x + ", " + y + ")";
+        };
+        std::vector<char> need, need_in;
+        slice({phs.ssa}, need, need_in);
+        o << "    float red" << ph << ";\n    {\n";
+        for (int l = 0; l < vec; l++) o << "    float acc" << l << " = " << ident << ";\n";
+        std::vector<std::string> in_off, out_off, names;
+        body_prefix(need_in, in_off, out_off, false);
+        emit_loads(o, k, vec, in_acc, in_off, names, "      ", &need_in);
+        emit_ssa(o, k, vec, names, in_acc, "      ", &need);
+        for (int l = 0; l < vec; l++)
+            o << "      acc" << l << " = " << comb("acc" + std::to_string(l), "v" + std::to_string(phs.ssa) + "_" + std::to_string(l)) << ";\n";
+        o << "    }\n";
+        if (vec == 4) o << "    float s = " << comb(comb("acc0", "acc1"), comb("acc2", "acc3")) << ";\n";
+        else o << "    float s = acc0;\n";
+        o << "    for (int m = 16; m > 0; m >>= 1) s = " << comb("s", "__shfl_xor_sync(0xffffffffu, s, m)") << ";\n";
+        o << "    __syncthreads();\n";   // the previous phase's readers of sm are done
+        o << "    if (lane == 0u) sm[wrp] = s;\n";
+        o << "    __syncthreads();\n";
+        o << "    s = sm[0];\n";
+        o << "    for (int w = 1; w < 8; w++) s = " << comb("s", "sm[w]") << ";\n";
+        o << "    red" << ph << " = s;\n";
+        o << "    if (threadIdx.x == 0u) a.out[" << k.outs.size() + ph << "][p] = s;\n";
+        o << "    }\n";
+    }
+    if (!k.outs.empty()) {
+        std::vector<int> roots;
+        for (auto& out : k.outs) roots.push_back(out.ssa);
+        std::vector<char> need, need_in;
+        slice(roots, need, need_in);
+        std::vector<std::string> in_off, out_off, names;
+        body_prefix(need_in, in_off, out_off, true);
+        emit_loads(o, k, vec, in_acc, in_off, names, "      ", &need_in);
+        emit_ssa(o, k, vec, names, in_acc, "      ", &need);
+        for (size_t i = 0; i < k.outs.size(); i++) {
+            std::string pp = "a.out[" + std::to_string(i) + "]";
+            std::string v = "v" + std::to_string(k.outs[i].ssa);
+            if (vec == 1)
+                o << "      " << pp << "[" << out_off[i] << "] = " << v << "_0;\n";
+            else if (out_acc[i].mode == Access::VEC4)
+                o << "      *reinterpret_cast<float4*>(" << pp << " + (" << out_off[i] << ")) = make_float4(" << v << "_0, " << v
+                  << "_1, " << v << "_2, " << v << "_3);\n";
+            else
+                for (int l = 0; l < 4; l++)
+                    o << "      " << pp << "[(" << out_off[i] << ") + " << l * out_acc[i].lane_stride << "] = " << v << "_" << l << ";\n";
+        }
+        o << "    }\n";
+    }
+    o << "  }\n}\n";
+    finish(k, o.str(), "adb_rows");
 }
 
 // -------------------------------------------------------------------------------- reduce
@@ -619,6 +750,7 @@ void generate_kernels(Plan& plan) {
     for (auto& k : plan.kernels) {
         if (!k.source.empty() || k.dead) continue;
         if (k.type == KernelSpec::ELW) gen_elw(k);
+        else if (k.type == KernelSpec::ROWS) gen_rows(k);
         else gen_reduce(k);
     }
 }

@@ -1209,6 +1209,7 @@ class Lowerer {
             for (auto& in : k.ins) rd.push_back(in.buf);
             for (auto& o : k.outs) wr.push_back(o.dst.buf);
             for (auto& r : k.reds) wr.push_back(r.dst.buf);
+            for (auto& ph : k.phases) wr.push_back(ph.dst.buf);
             break;
         }
         case Step::GEMM: rd = {s.gemm.a, s.gemm.b}; wr = {s.gemm.c}; break;
@@ -1244,7 +1245,171 @@ class Lowerer {
         }
         for (auto& sp : loop_spans_) { sp.first *= POS_SCALE; sp.second *= POS_SCALE; }
         pos_ *= POS_SCALE;
+        fuse_rows(plan_.main);
         fuse_block(plan_.main);
+    }
+
+    // ------------------------------------------------------------------ row reductions chained with their consumers
+    // mean -> variance -> normalise, max -> sum of exponentials -> divide: consecutive steps over the same [P, Q]
+    // space in which later ones read the per-row results of earlier ones.  As separate kernels every step streams
+    // the input again; as one ROWS kernel (one block per row, section "gen_rows" of the code generator) the input
+    // comes from HBM once.  Only adjacent steps are chained, rows of 512 .. 16384 elements, and the per-row results
+    // are still written out (other steps may read them).
+    void fuse_rows(StepBlock& blk) {
+        for (auto& s : blk.steps) {
+            if (s.body) fuse_rows(*s.body);
+            for (auto& br : s.branches) fuse_rows(*br.body);
+            if (s.else_body) fuse_rows(*s.else_body);
+        }
+        auto& steps = blk.steps;
+        for (size_t i = 0; i < steps.size(); i++) {
+            if (steps[i].kind != Step::REDUCE) continue;
+            const KernelSpec& first = plan_.kernels[size_t(steps[i].kernel)];
+            if (first.scratch >= 0 || first.split != 1 || first.mode != 0) continue;
+            const int64_t P = first.n, Q = first.r;
+            const bool small_ok = opt_.fuse_small_sums;
+            if (!small_ok && (P < 64 || Q < 512 || Q > 16384 || P * Q < FUSE_MIN_ELEMS)) continue;
+            if (P < 1 || Q < 1) continue;
+
+            KernelSpec rk;
+            rk.type = KernelSpec::ROWS;
+            rk.n = P * Q;
+            rk.p2 = P;
+            rk.q2 = Q;
+            std::map<std::tuple<int, int, uint32_t, int, int, int>, int> known;
+            auto key_of = [](const Ssa& v) {
+                uint32_t bits;
+                std::memcpy(&bits, &v.c, 4);
+                int a = v.kind == Ssa::OP ? v.a : -1, b = v.kind == Ssa::OP ? v.b : -1;
+                if (v.kind == Ssa::OP && b >= 0 && a > b) std::swap(a, b);
+                return std::make_tuple(int(v.kind), (v.kind == Ssa::LOAD || v.kind == Ssa::RED) ? v.operand : -1,
+                                       v.kind == Ssa::CONST ? bits : 0u, v.kind == Ssa::OP ? int(v.op) : -1, a, b);
+            };
+            auto intern = [&](Ssa v) {
+                auto it = known.find(key_of(v));
+                if (it != known.end()) return it->second;
+                rk.ssa.push_back(v);
+                known.emplace(key_of(v), int(rk.ssa.size()) - 1);
+                return int(rk.ssa.size()) - 1;
+            };
+            std::vector<int> written;   // buffers the chain writes (phase results, final outputs)
+            auto phase_of = [&](const Operand& o, const std::vector<Sub>& flat) -> int {
+                // a load of an earlier phase's per-row result, broadcast along the row?
+                std::vector<Sub> want;
+                if (P > 1) want.push_back({P, 1});
+                if (Q > 1) want.push_back({Q, 0});
+                canon_subs(want);
+                for (size_t k = 0; k < rk.phases.size(); k++)
+                    if (rk.phases[k].dst.buf == o.buf && rk.phases[k].dst.offset == o.offset && flat == want) return int(k);
+                return -1;
+            };
+            // adds one step to the ROWS kernel under construction; false = the chain ends before it
+            auto absorb = [&](const KernelSpec& k) {
+                const bool is_reduce = k.type == KernelSpec::REDUCE;
+                if (is_reduce) {
+                    // lanes along the summed axis only: a column sum walks memory with a large stride per row
+                    if (k.mode != 0 || k.n != P || k.r != Q || k.scratch >= 0 || k.split != 1) return false;
+                    std::vector<Sub> d = k.outs[0].dst.xsubs;
+                    canon_subs(d);
+                    std::vector<Sub> contiguous;
+                    if (P > 1) contiguous.push_back({P, 1});
+                    if (d != contiguous) return false;
+                } else {
+                    if (k.type != KernelSpec::ELW || k.n != P * Q || !k.reds.empty()) return false;
+                }
+                // operands
+                std::vector<int> in_of(k.ins.size(), -1), red_of(k.ins.size(), -1);
+                const size_t ins_before = rk.ins.size();
+                for (size_t t = 0; t < k.ins.size(); t++) {
+                    const Operand& o = k.ins[t];
+                    std::vector<Sub> flat = is_reduce ? flat_digits(o, true) : o.subs;
+                    canon_subs(flat);
+                    const bool chain_written = std::find(written.begin(), written.end(), o.buf) != written.end();
+                    if (chain_written) {
+                        red_of[t] = phase_of(o, flat);
+                        if (red_of[t] < 0) { rk.ins.resize(ins_before); return false; }
+                        continue;
+                    }
+                    Operand no;
+                    no.buf = o.buf;
+                    no.offset = o.offset;
+                    no.subs = flat;
+                    for (size_t u = 0; u < rk.ins.size(); u++)
+                        if (rk.ins[u].same_access(no)) in_of[t] = int(u);
+                    if (in_of[t] < 0) {
+                        rk.ins.push_back(no);
+                        in_of[t] = int(rk.ins.size()) - 1;
+                    }
+                }
+                // outputs must not touch anything the chain reads or wrote
+                for (auto& out : k.outs) {
+                    for (auto& in : rk.ins)
+                        if (in.buf == out.dst.buf) { rk.ins.resize(ins_before); return false; }
+                    if (std::find(written.begin(), written.end(), out.dst.buf) != written.end()) { rk.ins.resize(ins_before); return false; }
+                }
+                // splice the SSA
+                std::vector<int> remap(k.ssa.size(), -1);
+                for (size_t t = 0; t < k.ssa.size(); t++) {
+                    Ssa v = k.ssa[t];
+                    if (v.kind == Ssa::LOAD) {
+                        if (red_of[size_t(v.operand)] >= 0) { v.kind = Ssa::RED; v.operand = red_of[size_t(v.operand)]; }
+                        else v.operand = in_of[size_t(v.operand)];
+                    } else if (v.kind == Ssa::OP) {
+                        v.a = remap[size_t(v.a)];
+                        if (v.b >= 0) v.b = remap[size_t(v.b)];
+                    }
+                    remap[t] = intern(v);
+                }
+                if (is_reduce) {
+                    KernelSpec::Phase ph;
+                    ph.red_op = k.red_op;
+                    ph.ssa = remap[size_t(k.outs[0].ssa)];
+                    ph.dst = k.outs[0].dst;
+                    rk.phases.push_back(ph);
+                    written.push_back(ph.dst.buf);
+                } else {
+                    for (auto& out : k.outs) {
+                        KernelSpec::Out no = out;
+                        no.ssa = remap[size_t(out.ssa)];
+                        rk.outs.push_back(no);
+                        written.push_back(out.dst.buf);
+                    }
+                }
+                return true;
+            };
+
+            size_t j = i;
+            bool uses_result = false;
+            while (j < steps.size() && rk.phases.size() < 4) {
+                const Step& st = steps[j];
+                if (st.kind != Step::REDUCE && st.kind != Step::ELW) break;
+                const KernelSpec& k = plan_.kernels[size_t(st.kernel)];
+                if (!absorb(k)) break;
+                j++;
+                if (st.kind == Step::ELW) break;   // the store loop closes the chain
+            }
+            for (auto& v : rk.ssa) uses_result = uses_result || v.kind == Ssa::RED;
+            const size_t count = j - i;
+            if (count < 2 || !uses_result || rk.phases.empty()) continue;
+
+            // commit: one ROWS step at the position of the last chain member
+            const int pos = steps[j - 1].pos;
+            for (size_t q = i; q < j; q++) plan_.kernels[size_t(steps[q].kernel)].dead = true;
+            plan_.kernels.push_back(std::move(rk));
+            Step ns;
+            ns.kind = Step::ELW;
+            ns.pos = pos;
+            ns.kernel = int(plan_.kernels.size()) - 1;
+            {
+                std::vector<int> rd, wr;
+                const KernelSpec& nk = plan_.kernels.back();
+                for (auto& in : nk.ins) touch(in.buf, pos);
+                for (auto& out : nk.outs) touch(out.dst.buf, pos);
+                for (auto& ph : nk.phases) touch(ph.dst.buf, pos);
+            }
+            steps.erase(steps.begin() + long(i), steps.begin() + long(j));
+            steps.insert(steps.begin() + long(i), std::move(ns));
+        }
     }
 
     void fuse_block(StepBlock& blk) {
@@ -1255,6 +1420,7 @@ class Lowerer {
         }
         for (size_t e = 0; e < blk.steps.size(); e++) {
             if (blk.steps[e].kind != Step::ELW) continue;
+            if (plan_.kernels[size_t(blk.steps[e].kernel)].type != KernelSpec::ELW) continue;
             if (plan_.kernels[size_t(blk.steps[e].kernel)].n < (opt_.fuse_small_sums ? 1 : FUSE_MIN_ELEMS)) continue;
             bool again = true;
             while (again && plan_.kernels[size_t(blk.steps[e].kernel)].reds.size() < 4) {
@@ -1657,13 +1823,17 @@ static void dump_block(const Plan& p, const StepBlock& b, int ind, bool src, std
             auto& k = p.kernels[s.kernel];
             int nops = 0;
             for (auto& x : k.ssa) nops += x.kind == Ssa::OP;
-            if (s.kind == Step::ELW) o << pad << "#" << s.pos << " elw n=" << k.n;
+            if (k.type == KernelSpec::ROWS) o << pad << "#" << s.pos << " rows [" << k.p2 << "," << k.q2 << "] phases=" << k.phases.size();
+            else if (s.kind == Step::ELW) o << pad << "#" << s.pos << " elw n=" << k.n;
             else o << pad << "#" << s.pos << (k.red_op ? " reduce(max) rows=" : " reduce rows=") << k.n << " len=" << k.r << " mode=" << (k.mode ? "col" : "row") << " split=" << k.split;
             o << " ops=" << nops << " vec=" << k.vec << " ins=" << k.ins.size() << " outs=" << k.outs.size() << " " << k.entry << "\n";
             for (auto& in : k.ins)
                 o << pad << "    in  " << p.bufs[in.buf].name << "+" << in.offset << " " << (s.kind == Step::REDUCE ? subs_str(in.xsubs) + "," : "") << subs_str(in.subs) << "\n";
             for (auto& out : k.outs)
                 o << pad << "    out " << p.bufs[out.dst.buf].name << "+" << out.dst.offset << " " << (s.kind == Step::REDUCE ? subs_str(out.dst.xsubs) : subs_str(out.dst.subs)) << "\n";
+            for (auto& ph : k.phases)
+                o << pad << "    " << (ph.red_op ? "max" : "sum") << " v" << ph.ssa << " along each row -> " << p.bufs[ph.dst.buf].name << "+"
+                  << ph.dst.offset << "\n";
             for (auto& rd : k.reds)
                 o << pad << "    sum v" << rd.ssa << " over " << (rd.axis == 0 ? "columns" : "rows") << " of [" << k.p2 << "," << k.q2
                   << "] -> " << p.bufs[rd.dst.buf].name << " " << subs_str(rd.dst.subs) << " (rows per block " << k.row_chunk << ")\n";
@@ -1672,6 +1842,7 @@ static void dump_block(const Plan& p, const StepBlock& b, int ind, bool src, std
                     auto& x = k.ssa[i];
                     o << pad << "      v" << i << " = ";
                     if (x.kind == Ssa::LOAD) o << "load in" << x.operand;
+                    else if (x.kind == Ssa::RED) o << "row result " << x.operand;
                     else if (x.kind == Ssa::CONST) o << x.c;
                     else if (x.b >= 0) o << "v" << x.a << " " << eop_name(x.op) << " v" << x.b;
                     else o << eop_name(x.op) << "(v" << x.a << ")";

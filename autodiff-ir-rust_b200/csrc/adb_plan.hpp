@@ -38,15 +38,17 @@ struct Operand {
 };
 
 struct Ssa {
-    enum Kind : uint8_t { LOAD, CONST, OP } kind = CONST;
-    int operand = -1;  // LOAD
+    enum Kind : uint8_t { LOAD, CONST, OP, RED } kind = CONST;
+    int operand = -1;  // LOAD: index into ins; RED (ROWS kernels): index of the row reduction whose result this is
     float c = 0.f;     // CONST
     EOp op = E_ADD;    // OP
     int a = -1, b = -1;
 };
 
 struct KernelSpec {
-    enum Type { ELW, REDUCE } type = ELW;
+    // ROWS: several reductions along the rows of a [p2, q2] space and the element-wise work that uses their
+    // results, one block per row at a time (a normalisation layer in one pass over its input)
+    enum Type { ELW, REDUCE, ROWS } type = ELW;
     int64_t n = 0;  // ELW: elements; REDUCE: rows kept (V)
     int64_t r = 0;  // REDUCE: elements summed per row (R)
     int red_op = 0; // REDUCE: 0 = sum, 1 = maximum (fmaxf)
@@ -67,6 +69,14 @@ struct KernelSpec {
         Operand dst;  // scratch buffer of the partial sums (contiguous)
     };
     std::vector<Red> reds;
+    // ROWS only: the row reductions in the order they are computed; phase k may use the results of phases < k
+    // (Ssa::RED).  Each result is also stored to its destination ([p2] values, contiguous).
+    struct Phase {
+        int red_op = 0;   // 0 sum, 1 maximum
+        int ssa = -1;     // the value that is reduced
+        Operand dst;
+    };
+    std::vector<Phase> phases;
     int64_t p2 = 0, q2 = 0;
     int64_t row_chunk = 0;  // rows per blockIdx.y (a multiple of 8)
     bool dead = false;      // no step refers to this kernel any more (its work moved into another kernel)

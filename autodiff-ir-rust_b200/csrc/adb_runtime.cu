@@ -275,7 +275,17 @@ class Executor {
         args[ni + no] = uint64_t(k.n);
         dim3 grid(1, 1, 1), block(256, 1, 1);
         const int64_t cap = int64_t(d_->sm_count) * 16;
-        if (k.type == KernelSpec::ELW && !k.reds.empty()) {
+        if (k.type == KernelSpec::ROWS) {
+            // one block per row at a time; phase results follow the outputs in the argument block
+            args.assign(ni + k.outs.size() + k.phases.size() + 1, 0);
+            for (size_t i = 0; i < k.ins.size(); i++) args[i] = uint64_t(uintptr_t(buf_ptr(k.ins[i].buf, k.ins[i].offset)));
+            for (size_t i = 0; i < k.outs.size(); i++)
+                args[ni + i] = uint64_t(uintptr_t(buf_ptr(k.outs[i].dst.buf, k.outs[i].dst.offset)));
+            for (size_t i = 0; i < k.phases.size(); i++)
+                args[ni + k.outs.size() + i] = uint64_t(uintptr_t(buf_ptr(k.phases[i].dst.buf, k.phases[i].dst.offset)));
+            args[ni + k.outs.size() + k.phases.size()] = uint64_t(k.p2);
+            grid.x = unsigned(std::max<int64_t>(1, std::min<int64_t>(k.p2, int64_t(d_->sm_count) * 8)));
+        } else if (k.type == KernelSpec::ELW && !k.reds.empty()) {
             // element-wise pass with side sums: 2-d launch over [p2, q2]
             grid.x = unsigned((k.q2 + 32 * k.vec - 1) / (32 * k.vec));
             grid.y = unsigned((k.p2 + k.row_chunk - 1) / k.row_chunk);
@@ -307,6 +317,7 @@ class Executor {
         for (auto& in : k.ins) b += operand_bytes(in);
         for (auto& o : k.outs) b += k.type == KernelSpec::REDUCE ? 4.0 * double(k.n) * double(k.split) : operand_bytes(o.dst);
         for (auto& r : k.reds) b += operand_bytes(r.dst);
+        b += 4.0 * double(k.phases.size()) * double(k.p2);
         return b;
     }
 

@@ -113,6 +113,22 @@ def test_sums_ride_along_with_the_element_wise_pass_over_the_same_memory():
     assert sum(" reduce " in l and "len=2048" in l and "rows=1 " not in l for l in loop.plan.splitlines()) == 0
 
 
+def test_normalisation_layers_lower_to_one_kernel():
+    """mean -> variance -> normalise: consecutive steps over the same rows in which later ones use the per-row results
+    of earlier ones become one `adb_rows_*` kernel (it compiles for sm_100a here)."""
+    dev = _LowerOnly(with_source=True)
+    ad = adb.autodiff
+    ad.set_device(dev)
+    ad.eager_dep_opt()
+    x = np.linspace(-1, 1, 1024 * 512, dtype=np.float32)
+    y = adb.nn.LayerNorm(512).f(ad.tensor(x, [1024, 512])).forward()
+    y.keep()
+    ad.execute()
+    steps = [l for l in dev.plan.splitlines() if l.startswith("#")]
+    assert sum(" rows [1024,512] phases=2" in l for l in steps) == 1 and not any(" reduce " in l for l in steps), steps
+    assert "red0" in dev.plan and "red1" in dev.plan
+
+
 def test_no_fusion_flag_gives_one_kernel_per_command():
     dev = _LowerOnly(flags=adb.devices.FLAG_NO_FUSION)
     ref_programs.ct(dev)
