@@ -55,14 +55,14 @@ def test_two_gpus_match_one_gpu(tmp_path, flags):
 
 
 def test_two_gpus_match_one_gpu_at_the_benchmark_widths(tmp_path):
-    """The benchmark network (4096-8192-8192-4096-1000) at batch 8192: tensor-core dot products on CTA pairs, sums
+    """The benchmark network (4096-8192-8192-4096-1000) at batch 16384: tensor-core dot products on CTA pairs, sums
     fused into the element-wise passes, NCCL all-reduce of 553 MB of gradients per step; two steps, 2 GPUs against 1."""
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     adb = importlib.import_module("autodiff-ir-rust_b200")
-    kw = dict(batch=8192, widths=adb.configs.C4_WIDTHS, steps=2, lr=1e-3)
+    kw = dict(batch=16384, widths=adb.configs.C4_WIDTHS, steps=2, lr=1e-3)   # (a batch equal to a layer width would be ambiguous)
     port = 29700 + (os.getpid() % 2000)
     mp.spawn(_worker, args=(2, port, str(tmp_path), 0, kw), nprocs=2, join=True)
     dev = adb.devices.B200(0)
