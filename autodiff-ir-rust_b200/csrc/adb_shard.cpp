@@ -213,7 +213,8 @@ struct Sharder {
                 const Info& s = a.tag == T_SHARD ? a : b;
                 const Info& o = a.tag == T_SHARD ? b : a;
                 if (o.tag == T_REP) fail("'" + name(c.a) + "' and '" + name(c.b) + "' mix a sharded and a replicated tensor of the same shape");
-                if (o.tag == T_SHARD && o.axis != s.axis) fail("operands are sharded along different axes");
+                if (o.tag == T_SHARD && o.axis != s.axis) fail("operands are sharded along different axes (tensors are recognised as batch tensors by their first dimension: a "
+                                                                 "parameter with as many rows as the batch is mistaken for one -- use a batch size that differs from the layer widths)");
                 set(c.res, T_SHARD, s.axis, s.dims, c);
                 return;
             }
