@@ -4,6 +4,7 @@
     python autodiff-ir-rust_b200/run_case.py c3 --batch 64 --n 1024
     python autodiff-ir-rust_b200/run_case.py dot --m 4096 --n 4096 --k 4096 [--ta] [--tb]
     python autodiff-ir-rust_b200/run_case.py c5 --size 4096 --iters 3
+    python autodiff-ir-rust_b200/run_case.py ln --batch 65536 --n 1024        (layer normalisation of [batch, n])
 
 Small, single-purpose entry point for profilers (ncu -k regex:adb_ ...) and for quick timing of one
 kernel family; bench.py remains the benchmark.
@@ -23,7 +24,7 @@ if ROOT not in sys.path:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["c2", "c3", "c5", "dot"])
+    ap.add_argument("case", choices=["c2", "c3", "c5", "dot", "ln"])
     ap.add_argument("--size", type=int, default=8192)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--n", type=int, default=1024)
@@ -61,6 +62,13 @@ def main():
             x = torch.rand(args.batch * args.n * args.n, device="cuda", generator=g) * 2 - 1
             keep.append(x)
             cfg.c3_reduce_movement(dev, batch=args.batch, n=args.n, inputs={"x": DP(x.data_ptr(), x.numel(), x)}, execute=False)
+        elif args.case == "ln":
+            x = torch.randn(args.batch * args.n, device="cuda", generator=g) * 3 + 1
+            keep.append(x)
+            ad.set_device(dev)
+            ad.eager_dep_opt()
+            y = adb.nn.LayerNorm(args.n).f(ad.tensor(DP(x.data_ptr(), x.numel(), x), [args.batch, args.n])).forward()
+            y.keep()            # (read back with the result; the timing below is the device time of the kernels)
         elif args.case == "c5":
             n = args.size
             a, pa = resident(n * n, n ** -0.5)

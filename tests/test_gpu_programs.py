@@ -407,3 +407,25 @@ def test_max_reduce_every_launch_shape(shape, axis):
     want, got = run_both(prog)
     assert_exact("max", got["max"], want["max"])
     assert_exact("grad", got["grad"], want["grad"])
+
+
+def test_kept_tensor_can_stay_on_the_device():
+    """`adb_get_tensor_device`: address and shape of a kept tensor in HBM (valid until the next execute), for callers
+    that feed the result to other GPU code instead of reading it back."""
+    import torch
+    from cuda.bindings import runtime as cudart
+    n = 3 * 1000
+    x = rnd(n)
+    dev = b200()
+    ad.set_device(dev)
+    ad.eager_dep_opt()
+    y = (ad.tensor(x, [3, 1000]) * 2.0 + 1.0).forward()
+    y.keep()
+    ad.execute()
+    ptr, shape = dev.get_tensor_device(y.id)
+    assert shape == [3, 1000] and ptr
+    out = torch.empty(n, device="cuda")
+    (err,) = cudart.cudaMemcpy(out.data_ptr(), ptr, n * 4, cudart.cudaMemcpyKind.cudaMemcpyDeviceToDevice)
+    assert int(err) == 0
+    np.testing.assert_array_equal(out.cpu().numpy(), x * np.float32(2.0) + np.float32(1.0))
+    assert dev.get_tensor_device("no-such-id") is None
