@@ -5,16 +5,133 @@
 //   hostcheck <flags> <world> <shard_batch> <blob files ...>
 //
 // flags: bit 0 no fusion, bit 1 fold small sums, bit 2 correctly rounded division.
-// Malformed blobs must be rejected with an exception (counted), never crash.
+// Malformed blobs must be rejected with an exception (counted), never crash.  Every plan that does come out is
+// checked against the invariants below (step order, buffer lifetimes, arena placement).
+#include <algorithm>
+#include <climits>
 #include <cstdio>
 #include <cstdlib>
 #include <fstream>
 #include <iterator>
+#include <string>
 #include <vector>
 
 #include "adb_ir.hpp"
 #include "adb_lower.hpp"
 #include "adb_shard.hpp"
+
+// Invariants every plan must satisfy, whatever passes rewrote its step list:
+//   1. step positions increase in execution order (nested blocks lie between their parent and its successor);
+//   2. a buffer is alive at every step that touches it (external and whole-program buffers always are);
+//   3. buffers that are alive at the same time do not overlap in the arena.
+// Returns an empty string or a description of the first violation.
+static void step_buffers(const adb::Plan& plan, const adb::Step& s, std::vector<int>& bufs) {
+    using adb::Step;
+    bufs.clear();
+    switch (s.kind) {
+    case Step::ELW: case Step::REDUCE: {
+        const adb::KernelSpec& k = plan.kernels[size_t(s.kernel)];
+        for (auto& in : k.ins) bufs.push_back(in.buf);
+        for (auto& o : k.outs) bufs.push_back(o.dst.buf);
+        for (auto& r : k.reds) bufs.push_back(r.dst.buf);
+        for (auto& ph : k.phases) bufs.push_back(ph.dst.buf);
+        break;
+    }
+    case Step::GEMM: bufs = {s.gemm.a, s.gemm.b, s.gemm.c}; break;
+    case Step::UPLOAD: case Step::ALLREDUCE: bufs = {s.buf}; break;
+    case Step::WHILE: bufs = {s.cond_buf}; break;
+    case Step::IF: for (auto& br : s.branches) bufs.push_back(br.cond_buf); break;
+    default: break;
+    }
+}
+
+static std::string check_block(const adb::Plan& plan, const adb::StepBlock& blk, int& last_pos) {
+    std::vector<int> bufs;
+    for (auto& s : blk.steps) {
+        if (s.pos <= last_pos) return "step position " + std::to_string(s.pos) + " does not follow " + std::to_string(last_pos);
+        last_pos = s.pos;
+        if ((s.kind == adb::Step::ELW || s.kind == adb::Step::REDUCE) && plan.kernels[size_t(s.kernel)].dead)
+            return "step at " + std::to_string(s.pos) + " runs a kernel that was marked dead";
+        step_buffers(plan, s, bufs);
+        for (int b : bufs) {
+            if (b < 0 || size_t(b) >= plan.bufs.size()) return "step at " + std::to_string(s.pos) + " names buffer " + std::to_string(b);
+            const adb::BufferInfo& bi = plan.bufs[size_t(b)];
+            if (bi.external || bi.persistent) continue;
+            if (!(bi.first <= s.pos && s.pos <= bi.last))
+                return "buffer '" + bi.name + "' [" + std::to_string(bi.first) + "," + std::to_string(bi.last) + "] is touched at " + std::to_string(s.pos);
+            if (bi.arena_off < 0 && bi.numel > 0) return "buffer '" + bi.name + "' has no place in the arena";
+        }
+        std::string e;
+        if (s.body && !(e = check_block(plan, *s.body, last_pos)).empty()) return e;
+        for (auto& br : s.branches)
+            if (!(e = check_block(plan, *br.body, last_pos)).empty()) return e;
+        if (s.else_body && !(e = check_block(plan, *s.else_body, last_pos)).empty()) return e;
+    }
+    return "";
+}
+
+// every buffer touched in `blk` (nested blocks included) and the position range of the block
+static void collect(const adb::Plan& plan, const adb::StepBlock& blk, std::vector<int>& touched, int& lo, int& hi) {
+    std::vector<int> bufs;
+    for (auto& s : blk.steps) {
+        lo = std::min(lo, s.pos);
+        hi = std::max(hi, s.pos);
+        step_buffers(plan, s, bufs);
+        touched.insert(touched.end(), bufs.begin(), bufs.end());
+        if (s.body) collect(plan, *s.body, touched, lo, hi);
+        for (auto& br : s.branches) collect(plan, *br.body, touched, lo, hi);
+        if (s.else_body) collect(plan, *s.else_body, touched, lo, hi);
+    }
+}
+
+//   4. a buffer that a loop body shares with code outside the loop stays alive for the whole loop
+static std::string check_loops(const adb::Plan& plan, const adb::StepBlock& blk) {
+    for (auto& s : blk.steps) {
+        std::string e;
+        if (s.kind == adb::Step::WHILE && s.body) {
+            std::vector<int> touched;
+            int lo = INT_MAX, hi = -1;
+            collect(plan, *s.body, touched, lo, hi);
+            for (int b : touched) {
+                const adb::BufferInfo& bi = plan.bufs[size_t(b)];
+                if (bi.external || bi.persistent || hi < 0) continue;
+                const bool outside = bi.first < lo || bi.last > hi;
+                if (outside && !(bi.first <= lo && bi.last >= hi))
+                    return "buffer '" + bi.name + "' [" + std::to_string(bi.first) + "," + std::to_string(bi.last) +
+                           "] is shared with a loop spanning [" + std::to_string(lo) + "," + std::to_string(hi) + "] but dies inside it";
+            }
+            if (!(e = check_loops(plan, *s.body)).empty()) return e;
+        }
+        for (auto& br : s.branches)
+            if (!(e = check_loops(plan, *br.body)).empty()) return e;
+        if (s.else_body && !(e = check_loops(plan, *s.else_body)).empty()) return e;
+    }
+    return "";
+}
+
+static std::string check_plan(const adb::Plan& plan) {
+    int last = -1;
+    std::string e = check_block(plan, plan.main, last);
+    if (!e.empty()) return e;
+    if (!(e = check_loops(plan, plan.main)).empty()) return e;
+    struct Live { int64_t lo, hi; long long first, last; const adb::BufferInfo* b; };
+    std::vector<Live> live;
+    for (auto& b : plan.bufs) {
+        if (b.external || b.numel <= 0 || (!b.persistent && b.last < 0)) continue;
+        if (b.arena_off < 0) return "buffer '" + b.name + "' is used but not placed";
+        if (b.arena_off % 256) return "buffer '" + b.name + "' is not 256-byte aligned";
+        if (b.arena_off + b.numel * 4 > plan.arena_bytes) return "buffer '" + b.name + "' ends beyond the arena";
+        live.push_back({b.arena_off, b.arena_off + b.numel * 4, b.persistent ? LLONG_MIN : (long long)b.first,
+                        b.persistent ? LLONG_MAX : (long long)b.last, &b});
+    }
+    for (size_t i = 0; i < live.size(); i++)
+        for (size_t j = i + 1; j < live.size(); j++) {
+            const bool time = !(live[i].last < live[j].first || live[j].last < live[i].first);
+            const bool space = live[i].lo < live[j].hi && live[j].lo < live[i].hi;
+            if (time && space) return "buffers '" + live[i].b->name + "' and '" + live[j].b->name + "' are alive together and overlap in the arena";
+        }
+    return "";
+}
 
 int main(int argc, char** argv) {
     if (argc < 5) return 2;
@@ -44,6 +161,12 @@ int main(int argc, char** argv) {
                 }
                 std::string listing = adb::dump_plan(plan, true);
                 if (listing.empty()) return 3;
+                std::string bad = check_plan(plan);
+                if (!bad.empty()) {
+                    std::fprintf(stderr, "plan invariant violated in %s (rank %d): %s\n%s\n", argv[f], rank, bad.c_str(),
+                                 adb::dump_plan(plan, false).c_str());
+                    return 4;
+                }
             } catch (const std::exception& e) {
                 rejected++;
             }
