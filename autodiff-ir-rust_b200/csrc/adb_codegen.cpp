@@ -146,12 +146,17 @@ void emit_ssa(std::ostringstream& o, const KernelSpec& k, int vec, const std::ve
 
 void emit_loads(std::ostringstream& o, const KernelSpec& k, int vec, const std::vector<Access>& acc,
                 const std::vector<std::string>& off, std::vector<std::string>& names, const char* ind,
-                const std::vector<char>* need = nullptr) {
+                const std::vector<char>* need = nullptr, const std::vector<char>* cached = nullptr) {
     names.resize(k.ins.size());
     for (size_t i = 0; i < k.ins.size(); i++) {
         std::string nm = "l" + std::to_string(i);
         names[i] = nm;
         if (need && !(*need)[i]) continue;
+        if (cached && (*cached)[i]) {
+            // the value was loaded into registers at the start of the row (ROWS kernels, loop index t)
+            o << ind << "const " << (vec == 4 ? "float4 " : "float ") << nm << " = c" << i << "[t];\n";
+            continue;
+        }
         std::string p = "a.in[" + std::to_string(i) + "]";
         if (vec == 1 || acc[i].mode == Access::SCALAR)
             o << ind << "const float " << nm << " = " << p << "[" << off[i] << "];\n";
@@ -365,11 +370,13 @@ void gen_elw_red(KernelSpec& k) {
     finish(k, o.str(), "adb_elwsum");
 }
 
-// Row reductions and the element-wise work that depends on them in one kernel: one block walks one row of the
-// [P, Q] space at a time.  Phase k loops over the row, reduces its value across the block (warp shuffles, then
+// Row reductions and the element-wise work that depends on them in one kernel: one block (rows longer than 2048
+// elements) or one warp (shorter rows) walks one row of the [P, Q] space at a time.  Phase k loops over the row, reduces its value across the block (warp shuffles, then
 // eight partials in shared memory combined in a fixed order) and leaves the result in a register every thread
 // holds; later phases and the final store loop read the row again (it was just read by the same block, so it comes
 // from L1 / L2, not from HBM) and use those registers.
+int64_t footprint(const Operand& o);
+
 void gen_rows(KernelSpec& k) {
     std::vector<const Operand*> ops;
     for (auto& i : k.ins) ops.push_back(&i);
@@ -384,7 +391,11 @@ void gen_rows(KernelSpec& k) {
     for (auto& o : k.outs)
         if (!lanes_ok(o.dst.subs) || o.dst.subs.empty() || o.dst.subs.back().stride == 0) vec = 1;
     k.vec = vec;
-    k.threads = 256;
+    // threads per row: a warp for short rows (eight rows per block, shuffles only, eight times as many bytes in
+    // flight per SM), the whole block for long ones
+    const int TPR = Q <= 2048 ? 32 : 256;
+    const int RPB = 256 / TPR;
+    k.threads = TPR;
     std::vector<Access> in_acc(k.ins.size()), out_acc(k.outs.size());
     for (size_t i = 0; i < k.ins.size(); i++) in_acc[i] = classify(k.ins[i].subs, k.ins[i].offset, vec, false);
     for (size_t i = 0; i < k.outs.size(); i++) out_acc[i] = classify(k.outs[i].dst.subs, k.outs[i].dst.offset, vec, true);
@@ -404,16 +415,62 @@ void gen_rows(KernelSpec& k) {
         }
     };
 
+    // Operands that cover the whole [P, Q] space are read by every phase; when a thread's share of a row is small
+    // they are loaded into registers once per row (fully unrolled loops) instead of coming back from L1 / L2.
+    const int64_t NIT = (Q + int64_t(TPR) * vec - 1) / (int64_t(TPR) * vec);   // loop trips per row and thread
+    std::vector<char> cached(k.ins.size(), 0);
+    {
+        int64_t n_full = 0;
+        for (size_t i = 0; i < k.ins.size(); i++)
+            if ((in_acc[i].mode == Access::VEC4 || (vec == 1 && !k.ins[i].subs.empty() && k.ins[i].subs.back().stride == 1)) &&
+                footprint(k.ins[i]) == P * Q)
+                n_full++;
+        if (n_full > 0 && NIT * vec * n_full <= 64 && NIT <= 16)
+            for (size_t i = 0; i < k.ins.size(); i++)
+                cached[i] = (in_acc[i].mode == Access::VEC4 || (vec == 1 && !k.ins[i].subs.empty() && k.ins[i].subs.back().stride == 1)) &&
+                            footprint(k.ins[i]) == P * Q;
+    }
+    bool any_cached = false;
+    for (char c : cached) any_cached = any_cached || c;
+
     std::ostringstream o;
     o << helpers() << "struct Args { const float* in[" << std::max<size_t>(1, k.ins.size()) << "]; float* out["
       << k.outs.size() + k.phases.size() << "]; long long n; };\n";
     o << "extern \"C\" __global__ void __launch_bounds__(256) @ENTRY@(const __grid_constant__ Args a) {\n";
-    o << "  __shared__ float sm[8];\n";
+    if (TPR == 256) o << "  __shared__ float sm[8];\n";
     o << "  const unsigned int lane = threadIdx.x & 31u, wrp = threadIdx.x >> 5;\n";
-    o << "  for (" << idx_t << " p = blockIdx.x; p < " << P << "; p += gridDim.x) {\n";
+    if (TPR == 256)
+        o << "  for (" << idx_t << " p = blockIdx.x; p < " << P << "; p += gridDim.x) {\n";
+    else
+        o << "  for (" << idx_t << " p = (" << idx_t << ")blockIdx.x * " << RPB << "u + wrp; p < " << P << "; p += ("
+          << idx_t << ")gridDim.x * " << RPB << "u) {\n";
+    if (any_cached) {
+        for (size_t i = 0; i < k.ins.size(); i++)
+            if (cached[i]) o << "    " << (vec == 4 ? "float4" : "float") << " c" << i << "[" << NIT << "];\n";
+        o << "#pragma unroll\n    for (int t = 0; t < " << NIT << "; t++) {\n";
+        o << "      const " << idx_t << " q = (" << (TPR == 256 ? "threadIdx.x" : "lane") << " + (unsigned int)t * " << TPR << "u) * " << vec << "u;\n";
+        o << "      if (q >= " << Q << ") continue;\n";
+        o << "      const " << idx_t << " i = p * " << Q << " + q;\n";
+        for (size_t i = 0; i < k.ins.size(); i++) {
+            if (!cached[i]) continue;
+            std::ostringstream pre;
+            std::string e = offset_expr(k.ins[i].subs, "i", pre, "c" + std::to_string(i), idx_t);
+            o << pre.str();
+            if (vec == 4) o << "      c" << i << "[t] = *reinterpret_cast<const float4*>(a.in[" << i << "] + (" << e << "));\n";
+            else o << "      c" << i << "[t] = a.in[" << i << "][" << e << "];\n";
+        }
+        o << "    }\n";
+    }
     auto body_prefix = [&](const std::vector<char>& need_in, std::vector<std::string>& in_off, std::vector<std::string>& out_off,
                            bool with_outs) {
-        o << "    for (" << idx_t << " q = threadIdx.x * " << vec << "u; q < " << Q << "; q += " << 256 * vec << "u) {\n";
+        if (any_cached) {
+            o << "#pragma unroll\n    for (int t = 0; t < " << NIT << "; t++) {\n";
+            o << "      const " << idx_t << " q = (" << (TPR == 256 ? "threadIdx.x" : "lane") << " + (unsigned int)t * " << TPR << "u) * " << vec << "u;\n";
+            o << "      if (q >= " << Q << ") continue;\n";
+        } else {
+            o << "    for (" << idx_t << " q = " << (TPR == 256 ? "threadIdx.x" : "lane") << " * " << vec << "u; q < " << Q << "; q += "
+              << TPR * vec << "u) {\n";
+        }
         o << "      const " << idx_t << " i = p * " << Q << " + q;\n";
         std::vector<std::pair<std::vector<Sub>, std::string>> seen;
         auto offset_of = [&](const std::vector<Sub>& subs) {
@@ -430,7 +487,7 @@ void gen_rows(KernelSpec& k) {
         };
         in_off.assign(k.ins.size(), "0");
         for (size_t i = 0; i < k.ins.size(); i++)
-            if (need_in[i]) in_off[i] = offset_of(k.ins[i].subs);
+            if (need_in[i] && !cached[i]) in_off[i] = offset_of(k.ins[i].subs);
         out_off.assign(k.outs.size(), "0");
         if (with_outs)
             for (size_t i = 0; i < k.outs.size(); i++) out_off[i] = offset_of(k.outs[i].dst.subs);
@@ -447,7 +504,7 @@ void gen_rows(KernelSpec& k) {
         for (int l = 0; l < vec; l++) o << "    float acc" << l << " = " << ident << ";\n";
         std::vector<std::string> in_off, out_off, names;
         body_prefix(need_in, in_off, out_off, false);
-        emit_loads(o, k, vec, in_acc, in_off, names, "      ", &need_in);
+        emit_loads(o, k, vec, in_acc, in_off, names, "      ", &need_in, &cached);
         emit_ssa(o, k, vec, names, in_acc, "      ", &need);
         for (int l = 0; l < vec; l++)
             o << "      acc" << l << " = " << comb("acc" + std::to_string(l), "v" + std::to_string(phs.ssa) + "_" + std::to_string(l)) << ";\n";
@@ -455,13 +512,15 @@ void gen_rows(KernelSpec& k) {
         if (vec == 4) o << "    float s = " << comb(comb("acc0", "acc1"), comb("acc2", "acc3")) << ";\n";
         else o << "    float s = acc0;\n";
         o << "    for (int m = 16; m > 0; m >>= 1) s = " << comb("s", "__shfl_xor_sync(0xffffffffu, s, m)") << ";\n";
-        o << "    __syncthreads();\n";   // the previous phase's readers of sm are done
-        o << "    if (lane == 0u) sm[wrp] = s;\n";
-        o << "    __syncthreads();\n";
-        o << "    s = sm[0];\n";
-        o << "    for (int w = 1; w < 8; w++) s = " << comb("s", "sm[w]") << ";\n";
+        if (TPR == 256) {
+            o << "    __syncthreads();\n";   // the previous phase's readers of sm are done
+            o << "    if (lane == 0u) sm[wrp] = s;\n";
+            o << "    __syncthreads();\n";
+            o << "    s = sm[0];\n";
+            o << "    for (int w = 1; w < 8; w++) s = " << comb("s", "sm[w]") << ";\n";
+        }
         o << "    red" << ph << " = s;\n";
-        o << "    if (threadIdx.x == 0u) a.out[" << k.outs.size() + ph << "][p] = s;\n";
+        o << "    if (" << (TPR == 256 ? "threadIdx.x" : "lane") << " == 0u) a.out[" << k.outs.size() + ph << "][p] = s;\n";
         o << "    }\n";
     }
     if (!k.outs.empty()) {
@@ -471,7 +530,7 @@ void gen_rows(KernelSpec& k) {
         slice(roots, need, need_in);
         std::vector<std::string> in_off, out_off, names;
         body_prefix(need_in, in_off, out_off, true);
-        emit_loads(o, k, vec, in_acc, in_off, names, "      ", &need_in);
+        emit_loads(o, k, vec, in_acc, in_off, names, "      ", &need_in, &cached);
         emit_ssa(o, k, vec, names, in_acc, "      ", &need);
         for (size_t i = 0; i < k.outs.size(); i++) {
             std::string pp = "a.out[" + std::to_string(i) + "]";

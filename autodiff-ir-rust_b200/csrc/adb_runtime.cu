@@ -284,7 +284,8 @@ class Executor {
             for (size_t i = 0; i < k.phases.size(); i++)
                 args[ni + k.outs.size() + i] = uint64_t(uintptr_t(buf_ptr(k.phases[i].dst.buf, k.phases[i].dst.offset)));
             args[ni + k.outs.size() + k.phases.size()] = uint64_t(k.p2);
-            grid.x = unsigned(std::max<int64_t>(1, std::min<int64_t>(k.p2, int64_t(d_->sm_count) * 8)));
+            const int64_t rows_per_block = 256 / std::max(1, k.threads);   // one warp or one block per row
+            grid.x = unsigned(std::max<int64_t>(1, std::min<int64_t>((k.p2 + rows_per_block - 1) / rows_per_block, int64_t(d_->sm_count) * 8)));
         } else if (k.type == KernelSpec::ELW && !k.reds.empty()) {
             // element-wise pass with side sums: 2-d launch over [p2, q2]
             grid.x = unsigned((k.q2 + 32 * k.vec - 1) / (32 * k.vec));
