@@ -13,6 +13,7 @@
 
 #include <cuda.h>
 
+#include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -866,7 +867,8 @@ int gemm_launch(GemmContext& ctx, const GemmArgs& a, cudaStream_t stream, std::s
                 const long long tiles = (long long)p.tiles_m * p.tiles_n;
                 if (!plan_k_split(p, tiles, ctx.pair_clusters, a, stream, err)) return -1;
                 long long clusters = tiles * p.k_splits;
-                if (clusters > ctx.pair_clusters) clusters = ctx.pair_clusters;
+                const int usable = std::max(1, ctx.pair_clusters - (a.reserve_sms + 1) / 2);
+                if (clusters > usable) clusters = usable;
                 const int grid = int(2 * clusters);
                 using namespace pair;
                 if (A_MN && B_MN) adb_dot_tc_pair<true, true><<<grid, NUM_THREADS, PSMEM_BYTES, stream>>>(ma, mb, p);
@@ -881,7 +883,8 @@ int gemm_launch(GemmContext& ctx, const GemmArgs& a, cudaStream_t stream, std::s
             }
             if (!plan_k_split(p, (long long)p.tiles_m * p.tiles_n, ctx.sm_count, a, stream, err)) return -1;
             long long units = (long long)p.tiles_m * p.tiles_n * p.k_splits;
-            const int grid = int(units > ctx.sm_count ? ctx.sm_count : units);
+            const int usable_sms = std::max(1, ctx.sm_count - a.reserve_sms);
+            const int grid = int(units > usable_sms ? usable_sms : units);
             if (A_MN && B_MN) adb_dot_tc<true, true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, p);
             else if (A_MN) adb_dot_tc<true, false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, p);
             else if (B_MN) adb_dot_tc<false, true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, p);

@@ -16,6 +16,7 @@ struct GemmArgs {
     int64_t a_rs = 0, a_cs = 0, b_rs = 0, b_cs = 0;  // element strides of A[m,k] and B[k,n]
     bool force_simt = false;
     bool no_pair = false;  // keep the tensor-core kernel on one SM per tile
+    int reserve_sms = 0;   // leave this many SMs to a kernel running beside the product (a collective on another stream)
 };
 
 struct GemmContext {

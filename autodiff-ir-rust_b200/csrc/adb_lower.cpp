@@ -1247,6 +1247,52 @@ class Lowerer {
         pos_ *= POS_SCALE;
         fuse_rows(plan_.main);
         fuse_block(plan_.main);
+        if (opt_.world > 1) hoist_collectives(plan_.main);
+    }
+
+    // ------------------------------------------------------------------ collectives next to their producers
+    // The frontend's optimiser step comes after the whole backward pass, so every gradient all-reduce (and the small
+    // kernel that scales its operand) sits at the end of the step, behind the last dot product.  Each such pair is
+    // moved up to right behind the step that produces the gradient: a runtime that issues collectives on their own
+    // stream can then overlap them with the remaining dot products.  On a single stream the order is immaterial.
+    void hoist_collectives(StepBlock& blk) {
+        for (auto& s : blk.steps) {
+            if (s.body) hoist_collectives(*s.body);
+            for (auto& br : s.branches) hoist_collectives(*br.body);
+            if (s.else_body) hoist_collectives(*s.else_body);
+        }
+        auto& steps = blk.steps;
+        std::vector<int> rd, wr, prd, pwr;
+        for (size_t j = 1; j < steps.size(); j++) {
+            if (steps[j].kind != Step::ALLREDUCE || steps[j - 1].kind != Step::ELW) continue;
+            const KernelSpec& pk = plan_.kernels[size_t(steps[j - 1].kernel)];
+            if (pk.type != KernelSpec::ELW || pk.outs.size() != 1 || !pk.reds.empty() || pk.outs[0].dst.buf != steps[j].buf) continue;
+            step_rw(steps[j - 1], prd, pwr);   // the pair reads prd, writes pwr (the all-reduce works in place on pwr)
+            // how far up can the pair go?
+            size_t i = j - 1;                  // the pair ends up right behind steps[i - 1]
+            while (i > 0) {
+                const Step& q = steps[i - 1];
+                if (is_barrier(q)) break;
+                step_rw(q, rd, wr);
+                if (hits(wr, prd) || hits(wr, pwr) || hits(rd, pwr)) break;
+                i--;
+            }
+            if (i + 1 >= j) continue;          // nowhere to go (also: i == j - 1 means "stay")
+            // positions right behind steps[i - 1] (or in front of steps[i] at the head of the block)
+            const int base = i > 0 ? steps[i - 1].pos : steps[i].pos - POS_SCALE;
+            int next_pos = base + 1;
+            size_t ins_at = i;
+            while (ins_at < steps.size() && steps[ins_at].pos < base + POS_SCALE && ins_at < j - 1) { next_pos = steps[ins_at].pos + 1; ins_at++; }
+            if (ins_at >= j - 1 || next_pos + 2 >= base + POS_SCALE - 1 || (ins_at < steps.size() && next_pos + 1 >= steps[ins_at].pos)) continue;
+            Step a = std::move(steps[j - 1]), b = std::move(steps[j]);
+            steps.erase(steps.begin() + long(j - 1), steps.begin() + long(j + 1));
+            a.pos = next_pos;
+            b.pos = next_pos + 1;
+            for (int x : prd) touch(x, a.pos);
+            for (int x : pwr) { touch(x, a.pos); touch(x, b.pos); }
+            steps.insert(steps.begin() + long(ins_at), std::move(b));
+            steps.insert(steps.begin() + long(ins_at), std::move(a));
+        }
     }
 
     // ------------------------------------------------------------------ row reductions chained with their consumers

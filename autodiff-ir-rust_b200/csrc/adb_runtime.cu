@@ -110,6 +110,7 @@ struct StepSched {
     bool on_comm = false;
     int wait_main = -1;   // (comm step) index of the last earlier main-stream step touching one of its buffers
     int wait_comm = -1;   // (main step) index of the last earlier comm-stream step touching one of its buffers
+    bool beside_comm = false;  // (main step) a collective launched earlier in the range may still be running
     bool record_after = false;
     cudaEvent_t done = nullptr;
 };
@@ -353,6 +354,7 @@ class Executor {
             a.a_rs = g.a_rs; a.a_cs = g.a_cs; a.b_rs = g.b_rs; a.b_cs = g.b_cs;
             a.force_simt = (d_->flags & ADB_FLAG_SIMT_DOT) != 0;
             a.no_pair = (d_->flags & ADB_FLAG_SINGLE_SM_DOT) != 0;
+            a.reserve_sms = gemm_reserve_;
             std::string e;
             const unsigned long long tc0 = d_->gemm.tc_total;
             int n = gemm_launch(d_->gemm, a, cur_stream_, e);
@@ -524,6 +526,20 @@ class Executor {
                 if (sc.wait_main >= 0) rs.steps[size_t(sc.wait_main)].record_after = true;
             }
         }
+        // which compute-stream steps run while a collective may still be in flight (the communication stream
+        // completes in order: once the compute stream has waited for comm step k, all comm steps <= k are done)
+        {
+            int latest_comm = -1, waited = -1;
+            for (size_t t = 0; t < rs.steps.size(); t++) {
+                StepSched& sc = rs.steps[t];
+                if (sc.on_comm) {
+                    if (blk.steps[begin + t].kind == Step::ALLREDUCE) latest_comm = int(t);
+                } else {
+                    waited = std::max(waited, sc.wait_comm);
+                    sc.beside_comm = latest_comm > waited;
+                }
+            }
+        }
         for (auto& sc : rs.steps)
             if (sc.on_comm || sc.record_after) ck(cudaEventCreateWithFlags(&sc.done, cudaEventDisableTiming), "event create");
         if (rs.any_comm) ck(cudaEventCreateWithFlags(&rs.fork, cudaEventDisableTiming), "event create");
@@ -552,7 +568,11 @@ class Executor {
                 last_comm = int(t - begin);
             } else {
                 if (sc.wait_comm >= 0) ck(cudaStreamWaitEvent(d_->stream, rs.steps[size_t(sc.wait_comm)].done, 0), "main waits");
+                // a dot product that runs beside a collective leaves it a few SMs: its persistent CTAs would
+                // otherwise hold every SM until they finish and the collective could not start
+                gemm_reserve_ = sc.beside_comm ? COMM_SMS : 0;
                 run_step(blk.steps[t]);
+                gemm_reserve_ = 0;
                 if (sc.record_after) ck(cudaEventRecord(sc.done, d_->stream), "event");
             }
         }
@@ -706,6 +726,8 @@ class Executor {
         used_events_.clear();
     }
 
+    static constexpr int COMM_SMS = 8;   // SMs left to NCCL while a collective overlaps dot products
+    int gemm_reserve_ = 0;
     uint64_t launches_ = 0, gemms_ = 0, tc_ = 0;
     bool capturing_ = false;
     int loop_depth_ = 0;
@@ -1022,6 +1044,8 @@ adb_status adb_create(const adb_config* cfg, adb_device** out) {
             ncclUniqueId uid;
             static_assert(sizeof(uid) == 128, "ncclUniqueId is 128 bytes");
             std::memcpy(&uid, cfg->nccl_unique_id, 128);
+            // collectives that overlap dot products get 8 SMs (Executor::COMM_SMS): keep NCCL's kernels that small
+            if (d->flags & ADB_FLAG_COMM_STREAM) setenv("NCCL_MAX_CTAS", "8", 0);
             if (g_nccl.CommInitRank(&d->nccl_comm, d->world, uid, d->rank) != ncclSuccess) return ADB_ERR_NCCL;
         }
     } catch (CudaFail& f) {

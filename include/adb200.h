@@ -80,9 +80,9 @@ typedef struct adb_config {
 #define ADB_FLAG_PROFILE 8u           /* CUDA events around every kernel (fills the per-kind times of adb_stats);
                                          loop bodies are then launched kernel by kernel, not as graphs */
 #define ADB_FLAG_COMM_STREAM 16u      /* issue collectives on a second, high-priority stream (ordered by events on the
-                                         memory they touch) instead of the compute stream; off by default: the persistent
-                                         dot-product kernel holds every SM, so the collective only starts when it ends and
-                                         then delays the next one (measured 2 % slower on 2 GPUs) */
+                                         memory they touch) beside the remaining dot products, which then leave 8 SMs
+                                         free; off by default: measured 1.5-3 % slower on 2 and on 8 GPUs (the dot
+                                         products lose more than the all-reduce time that is hidden) */
 #define ADB_FLAG_SINGLE_SM_DOT 32u    /* keep the tcgen05 dot kernel on one SM per 128 x 256 tile instead of pairing two
                                          SMs (cta_group::2) on a 256 x 256 tile */
 #define ADB_FLAG_EXACT_DIV 64u        /* Recip and Sqrt correctly rounded (bit-identical to IEEE 1.0f/x and sqrtf) instead
