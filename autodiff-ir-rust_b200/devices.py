@@ -231,6 +231,20 @@ class B200:
             return None
         return ctypes.cast(data, ctypes.c_void_p).value, [int(dims[i]) for i in range(nd.value)]
 
+    def save_tensors(self, path: str, ids) -> list:
+        """Checkpoint helper: writes the kept tensors named in `ids` (Tensor / Value objects or id strings) of the last
+        execute to one `.npz` file, keyed by id, and returns the ids written.  The reference has no checkpointing;
+        weights are only reachable through `keep()` + `get()` (src/core/value.rs:97-99), which is what this wraps."""
+        out = {}
+        for t in ids:
+            id_ = t if isinstance(t, str) else (t.val().id if hasattr(t, "val") and not hasattr(t, "get") else t.id)
+            v = self.get_tensor(id_)
+            if v.is_none:
+                raise KeyError(f"'{id_}' was not kept by the last execute")
+            out[id_] = np.asarray(v.data, np.float32).reshape(v.dim)
+        np.savez(path, **out)
+        return list(out)
+
     def stats(self) -> dict:
         s = AdbStats()
         self._L.adb_get_stats(self._h, ctypes.byref(s))

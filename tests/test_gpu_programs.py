@@ -429,3 +429,32 @@ def test_kept_tensor_can_stay_on_the_device():
     assert int(err) == 0
     np.testing.assert_array_equal(out.cpu().numpy(), x * np.float32(2.0) + np.float32(1.0))
     assert dev.get_tensor_device("no-such-id") is None
+
+
+def test_checkpoint_of_kept_tensors_round_trips(tmp_path):
+    """`B200.save_tensors`: kept tensors of the last execute into one .npz; loading them as payloads resumes the run."""
+    w0 = rnd(64 * 32)
+    x = rnd(16 * 64)
+
+    def step(dev, w_init):
+        ad.set_device(dev)
+        ad.eager_dep_opt()
+        w = ad.tensor(w_init, [64, 32])
+        y = ad.dot(ad.tensor(x, [16, 64]), w)
+        loss = nn.mse_loss(y, ad.tensor(np.zeros(16 * 32, np.float32), [16, 32]))
+        loss.forward()
+        loss.backward()
+        nn.SGD([w], 0.1).step()
+        w.val().keep()
+        ad.execute()
+        return w
+    dev = b200()
+    w = step(dev, w0)
+    path = str(tmp_path / "ckpt.npz")
+    assert dev.save_tensors(path, [w]) == [w.val().id]
+    saved = np.load(path)[w.val().id]
+    np.testing.assert_array_equal(saved.reshape(-1), w.val().get().data)
+    # two steps in a row == one step, checkpoint, one step from the checkpoint
+    w2 = step(dev, saved.reshape(-1).copy())
+    ref = step(oracle(), np.asarray(step(oracle(), w0).val().get().data, np.float32))
+    assert_rel("w after resume", w2.val().get(), ref.val().get(), 1e-5)
