@@ -15,6 +15,7 @@
 #include <chrono>
 #include <cstdarg>
 #include <cstdio>
+#include <cstddef>
 #include <cstring>
 #include <map>
 #include <memory>
@@ -143,6 +144,7 @@ struct adb_device {
     int rank = 0, world = 1;
     uint32_t flags = 0;
     uint64_t shard_batch = 0;
+    std::vector<std::string> shard_ids;  // optional: the CreateMat ids that hold the batch
     int sm_count = 148;
     cudaStream_t stream = nullptr;
     cudaStream_t copy_stream = nullptr;  // host->device prefetch of in-loop payloads
@@ -802,7 +804,7 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
     Program prog = parse_program(blob, nbytes);
     d->stats = adb_stats{};
     d->stats.ir_commands = prog.n_cmds;
-    if (d->world > 1 && d->shard_batch) shard_program(prog, d->rank, d->world, int64_t(d->shard_batch));
+    if (d->world > 1 && d->shard_batch) shard_program(prog, d->rank, d->world, int64_t(d->shard_batch), &d->shard_ids);
     std::vector<uint8_t> structure;
     uint64_t key = structure_key(prog, d->flags, d->rank, d->world, d->shard_batch, structure);
 
@@ -1000,6 +1002,16 @@ extern "C" {
 
 const char* adb_version(void) { return "adb200 0.1 (sm_100a)"; }
 
+// the optional tail of adb_config (older callers pass a shorter struct)
+static std::vector<std::string> config_shard_ids(const adb_config* cfg) {
+    std::vector<std::string> ids;
+    if (!cfg || cfg->struct_size < offsetof(adb_config, n_shard_ids) + sizeof(uint32_t)) return ids;
+    if (!cfg->shard_ids) return ids;
+    for (uint32_t i = 0; i < cfg->n_shard_ids; i++)
+        if (cfg->shard_ids[i]) ids.emplace_back(cfg->shard_ids[i]);
+    return ids;
+}
+
 adb_status adb_create(const adb_config* cfg, adb_device** out) {
     if (!out) return ADB_ERR_INVALID;
     *out = nullptr;
@@ -1016,6 +1028,7 @@ adb_status adb_create(const adb_config* cfg, adb_device** out) {
         d->world = cfg->world_size > 0 ? cfg->world_size : 1;
         d->flags = cfg->flags;
         d->shard_batch = cfg->shard_batch;
+        d->shard_ids = config_shard_ids(cfg);
     }
     if (d->ordinal < 0 || d->ordinal >= count) return ADB_ERR_INVALID;
     try {
@@ -1174,7 +1187,8 @@ adb_status adb_lower_check(const uint8_t* blob, size_t nbytes, const adb_config*
             opt.fuse_small_sums = (cfg->flags & ADB_FLAG_FUSE_SMALL_SUMS) != 0;
             opt.rank = cfg->rank;
             opt.world = cfg->world_size > 0 ? cfg->world_size : 1;
-            if (opt.world > 1 && cfg->shard_batch) shard_program(prog, opt.rank, opt.world, int64_t(cfg->shard_batch));
+            std::vector<std::string> ids = config_shard_ids(cfg);
+            if (opt.world > 1 && cfg->shard_batch) shard_program(prog, opt.rank, opt.world, int64_t(cfg->shard_batch), &ids);
         }
         Plan plan;
         lower_program(prog, plan, opt);
@@ -1204,11 +1218,13 @@ adb_status adb_lower_check(const uint8_t* blob, size_t nbytes, const adb_config*
     }
 }
 
-adb_status adb_shard_ir(const uint8_t* blob, size_t nbytes, int32_t rank, int32_t world_size, uint64_t shard_batch,
-                        uint8_t* out, size_t cap, size_t* needed, char* err, size_t err_cap) {
+adb_status adb_shard_ir(const uint8_t* blob, size_t nbytes, const adb_config* cfg, uint8_t* out, size_t cap, size_t* needed,
+                        char* err, size_t err_cap) {
     try {
+        if (!cfg) throw IrError("data-parallel rewrite: no configuration");
         Program prog = parse_program(blob, nbytes);
-        shard_program(prog, rank, world_size, int64_t(shard_batch));
+        std::vector<std::string> ids = config_shard_ids(cfg);
+        shard_program(prog, cfg->rank, cfg->world_size, int64_t(cfg->shard_batch), &ids);
         std::vector<uint8_t> bytes = serialize_program(prog);
         if (needed) *needed = bytes.size();
         if (out && cap >= bytes.size()) std::memcpy(out, bytes.data(), bytes.size());

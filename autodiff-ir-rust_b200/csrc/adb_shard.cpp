@@ -11,9 +11,18 @@
 // Linear ops keep PART (scaling by a constant, adding two partial sums, Sum); everything else forces an
 // AllReduce of the partial operand first.  That puts the collective where the SGD update consumes the
 // gradient: `p += -1 * (lr * grad)` all-reduces the scaled gradient right before the in-place add.
+//
+// Which CreateMat tensors hold the batch is either given (their ids) or guessed from the first dimension.  Constants
+// and broadcasts carry no such information: a CreateConstant with a dimension equal to the batch, or a broadcast to
+// that many entries, is first assumed to be batch-shaped and the assumption is checked where the value meets a
+// tensor whose distribution is known.  When it does not fit (a constant shaped like a parameter whose width happens
+// to equal the batch), the decision is recorded and the rewrite starts over with it; the program that is finally
+// rewritten in place uses the decisions found that way.
 #include "adb_shard.hpp"
 
+#include <algorithm>
 #include <functional>
+#include <map>
 #include <set>
 
 namespace adb {
@@ -25,7 +34,15 @@ enum Tag : uint8_t { T_UNDEF, T_REP, T_SHARD, T_PART, T_CONST };
 struct Info {
     Tag tag = T_UNDEF;
     int axis = 0;
-    std::vector<int64_t> dims;  // global shape
+    std::vector<int64_t> dims;   // global shape
+    std::vector<int64_t> ldims;  // CONST: the shape the command was given (possibly cut along the batch)
+    int origin = -1;             // ordinal of the guessed decision this value's distribution rests on (-1: none)
+};
+
+// thrown when a guessed decision turns out wrong: command number `ordinal` must cut `axis` instead (-1: nothing)
+struct Decide {
+    int ordinal;
+    int axis;
 };
 
 struct Sharder {
@@ -34,6 +51,10 @@ struct Sharder {
     int64_t batch;
     std::vector<Info> info;
     std::vector<char> needed, is_dep;
+    const std::vector<std::string>* only = nullptr;   // ids of the CreateMat tensors that hold the batch (optional)
+    const std::map<int, int>* decided = nullptr;      // command ordinal -> axis to cut (-1: none), found by earlier attempts
+    int ordinal_ = 0;                                  // counts the commands that went through step()
+    int pending_origin_ = -1;                          // origin the result of the current command inherits
 
     Sharder(Program& p, int r, int w, int64_t b) : prog(p), rank(r), world(w), batch(b) {
         info.resize(p.ids.size());
@@ -114,6 +135,23 @@ struct Sharder {
         i.tag = t;
         i.axis = axis;
         i.dims = dims;
+        i.ldims.clear();
+        i.origin = (t == T_SHARD || t == T_CONST) ? pending_origin_ : -1;
+    }
+
+    std::vector<int64_t> local_dims(const Info& i) const {
+        if (i.tag == T_CONST) return i.ldims;
+        std::vector<int64_t> d = i.dims;
+        if (i.tag == T_SHARD && size_t(i.axis) < d.size()) d[size_t(i.axis)] /= world;
+        return d;
+    }
+    // a guessed decision (if there is one behind `i`) is replaced by `axis`; otherwise the program is refused
+    [[noreturn]] void redecide(const Info& i, int axis, const std::string& why) {
+        if (i.origin >= 0) {
+            auto it = decided ? decided->find(i.origin) : std::map<int, int>::const_iterator();
+            if (!decided || it == decided->end() || it->second != axis) throw Decide{i.origin, axis};
+        }
+        fail(why);
     }
 
     void block(Block& b) {
@@ -167,11 +205,35 @@ struct Sharder {
     }
 
     void step(Cmd& c, std::vector<Cmd>& out) {
+        const int ord = ordinal_++;
+        {
+            // the result inherits the guess behind the operand that fixes its distribution
+            uint32_t r[2];
+            int n;
+            reads(c, r, n);
+            pending_origin_ = -1;
+            for (int k = 0; k < n && pending_origin_ < 0; k++)
+                if (info[r[k]].tag == T_SHARD) pending_origin_ = info[r[k]].origin;
+            for (int k = 0; k < n && pending_origin_ < 0; k++)
+                if (info[r[k]].tag == T_CONST) pending_origin_ = info[r[k]].origin;
+            // constants only ever meet tensors in element-wise commands; anywhere else a cut constant is a wrong guess
+            const bool elementwise = c.op == OP_MUL || c.op == OP_ADD || c.op == OP_MUL_EQ || c.op == OP_ADD_EQ || c.op == OP_EQZ ||
+                                     c.op == OP_GTZ || c.op == OP_LTZ || c.op == OP_EXP2 || c.op == OP_LOG2 || c.op == OP_SIN ||
+                                     c.op == OP_RECIP || c.op == OP_SQRT || c.op == OP_CONTIG;
+            if (!elementwise)
+                for (int k = 0; k < n; k++) {
+                    const Info& x = info[r[k]];
+                    if (x.tag == T_CONST && x.ldims != x.dims) redecide(x, -1, "constant '" + name(r[k]) + "' is reshaped after it was cut along the batch");
+                }
+        }
         switch (c.op) {
         case OP_CREATE_MAT: {
             std::vector<int64_t> g = c.dims;
             int64_t n = prod(g, 0, g.size());
-            if (!g.empty() && g[0] == batch) {
+            const bool listed = !only || std::find(only->begin(), only->end(), name(c.res)) != only->end();
+            if (only && listed && (g.empty() || g[0] != batch))
+                fail("CreateMat '" + name(c.res) + "' is listed as holding the batch but its first dimension is not the batch");
+            if (!g.empty() && g[0] == batch && listed) {
                 if (batch % world) fail("batch is not divisible by the number of ranks");
                 int64_t local = n / world;
                 if (int64_t(c.count) == n) {
@@ -188,9 +250,22 @@ struct Sharder {
         }
         case OP_CREATE_CONST: {
             std::vector<int64_t> g = c.dims;
-            for (auto& d : c.dims)
-                if (d == batch) { d = batch / world; break; }
-            set(c.res, T_CONST, 0, g, c);
+            // guess: the first dimension that equals the batch is the batch (unless an earlier attempt found otherwise)
+            int cut = -1;
+            for (size_t k = 0; k < g.size() && cut < 0; k++)
+                if (g[k] == batch) cut = int(k);
+            const bool guessed = cut >= 0;
+            if (decided) {
+                auto it = decided->find(ord);
+                if (it != decided->end()) cut = it->second;
+            }
+            if (cut >= 0) {
+                if (size_t(cut) >= g.size() || g[size_t(cut)] % world) fail("constant '" + name(c.res) + "' cannot be cut along axis " + std::to_string(cut));
+                c.dims[size_t(cut)] = g[size_t(cut)] / world;
+            }
+            pending_origin_ = (guessed || cut >= 0) ? ord : -1;
+            set(c.res, T_CONST, std::max(cut, 0), g, c);
+            info[c.res].ldims = c.dims;
             return;
         }
         case OP_MUL: case OP_ADD: case OP_MUL_EQ: case OP_ADD_EQ: {
@@ -207,14 +282,35 @@ struct Sharder {
                 b = info[c.b];
             }
             const Info& shape_src = a.tag == T_CONST ? b : a;
+            // a constant must have the local shape of the tensor it meets
+            if ((a.tag == T_CONST) != (b.tag == T_CONST)) {
+                const Info& k = a.tag == T_CONST ? a : b;
+                const Info& t = a.tag == T_CONST ? b : a;
+                if (k.dims == t.dims && k.ldims != local_dims(t))
+                    redecide(k, t.tag == T_SHARD ? t.axis : -1,
+                             "constant '" + name(a.tag == T_CONST ? c.a : c.b) + "' does not have the shape of the tensor it is combined with");
+            }
             if (keep_partial) { set(c.res, T_PART, 0, shape_src.dims, c); return; }
-            if (a.tag == T_CONST && b.tag == T_CONST) { set(c.res, T_CONST, 0, a.dims, c); return; }
+            if (a.tag == T_CONST && b.tag == T_CONST) {
+                if (a.dims == b.dims && a.ldims != b.ldims) {
+                    if (b.origin >= 0) redecide(b, a.ldims == a.dims ? -1 : a.axis, "constants of different local shapes are combined");
+                    redecide(a, b.ldims == b.dims ? -1 : b.axis, "constants of different local shapes are combined");
+                }
+                set(c.res, T_CONST, a.axis, a.dims, c);
+                info[c.res].ldims = a.ldims;
+                return;
+            }
             if (a.tag == T_SHARD || b.tag == T_SHARD) {
                 const Info& s = a.tag == T_SHARD ? a : b;
                 const Info& o = a.tag == T_SHARD ? b : a;
+                if (o.tag == T_REP && s.origin >= 0) redecide(s, -1, "a broadcast along the batch meets a replicated tensor");
+                if (o.tag == T_SHARD && o.axis != s.axis) {
+                    if (o.origin >= 0) redecide(o, -1, "operands are sharded along different axes");
+                    if (s.origin >= 0) redecide(s, -1, "operands are sharded along different axes");
+                }
                 if (o.tag == T_REP) fail("'" + name(c.a) + "' and '" + name(c.b) + "' mix a sharded and a replicated tensor of the same shape");
                 if (o.tag == T_SHARD && o.axis != s.axis) fail("operands are sharded along different axes (tensors are recognised as batch tensors by their first dimension: a "
-                                                                 "parameter with as many rows as the batch is mistaken for one -- use a batch size that differs from the layer widths)");
+                                                                 "parameter with as many rows as the batch is mistaken for one -- name the batch tensors (adb_config.shard_ids) or use a batch size that differs from the layer widths)");
                 set(c.res, T_SHARD, s.axis, s.dims, c);
                 return;
             }
@@ -226,6 +322,7 @@ struct Sharder {
             resolve_partial(c.a, out);
             Info a = info[c.a];
             set(c.res, a.tag, a.axis, a.dims, c);
+            if (a.tag == T_CONST) info[c.res].ldims = a.ldims;
             return;
         }
         case OP_SUM: {
@@ -263,7 +360,11 @@ struct Sharder {
             else if (a.tag == T_SHARD && a.axis == 1 && b.tag == T_SHARD && b.axis == 0) set(c.res, T_PART, 0, g, c);
             else if (a_rep && b.tag == T_SHARD && b.axis == 1) set(c.res, T_SHARD, 1, g, c);
             else if (a_rep && b_rep) set(c.res, T_REP, 0, g, c);
-            else fail("DotProduct of '" + name(c.a) + "' and '" + name(c.b) + "' cannot be split over the batch");
+            else {
+                if (b.tag == T_SHARD && b.origin >= 0) redecide(b, -1, "DotProduct operand is a broadcast along the batch");
+                if (a.tag == T_SHARD && a.origin >= 0) redecide(a, -1, "DotProduct operand is a broadcast along the batch");
+                fail("DotProduct of '" + name(c.a) + "' and '" + name(c.b) + "' cannot be split over the batch");
+            }
             return;
         }
         case OP_VIEW: {
@@ -320,9 +421,11 @@ struct Sharder {
             if (a.tag == T_SHARD) {
                 if (int(c.dim) == a.axis) fail("Broadcast along the sharded axis");
                 set(c.res, T_SHARD, a.axis, g, c);
-            } else if (int64_t(c.count) == batch) {
-                // a replicated value repeated along the batch: every rank materialises only its rows
+            } else if (int64_t(c.count) == batch && !(decided && decided->count(ord) && decided->at(ord) < 0)) {
+                // a replicated value repeated along the batch (a guess: the count could be a layer width that
+                // happens to equal the batch): every rank materialises only its rows
                 c.count = uint64_t(batch / world);
+                pending_origin_ = ord;
                 set(c.res, T_SHARD, int(c.dim), g, c);
             } else
                 set(c.res, a.tag, 0, g, c);
@@ -352,13 +455,38 @@ struct Sharder {
 
 }  // namespace
 
-void shard_program(Program& prog, int rank, int world, int64_t batch) {
+void shard_program(Program& prog, int rank, int world, int64_t batch, const std::vector<std::string>* only) {
     if (world <= 1) return;
     if (batch <= 0) throw IrError("data-parallel rewrite: shard_batch must be positive");
     if (rank < 0 || rank >= world) throw IrError("data-parallel rewrite: rank out of range");
+    if (only && only->empty()) only = nullptr;
+    // attempts on scratch copies find out which guesses about constants / broadcasts do not hold ...
+    std::map<int, int> decided;
+    const std::vector<uint8_t> bytes = serialize_program(prog);
+    for (int attempt = 0;; attempt++) {
+        Program scratch = parse_program(bytes.data(), bytes.size());
+        Sharder s(scratch, rank, world, batch);
+        s.only = only;
+        s.decided = &decided;
+        try {
+            s.mark_needed();
+            s.block(scratch.main);
+            break;
+        } catch (const Decide& d) {
+            if (attempt >= 256) throw IrError("data-parallel rewrite: the shapes of constants and broadcasts cannot be reconciled");
+            decided[d.ordinal] = d.axis;
+        }
+    }
+    // ... and the program itself is rewritten in place with what they found
     Sharder s(prog, rank, world, batch);
-    s.mark_needed();
-    s.block(prog.main);
+    s.only = only;
+    s.decided = &decided;
+    try {
+        s.mark_needed();
+        s.block(prog.main);
+    } catch (const Decide&) {
+        throw IrError("data-parallel rewrite: internal inconsistency while applying decisions");
+    }
 }
 
 }  // namespace adb

@@ -37,7 +37,8 @@ NOALLOC_MAX_PARTIALS = 1 << 20
 class AdbConfig(ctypes.Structure):
     _fields_ = [("struct_size", ctypes.c_uint32), ("device_ordinal", ctypes.c_int32), ("rank", ctypes.c_int32),
                 ("world_size", ctypes.c_int32), ("nccl_unique_id", ctypes.c_void_p), ("flags", ctypes.c_uint32),
-                ("shard_batch", ctypes.c_uint64)]
+                ("shard_batch", ctypes.c_uint64), ("shard_ids", ctypes.POINTER(ctypes.c_char_p)),
+                ("n_shard_ids", ctypes.c_uint32)]
 
 
 class AdbStats(ctypes.Structure):
@@ -100,7 +101,7 @@ def load_library():
                                   ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t),
                                   ctypes.c_char_p, ctypes.c_size_t]
     L.adb_lower_check.restype = ctypes.c_int
-    L.adb_shard_ir.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64,
+    L.adb_shard_ir.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(AdbConfig),
                                u8p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t), ctypes.c_char_p, ctypes.c_size_t]
     L.adb_shard_ir.restype = ctypes.c_int
     L.adb_nccl_unique_id.argtypes = [ctypes.c_void_p]
@@ -113,12 +114,20 @@ def load_library():
     return L
 
 
-def lower_check(proc, dep_list, *, with_source=False, flags=0, rank=0, world=1, shard_batch=0) -> str:
+def _id_array(ids):
+    if not ids:
+        return None, 0
+    arr = (ctypes.c_char_p * len(ids))(*[i.encode() for i in ids])
+    return arr, len(ids)
+
+
+def lower_check(proc, dep_list, *, with_source=False, flags=0, rank=0, world=1, shard_batch=0, shard_ids=None) -> str:
     """Host-only: lower a traced program and JIT-compile every generated kernel for sm_100a
     (no GPU needed).  Returns the plan listing; raises AdbError with the reason on failure."""
     L = load_library()
     blob, keep = _ir.serialize(proc, dep_list)
-    cfg = AdbConfig(ctypes.sizeof(AdbConfig), 0, rank, world, None, flags, shard_batch)
+    ids, n_ids = _id_array(shard_ids)
+    cfg = AdbConfig(ctypes.sizeof(AdbConfig), 0, rank, world, None, flags, shard_batch, ids, n_ids)
     err = ctypes.create_string_buffer(1 << 16)
     need = ctypes.c_size_t(0)
     cap = 1 << 20
@@ -134,16 +143,18 @@ def lower_check(proc, dep_list, *, with_source=False, flags=0, rank=0, world=1, 
         cap = need.value + 16
 
 
-def shard_ir(blob: bytes, rank: int, world: int, shard_batch: int) -> bytes:
+def shard_ir(blob: bytes, rank: int, world: int, shard_batch: int, shard_ids=None) -> bytes:
     """Host-only: the data-parallel rewrite applied when world_size > 1, as a blob -> blob function."""
     L = load_library()
     err = ctypes.create_string_buffer(1 << 14)
     need = ctypes.c_size_t(0)
-    rc = L.adb_shard_ir(blob, len(blob), rank, world, shard_batch, None, 0, ctypes.byref(need), err, len(err))
+    ids, n_ids = _id_array(shard_ids)
+    cfg = AdbConfig(ctypes.sizeof(AdbConfig), 0, rank, world, None, 0, shard_batch, ids, n_ids)
+    rc = L.adb_shard_ir(blob, len(blob), ctypes.byref(cfg), None, 0, ctypes.byref(need), err, len(err))
     if rc != ADB_OK:
         raise AdbError(rc, err.value.decode(errors="replace"))
     out = (ctypes.c_uint8 * need.value)()
-    rc = L.adb_shard_ir(blob, len(blob), rank, world, shard_batch, out, need.value, ctypes.byref(need), err, len(err))
+    rc = L.adb_shard_ir(blob, len(blob), ctypes.byref(cfg), out, need.value, ctypes.byref(need), err, len(err))
     if rc != ADB_OK:
         raise AdbError(rc, err.value.decode(errors="replace"))
     return bytes(out)
@@ -154,7 +165,7 @@ class B200:
     reference's `Device` trait; `ir_callback` is a no-op and `dot_prod_shape` the trait's default."""
 
     def __init__(self, device_ordinal: int = 0, *, rank: int = 0, world_size: int = 1, nccl_unique_id: bytes | None = None,
-                 flags: int = 0, shard_batch: int = 0):
+                 flags: int = 0, shard_batch: int = 0, shard_ids=None):
         L = load_library()
         self._L = L
         uid = None
@@ -162,7 +173,8 @@ class B200:
             assert len(nccl_unique_id) == 128
             self._uid = ctypes.create_string_buffer(nccl_unique_id, 128)
             uid = ctypes.cast(self._uid, ctypes.c_void_p)
-        cfg = AdbConfig(ctypes.sizeof(AdbConfig), device_ordinal, rank, world_size, uid, flags, shard_batch)
+        ids, n_ids = _id_array(shard_ids)   # the ids of the CreateMat tensors that hold the batch (optional)
+        cfg = AdbConfig(ctypes.sizeof(AdbConfig), device_ordinal, rank, world_size, uid, flags, shard_batch, ids, n_ids)
         h = ctypes.c_void_p()
         rc = L.adb_create(ctypes.byref(cfg), ctypes.byref(h))
         if rc != ADB_OK:

@@ -72,6 +72,11 @@ typedef struct adb_config {
     const void *nccl_unique_id;/* 128 bytes from adb_nccl_unique_id on rank 0; NULL when world_size == 1 */
     uint32_t flags;            /* ADB_FLAG_* */
     uint64_t shard_batch;      /* world_size > 1: CreateMat tensors whose dim 0 equals this are split by rank */
+    /* Optional (read only when struct_size covers them): the ids of the CreateMat tensors that hold the batch.  When
+     * given, only these are split; otherwise every CreateMat whose dim 0 equals shard_batch is, which cannot tell a
+     * batch tensor from a parameter that happens to have as many rows. */
+    const char *const *shard_ids;
+    uint32_t n_shard_ids;
 } adb_config;
 
 #define ADB_FLAG_NO_GRAPHS 1u         /* launch loop bodies kernel by kernel instead of replaying CUDA graphs */
@@ -164,12 +169,11 @@ adb_status adb_lower_check(const uint8_t *blob, size_t nbytes, const adb_config 
                            char *buf, size_t cap, size_t *needed, char *err, size_t err_cap);
 
 /* Data-parallel rewrite used when world_size > 1 (no reference counterpart; the reference is
- * single-device): splits dim 0 of CreateMat tensors whose dim 0 == shard_batch across ranks and
- * inserts AllReduce commands where batch-partial values meet replicated ones.  Writes the new
- * blob into out (cap bytes); *needed receives its size. */
-adb_status adb_shard_ir(const uint8_t *blob, size_t nbytes, int32_t rank, int32_t world_size,
-                        uint64_t shard_batch, uint8_t *out, size_t cap, size_t *needed,
-                        char *err, size_t err_cap);
+ * single-device): splits dim 0 of CreateMat tensors whose dim 0 == cfg->shard_batch (or exactly those named in
+ * cfg->shard_ids) across cfg->world_size ranks and inserts AllReduce commands where batch-partial values meet
+ * replicated ones.  Writes rank cfg->rank's blob into out (cap bytes); *needed receives its size. */
+adb_status adb_shard_ir(const uint8_t *blob, size_t nbytes, const adb_config *cfg, uint8_t *out, size_t cap,
+                        size_t *needed, char *err, size_t err_cap);
 
 /* 128-byte NCCL unique id for adb_config.nccl_unique_id (rank 0 creates, the caller broadcasts it). */
 adb_status adb_nccl_unique_id(void *out128);

@@ -12,7 +12,20 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 KW = dict(batch=256, widths=(64, 128, 128, 64, 16), steps=4, lr=1e-2)
 
 
-def _worker(rank, world, port, out_dir, flags, kw=None):
+def _batch_ids(adb, kw):
+    """ids of x and t in the program `c4_mlp_train` traces (weights first, then biases, then x and t)"""
+    class Probe:
+        def ir_callback(self, irb): pass
+        def dot_prod_shape(self, a, b): return [a[0], b[1]]
+        def execute(self, proc, dep): self.mats = [c[3] for c in proc.main if c[0] == "CreateMat"]
+        def get_tensor(self, id_): return adb.autodiff.ValueData([1], np.zeros(1, np.float32), id_, False)
+    probe = Probe()
+    adb.configs.c4_mlp_train(probe, inputs=adb.configs.c4_inputs(batch=kw["batch"], widths=kw["widths"]), **kw)
+    n_layers = len(kw["widths"]) - 1
+    return probe.mats[2 * n_layers: 2 * n_layers + 2]
+
+
+def _worker(rank, world, port, out_dir, flags, kw=None, name_batch=False):
     kw = kw or KW
     sys.path.insert(0, ROOT)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
@@ -25,7 +38,8 @@ def _worker(rank, world, port, out_dir, flags, kw=None):
     adb = importlib.import_module("autodiff-ir-rust_b200")
     box = [adb.devices.nccl_unique_id() if rank == 0 else None]
     dist.broadcast_object_list(box, src=0)
-    dev = adb.devices.B200(rank, rank=rank, world_size=world, nccl_unique_id=box[0], shard_batch=kw["batch"], flags=flags)
+    dev = adb.devices.B200(rank, rank=rank, world_size=world, nccl_unique_id=box[0], shard_batch=kw["batch"], flags=flags,
+                           shard_ids=_batch_ids(adb, kw) if name_batch else None)
     inputs = adb.configs.c4_inputs(batch=kw["batch"], widths=kw["widths"])     # full tensors: the device takes its rows
     out = adb.configs.c4_mlp_train(dev, inputs=inputs, **kw)
     np.savez(os.path.join(out_dir, f"rank{rank}.npz"), **{k: v.numpy() for k, v in out.items()})
@@ -68,6 +82,28 @@ def test_two_gpus_match_one_gpu_at_the_benchmark_widths(tmp_path):
     dev = adb.devices.B200(0)
     want = adb.configs.c4_mlp_train(dev, inputs=adb.configs.c4_inputs(batch=kw["batch"], widths=kw["widths"]), **kw)
     assert dev.stats()["tc_gemm_launches"] == 22
+    dev.close()
+    for r in range(2):
+        got = np.load(tmp_path / f"rank{r}.npz")
+        for k, v in want.items():
+            ref = v.numpy()
+            err = np.abs(got[k] - ref).max() / max(np.abs(ref).max(), 1e-30)
+            assert err < 1e-4, (r, k, err)
+
+
+def test_batch_equal_to_a_layer_width_with_named_batch_tensors(tmp_path):
+    """batch 128 with 128-wide layers: shapes alone cannot tell the weights from the batch tensors; with x and t named
+    (adb_config.shard_ids) two GPUs reproduce the single-GPU run."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    adb = importlib.import_module("autodiff-ir-rust_b200")
+    kw = dict(batch=128, widths=(64, 128, 128, 64, 16), steps=3, lr=1e-2)
+    port = 29800 + (os.getpid() % 2000)
+    mp.spawn(_worker, args=(2, port, str(tmp_path), 0, kw, True), nprocs=2, join=True)
+    dev = adb.devices.B200(0)
+    want = adb.configs.c4_mlp_train(dev, inputs=adb.configs.c4_inputs(batch=kw["batch"], widths=kw["widths"]), **kw)
     dev.close()
     for r in range(2):
         got = np.load(tmp_path / f"rank{r}.npz")

@@ -28,12 +28,20 @@ class _Capture:
         return adb.autodiff.ValueData([1], np.zeros(1, np.float32), id_, False)
 
 
-def _traced_c4():
+def _traced_c4(kw=None):
+    kw = kw or KW
     cap = _Capture()
-    inputs = cfg.c4_inputs(batch=KW["batch"], widths=KW["widths"])
-    handles = cfg.c4_mlp_train(cap, inputs=inputs, execute=False, **KW)
+    inputs = cfg.c4_inputs(batch=kw["batch"], widths=kw["widths"])
+    handles = cfg.c4_mlp_train(cap, inputs=inputs, execute=False, **kw)
     adb.autodiff.execute()
     return cap, handles, inputs
+
+
+def _batch_ids(kw):
+    """ids of x and t: `c4_mlp_train` creates the weights, then the biases, then x and t"""
+    mats = [c[3] for c in adb.autodiff.current_ir().main if c[0] == "CreateMat"]
+    n_layers = len(kw["widths"]) - 1
+    return mats[2 * n_layers: 2 * n_layers + 2]
 
 
 def test_rewrite_places_one_allreduce_per_parameter_and_one_for_the_loss():
@@ -46,7 +54,7 @@ def test_rewrite_places_one_allreduce_per_parameter_and_one_for_the_loss():
     assert sharded != cap.blob
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, kw=None, with_ids=False):
     sys.path.insert(0, ROOT)
     import torch
     import torch.distributed as dist
@@ -54,8 +62,9 @@ def _worker(rank, world, port, out_dir):
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     from oracle.oracle import OracleDevice
-    cap, handles, _ = _traced_c4()
-    blob = adb.devices.shard_ir(cap.blob, rank, world, KW["batch"])
+    kw = kw or KW
+    cap, handles, _ = _traced_c4(kw)
+    blob = adb.devices.shard_ir(cap.blob, rank, world, kw["batch"], _batch_ids(kw) if with_ids else None)
 
     def allreduce(arr):
         t = torch.from_numpy(arr)
@@ -96,3 +105,31 @@ def test_rewrite_rejects_programs_it_cannot_split():
     with pytest.raises(adb.devices.AdbError) as e:
         adb.devices.shard_ir(cap.blob, 0, 2, 32)
     assert "sharded axis" in str(e.value)
+
+
+@pytest.mark.parametrize("kw,world", [
+    (dict(batch=24, widths=(16, 24, 24, 16, 8), steps=3, lr=1e-2), 2),     # batch == hidden widths
+    (dict(batch=16, widths=(16, 24, 24, 16, 8), steps=2, lr=1e-2), 2),     # batch == input width (x is square) and a hidden width
+    (dict(batch=8, widths=(16, 24, 24, 16, 8), steps=2, lr=1e-2), 2),      # batch == output width (t is square)
+    (dict(batch=24, widths=(24, 24, 24, 24, 24), steps=2, lr=1e-2), 4),    # everything is 24 wide, four ranks
+])
+def test_named_batch_tensors_resolve_a_batch_that_equals_a_layer_width(tmp_path, kw, world):
+    """A batch that equals layer widths: by shape alone a weight looks like a batch tensor and the rewrite refuses the
+    program; with x and t named, constants and broadcasts that merely look batch-shaped are sorted out where they meet
+    tensors, and the gloo ranks reproduce the single-process run."""
+    import torch.multiprocessing as mp
+    from oracle.oracle import OracleDevice
+    cap, _, _ = _traced_c4(kw)
+    ids = _batch_ids(kw)
+    assert len(ids) == 2
+    with pytest.raises(adb.devices.AdbError):
+        adb.devices.shard_ir(cap.blob, 0, world, kw["batch"])
+    port = 31500 + (os.getpid() % 2000) + world * 7 + kw["batch"]
+    mp.spawn(_worker, args=(world, port, str(tmp_path), kw, True), nprocs=world, join=True)
+    want = cfg.c4_mlp_train(OracleDevice(), inputs=cfg.c4_inputs(batch=kw["batch"], widths=kw["widths"]), **kw)
+    for r in range(world):
+        got = np.load(tmp_path / f"rank{r}.npz")
+        for k, v in want.items():
+            ref = v.numpy()
+            err = np.abs(got[k] - ref).max() / max(np.abs(ref).max(), 1e-30)
+            assert err < 1e-5, (r, k, err)
