@@ -4,7 +4,8 @@
 //
 //   hostcheck <flags> <world> <shard_batch> <blob files ...>
 //
-// flags: bit 0 no fusion, bit 1 fold small sums, bit 2 correctly rounded division.
+// flags: bit 0 no fusion, bit 1 fold small sums, bit 2 correctly rounded division, bit 3 also execute every plan on
+// the CPU (plan_interp.hpp) and write the kept tensors to <blob file>.out.
 // Malformed blobs must be rejected with an exception (counted), never crash.  Every plan that does come out is
 // checked against the invariants below (step order, buffer lifetimes, arena placement).
 #include <algorithm>
@@ -19,6 +20,7 @@
 #include "adb_ir.hpp"
 #include "adb_lower.hpp"
 #include "adb_shard.hpp"
+#include "plan_interp.hpp"
 
 // Invariants every plan must satisfy, whatever passes rewrote its step list:
 //   1. step positions increase in execution order (nested blocks lie between their parent and its successor);
@@ -138,7 +140,7 @@ int main(int argc, char** argv) {
     const unsigned flags = unsigned(std::atoi(argv[1]));
     const int world = std::atoi(argv[2]);
     const long long batch = std::atoll(argv[3]);
-    size_t kernels = 0, rejected = 0, fused = 0;
+    size_t kernels = 0, rejected = 0, fused = 0, executed = 0;
     for (int f = 4; f < argc; f++) {
         std::ifstream in(argv[f], std::ios::binary);
         std::vector<uint8_t> blob((std::istreambuf_iterator<char>(in)), std::istreambuf_iterator<char>());
@@ -157,10 +159,31 @@ int main(int argc, char** argv) {
                 adb::generate_kernels(plan);
                 for (auto& k : plan.kernels) {
                     kernels += !k.dead;
-                    fused += k.reds.size();
+                    fused += k.reds.size() + (k.type == adb::KernelSpec::ROWS ? 1 : 0);
                 }
                 std::string listing = adb::dump_plan(plan, true);
                 if (listing.empty()) return 3;
+                if ((flags & 8) && world == 1) {
+                    adbtest::PlanInterp run(plan);
+                    run.run();
+                    std::ofstream res(std::string(argv[f]) + ".out", std::ios::binary);
+                    for (auto& r : plan.results) {
+                        const uint32_t len = uint32_t(r.id.size()), nd = uint32_t(r.shape.size());
+                        res.write(reinterpret_cast<const char*>(&len), 4);
+                        res.write(r.id.data(), len);
+                        res.write(reinterpret_cast<const char*>(&nd), 4);
+                        uint64_t n = 1;
+                        for (auto d : r.shape) {
+                            const uint64_t dd = uint64_t(d);
+                            res.write(reinterpret_cast<const char*>(&dd), 8);
+                            n *= dd;
+                        }
+                        const uint8_t defined = r.buf >= 0;
+                        res.write(reinterpret_cast<const char*>(&defined), 1);
+                        if (defined) res.write(reinterpret_cast<const char*>(run.ptr(r.buf, r.off)), std::streamsize(n * 4));
+                    }
+                    executed++;
+                }
                 std::string bad = check_plan(plan);
                 if (!bad.empty()) {
                     std::fprintf(stderr, "plan invariant violated in %s (rank %d): %s\n%s\n", argv[f], rank, bad.c_str(),
@@ -172,6 +195,6 @@ int main(int argc, char** argv) {
             }
         }
     }
-    std::printf("files=%d kernels=%zu fused_sums=%zu rejected=%zu\n", argc - 4, kernels, fused, rejected);
+    std::printf("files=%d kernels=%zu fused_sums=%zu rejected=%zu executed=%zu\n", argc - 4, kernels, fused, rejected, executed);
     return 0;
 }

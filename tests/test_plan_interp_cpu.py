@@ -1,0 +1,147 @@
+"""The lowering, checked numerically without a GPU: every plan is executed on the CPU by the interpreter in
+tests/hostcheck/plan_interp.hpp (same arena layout, same partial-sum layouts as the generated kernels, arena poisoned
+with NaN) and the kept tensors are compared with the CPU oracle -- the reference's known-answer programs, the benchmark
+programs at sizes that reach every fusion pass, and a few hundred random programs, with and without the passes."""
+import importlib
+import os
+import struct
+import subprocess
+
+import numpy as np
+import pytest
+
+import fuzz_programs
+import ref_programs
+from oracle.oracle import OracleDevice
+from test_host_sanitizers_cpu import hostcheck  # noqa: F401  (fixture: the sanitizer build of the host code)
+
+adb = importlib.import_module("autodiff-ir-rust_b200")
+ad, nn, cfg = adb.autodiff, adb.nn, adb.configs
+
+
+class _Both(OracleDevice):
+    """Runs the program on the oracle and keeps the self-contained blob for the interpreter."""
+
+    def __init__(self):
+        super().__init__()
+        self.blobs = []
+
+    def execute(self, proc, dep):
+        self.blobs.append(adb.ir.serialize(proc, dep, inline_limit=1 << 40)[0])
+        super().execute(proc, dep)
+
+
+def _read_results(path):
+    out = {}
+    data = open(path, "rb").read()
+    pos = 0
+    while pos < len(data):
+        (n,) = struct.unpack_from("<I", data, pos); pos += 4
+        name = data[pos:pos + n].decode(); pos += n
+        (nd,) = struct.unpack_from("<I", data, pos); pos += 4
+        dims = struct.unpack_from("<%dQ" % nd, data, pos); pos += 8 * nd
+        defined = data[pos]; pos += 1
+        if defined:
+            cnt = int(np.prod(dims)) if nd else 1
+            out[name] = (list(dims), np.frombuffer(data, np.float32, cnt, pos).copy()); pos += 4 * cnt
+    return out
+
+
+def _interpret(binary, tmp_path, blob, flags, tag):
+    f = tmp_path / f"{tag}.adir"
+    f.write_bytes(blob)
+    env = dict(os.environ, ASAN_OPTIONS="detect_leaks=1", UBSAN_OPTIONS="print_stacktrace=1")
+    r = subprocess.run([binary, str(flags | 8), "1", "0", str(f)], capture_output=True, text=True, env=env, timeout=900)
+    assert r.returncode == 0, r.stderr[-3000:]
+    assert "executed=1" in r.stdout, r.stdout
+    return _read_results(str(f) + ".out")
+
+
+def _compare(got, kept, tol, atol=0.0):
+    for name, v in kept.items():
+        if v.is_none:
+            continue
+        assert name in got, f"{name} missing from the interpreted plan"
+        dims, data = got[name]
+        assert dims == list(v.dim), (name, dims, v.dim)
+        want = np.asarray(v.data, np.float64)
+        if not np.isfinite(want).all():
+            continue
+        scale = max(float(np.abs(want).max()), 1e-30) if want.size else 1.0
+        diff = float(np.abs(data.astype(np.float64) - want).max()) if want.size else 0.0
+        assert diff <= tol * scale + atol, f"{name}: error {diff:.3e} on a tensor of magnitude {scale:.3e}"
+
+
+@pytest.mark.parametrize("flags", [0, 1, 2], ids=["default", "one-kernel-per-command", "fusions-at-any-size"])
+def test_reference_and_benchmark_programs(hostcheck, tmp_path, flags):  # noqa: F811
+    programs = [(n, ref_programs.ALL[n], {}) for n in sorted(ref_programs.ALL)]
+    programs += [("c1", cfg.c1_readme_mlp, {}),
+                 ("c2", cfg.c2_fused_elementwise, dict(rows=96, cols=136)),
+                 ("c3", cfg.c3_reduce_movement, dict(batch=8, n=16)),
+                 ("c4", cfg.c4_mlp_train, dict(batch=96, widths=(24, 40, 40, 24, 8), steps=3, lr=1e-2)),
+                 ("c5", cfg.c5_dot_loop, dict(n=24, max_iters=4))]
+    for name, fn, kw in programs:
+        dev = _Both()
+        kept = fn(dev, **kw)
+        got = _interpret(hostcheck, tmp_path, dev.blobs[-1], flags, name)
+        if isinstance(kept, dict):
+            by_id = {v.id: v for v in kept.values() if hasattr(v, "id")}
+            # (the known-answer programs return values rounded to four decimals, as the reference's tests compare them)
+            _compare(got, by_id, 1e-4, atol=6e-5)
+        assert got, name
+
+
+def test_fusions_at_their_real_thresholds(hostcheck, tmp_path):  # noqa: F811
+    """Sizes at which the sum fusion and the row chains switch on by themselves."""
+    dev = _Both()
+    kept = cfg.c2_fused_elementwise(dev, rows=520, cols=1000)
+    _compare(_interpret(hostcheck, tmp_path, dev.blobs[-1], 0, "c2big"), {v.id: v for v in kept.values()}, 1e-4)
+    dev = _Both()
+    ad.set_device(dev)
+    ad.eager_dep_opt()
+    x = np.random.default_rng(5).standard_normal(300 * 1024).astype(np.float32)
+    y = nn.LayerNorm(1024).f(ad.tensor(x, [300, 1024])).forward()
+    y.keep()
+    ad.execute()
+    _compare(_interpret(hostcheck, tmp_path, dev.blobs[-1], 0, "ln"), {y.id: y.get()}, 1e-4)
+
+
+@pytest.mark.parametrize("chunk", range(6))
+def test_random_programs(hostcheck, tmp_path, chunk):  # noqa: F811
+    """50 random programs per case, each through the default lowering and with every fusion at any size."""
+    for seed in range(chunk * 50, chunk * 50 + 50):
+        exact = seed % 2 == 0
+        dev = _Both()
+        with np.errstate(all="ignore"):
+            kept = fuzz_programs.build(seed if exact else 1000 + seed, exact=exact)(dev)
+        by_id = {v.id: v for v in kept.values()}
+        for flags in (0, 2):
+            got = _interpret(hostcheck, tmp_path, dev.blobs[-1], flags, f"fz{seed}_{flags}")
+            _compare(got, by_id, 0.0 if exact else 1e-4)
+
+
+@pytest.mark.parametrize("P,Q", [(7, 5), (33, 131), (40, 64), (3, 1000)])
+def test_side_sums_and_row_chains_on_ragged_shapes(hostcheck, tmp_path, P, Q):  # noqa: F811
+    """Element-wise passes with row and column side sums, and max / sum row chains, on shapes that are not multiples
+    of the vector width or the tile sizes (fusions forced on at any size)."""
+    rng = np.random.default_rng(P * 1000 + Q)
+    x = rng.standard_normal(P * Q).astype(np.float32)
+    w = rng.standard_normal(Q).astype(np.float32)
+    dev = _Both()
+    ad.set_device(dev)
+    ad.eager_dep_opt()
+    t = ad.tensor(x, [P, Q])
+    tw = ad.tensor(w, [Q]).view([1, Q]).broadcast(0, P)
+    y = ((t * tw + 0.5).sin() * t).forward()
+    rows = y.to_node().sum(1).forward() if hasattr(y, "to_node") else None
+    cols = (y.to_node() * y.to_node()).sum(0).forward()
+    m = t.max(1)
+    e = (t - m.unsqueeze(-1).broadcast(-1, Q)).exp()
+    sm = (e * e.sum(1).recip().unsqueeze(-1).broadcast(-1, Q)).forward()
+    kept = {}
+    for v in (y, rows, cols, sm):
+        v.keep()
+    ad.execute()
+    kept = {v.id: v.get() for v in (y, rows, cols, sm)}
+    for flags in (0, 2):
+        _compare(_interpret(hostcheck, tmp_path, dev.blobs[-1], flags, f"ragged{flags}"), kept, 1e-4)
