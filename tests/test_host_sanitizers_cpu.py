@@ -37,16 +37,6 @@ class _Capture:
         return adb.autodiff.ValueData([1], np.zeros(1, np.float32), id_, False)
 
 
-@pytest.fixture(scope="module")
-def hostcheck(tmp_path_factory):
-    out = tmp_path_factory.mktemp("hostcheck") / "hostcheck"
-    cmd = ["g++", "-std=c++17", "-O1", "-g", "-fsanitize=address,undefined", "-fno-sanitize-recover=undefined",
-           "-I", CSRC, os.path.join(ROOT, "tests", "hostcheck", "hostcheck.cpp"), os.path.join(CSRC, "adb_lower.cpp"),
-           os.path.join(CSRC, "adb_codegen.cpp"), os.path.join(CSRC, "adb_shard.cpp"), "-o", str(out)]
-    subprocess.run(cmd, check=True, capture_output=True, text=True)
-    return str(out)
-
-
 def _run(binary, files, flags=0, world=1, batch=0):
     env = dict(os.environ, ASAN_OPTIONS="detect_leaks=1:abort_on_error=0", UBSAN_OPTIONS="print_stacktrace=1")
     r = subprocess.run([binary, str(flags), str(world), str(batch)] + files, capture_output=True, text=True, env=env, timeout=600)

@@ -13,7 +13,6 @@ import pytest
 import fuzz_programs
 import ref_programs
 from oracle.oracle import OracleDevice
-from test_host_sanitizers_cpu import hostcheck  # noqa: F401  (fixture: the sanitizer build of the host code)
 
 adb = importlib.import_module("autodiff-ir-rust_b200")
 ad, nn, cfg = adb.autodiff, adb.nn, adb.configs
@@ -73,7 +72,7 @@ def _compare(got, kept, tol, atol=0.0):
 
 
 @pytest.mark.parametrize("flags", [0, 1, 2], ids=["default", "one-kernel-per-command", "fusions-at-any-size"])
-def test_reference_and_benchmark_programs(hostcheck, tmp_path, flags):  # noqa: F811
+def test_reference_and_benchmark_programs(hostcheck, tmp_path, flags):
     programs = [(n, ref_programs.ALL[n], {}) for n in sorted(ref_programs.ALL)]
     programs += [("c1", cfg.c1_readme_mlp, {}),
                  ("c2", cfg.c2_fused_elementwise, dict(rows=96, cols=136)),
@@ -91,7 +90,7 @@ def test_reference_and_benchmark_programs(hostcheck, tmp_path, flags):  # noqa: 
         assert got, name
 
 
-def test_fusions_at_their_real_thresholds(hostcheck, tmp_path):  # noqa: F811
+def test_fusions_at_their_real_thresholds(hostcheck, tmp_path):
     """Sizes at which the sum fusion and the row chains switch on by themselves."""
     dev = _Both()
     kept = cfg.c2_fused_elementwise(dev, rows=520, cols=1000)
@@ -107,7 +106,7 @@ def test_fusions_at_their_real_thresholds(hostcheck, tmp_path):  # noqa: F811
 
 
 @pytest.mark.parametrize("chunk", range(6))
-def test_random_programs(hostcheck, tmp_path, chunk):  # noqa: F811
+def test_random_programs(hostcheck, tmp_path, chunk):
     """50 random programs per case, each through the default lowering and with every fusion at any size."""
     for seed in range(chunk * 50, chunk * 50 + 50):
         exact = seed % 2 == 0
@@ -121,7 +120,7 @@ def test_random_programs(hostcheck, tmp_path, chunk):  # noqa: F811
 
 
 @pytest.mark.parametrize("P,Q", [(7, 5), (33, 131), (40, 64), (3, 1000)])
-def test_side_sums_and_row_chains_on_ragged_shapes(hostcheck, tmp_path, P, Q):  # noqa: F811
+def test_side_sums_and_row_chains_on_ragged_shapes(hostcheck, tmp_path, P, Q):
     """Element-wise passes with row and column side sums, and max / sum row chains, on shapes that are not multiples
     of the vector width or the tile sizes (fusions forced on at any size)."""
     rng = np.random.default_rng(P * 1000 + Q)
