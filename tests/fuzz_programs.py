@@ -123,3 +123,55 @@ def build(seed: int, exact: bool, n_ops: int = 14):
         ad.execute()
         return {k: v.get() for k, v in outs.items()}
     return prog
+
+
+def build_loop(seed: int):
+    """A random loop program: two matrices, a row vector and two accumulators updated in place by a random sequence of
+    statements (scaled adds, sin chains, row / column sums and maxima fed back through broadcasts) for a few
+    iterations of an IR for-loop.  Some seeds describe cyclic updates the frontend cannot trace (RecursionError);
+    callers skip those."""
+    rng = np.random.default_rng(seed)
+    P, Q, iters = int(rng.integers(1, 12)), int(rng.integers(1, 20)), int(rng.integers(1, 4))
+    xa = rng.standard_normal(P * Q).astype(np.float32)
+    xb = rng.standard_normal(P * Q).astype(np.float32)
+    xw = rng.standard_normal(Q).astype(np.float32)
+    plan = [int(k) for k in rng.integers(0, 8, size=int(rng.integers(2, 7)))]
+
+    def prog(dev):
+        ad.set_device(dev)
+        st = {"a": ad.tensor(xa, [P, Q]), "b": ad.tensor(xb, [P, Q]), "w": ad.tensor(xw, [Q]),
+              "c": ad.tensor(np.zeros(Q, np.float32), [Q]), "r": ad.tensor(np.zeros(P, np.float32), [P])}
+
+        def body(i):
+            for k in plan:
+                a, b, w, c, r = st["a"], st["b"], st["w"], st["c"], st["r"]
+                wb = w.view([1, Q]).broadcast(0, P)
+                if k == 0:
+                    a += b * 0.5
+                    a.forward()
+                elif k == 1:
+                    b += (a * wb).sin() * 0.1
+                    b.forward()
+                elif k == 2:
+                    c += a.sum(0)
+                    c.forward()
+                elif k == 3:
+                    r += (a * b).sum(1)
+                    r.forward()
+                elif k == 4:
+                    w += a.sum(0) * 0.01
+                    w.forward()
+                elif k == 5:
+                    a += r.unsqueeze(-1).broadcast(-1, Q) * 0.01
+                    a.forward()
+                elif k == 6:
+                    b += c.view([1, Q]).broadcast(0, P) * 0.01
+                    b.forward()
+                else:
+                    m = a.max(1)
+                    a += (a - m.unsqueeze(-1).broadcast(-1, Q)) * 0.1
+                    a.forward()
+        ad.ir_for(range(0, iters), body)
+        ad.execute()
+        return {k: v.val().get() for k, v in st.items()}
+    return prog

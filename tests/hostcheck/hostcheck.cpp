@@ -88,16 +88,20 @@ static void collect(const adb::Plan& plan, const adb::StepBlock& blk, std::vecto
 
 //   4. a buffer that a loop body shares with code outside the loop stays alive for the whole loop
 static std::string check_loops(const adb::Plan& plan, const adb::StepBlock& blk) {
-    for (auto& s : blk.steps) {
+    for (size_t si = 0; si < blk.steps.size(); si++) {
+        const adb::Step& s = blk.steps[si];
         std::string e;
         if (s.kind == adb::Step::WHILE && s.body) {
             std::vector<int> touched;
             int lo = INT_MAX, hi = -1;
             collect(plan, *s.body, touched, lo, hi);
+            // positions that belong to the loop: behind the While step, in front of its successor (steps that a
+            // pass moved or removed may have left earlier positions of the body in a buffer's lifetime)
+            const int span_lo = s.pos, span_hi = si + 1 < blk.steps.size() ? blk.steps[si + 1].pos : INT_MAX;
             for (int b : touched) {
                 const adb::BufferInfo& bi = plan.bufs[size_t(b)];
                 if (bi.external || bi.persistent || hi < 0) continue;
-                const bool outside = bi.first < lo || bi.last > hi;
+                const bool outside = bi.first <= span_lo || bi.last >= span_hi;
                 if (outside && !(bi.first <= lo && bi.last >= hi))
                     return "buffer '" + bi.name + "' [" + std::to_string(bi.first) + "," + std::to_string(bi.last) +
                            "] is shared with a loop spanning [" + std::to_string(lo) + "," + std::to_string(hi) + "] but dies inside it";

@@ -144,3 +144,21 @@ def test_side_sums_and_row_chains_on_ragged_shapes(hostcheck, tmp_path, P, Q):
     kept = {v.id: v.get() for v in (y, rows, cols, sm)}
     for flags in (0, 2):
         _compare(_interpret(hostcheck, tmp_path, dev.blobs[-1], flags, f"ragged{flags}"), kept, 1e-4)
+
+
+def test_random_loop_programs(hostcheck, tmp_path):
+    """In-place updates, sums and maxima fed back through broadcasts inside IR loops: default lowering, one kernel
+    per command, and every fusion at any size."""
+    ran = 0
+    for seed in range(150):
+        dev = _Both()
+        try:
+            with np.errstate(all="ignore"):
+                kept = fuzz_programs.build_loop(seed)(dev)
+        except RecursionError:
+            continue            # a cyclic update the frontend cannot trace
+        ran += 1
+        by_id = {v.id: v for v in kept.values()}
+        for flags in (0, 1, 2):
+            _compare(_interpret(hostcheck, tmp_path, dev.blobs[-1], flags, f"loop{seed}_{flags}"), by_id, 2e-4)
+    assert ran >= 30
