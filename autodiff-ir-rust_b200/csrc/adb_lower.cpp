@@ -93,6 +93,10 @@ class Lowerer {
         // aliases keep their parents alive and make them cross-segment when they are
         propagate_alias_cross(prog_.main);
         index_mats(prog_.main);
+        {
+            std::vector<uint32_t> all;
+            collect_assigned(prog_.main, all);
+        }
         cur_ = &plan_.main;
         bool stopped = lower_block(prog_.main, true);
         (void)stopped;
@@ -135,6 +139,139 @@ class Lowerer {
 
     [[noreturn]] void fail(const std::string& msg) { throw LowerError(msg); }
     const std::string& name(uint32_t id) const { return prog_.ids[id]; }
+
+    // ------------------------------------------------------------------ views at control-flow joins
+    // An id bound to a View / Index / Permute / Broadcast / Concat is not a value but a window: it shows whatever its
+    // source holds when it is read.  Straight-line code resolves that at lowering time.  Where paths meet -- a loop
+    // body that runs zero, one or many times, a branch that is taken or not -- an id must look the same whichever
+    // path was taken, and the only common form is "the value sits in the id's own buffer".  So an id that is a window
+    // in front of a While / If and is assigned somewhere inside, or that a block leaves behind as a window, is
+    // frozen: its current contents are copied into its buffer.  A frozen copy stops following its source, which is
+    // only right when nothing reads the id (or a view of it) after its source has changed while it would still be a
+    // window; `check_freeze` walks the rest of the program (loop back-edges included) and the lowering refuses the
+    // program when that can happen.
+    struct Frame { const Block* blk; size_t idx; bool is_while; };
+    std::vector<Frame> frames_;                                          // blocks being lowered, outermost first
+    std::unordered_map<const Block*, std::vector<uint32_t>> assigned_;   // ids assigned anywhere inside a block
+
+    void collect_assigned(Block& b, std::vector<uint32_t>& out) {
+        auto nested = [&](Block& inner) {
+            std::vector<uint32_t>& v = assigned_[&inner];
+            collect_assigned(inner, v);
+            out.insert(out.end(), v.begin(), v.end());
+        };
+        for (auto& c : b.cmds) {
+            if (c.op == OP_WHILE) nested(*c.block);
+            else if (c.op == OP_IF) {
+                for (auto& cb : c.conds) nested(*cb.second);
+                if (c.else_block) nested(*c.else_block);
+            } else if (has_result(c.op)) out.push_back(c.res);
+        }
+        std::sort(out.begin(), out.end());
+        out.erase(std::unique(out.begin(), out.end()), out.end());
+    }
+
+    enum : uint8_t { S_WINDOW = 1, S_STALE = 2, S_REBOUND = 4 };   // possible states of a frozen id along the paths that reach a point
+    struct FreezeScan {
+        uint32_t id;
+        std::unordered_set<uint32_t> sources;   // ids the window looks through, transitively
+        std::unordered_set<uint32_t> readers;   // the id and the views derived from it afterwards
+        bool conflict = false;
+        uint32_t where = 0;
+    };
+    void scan_read(uint32_t r, uint8_t st, FreezeScan& f) {
+        if ((st & S_STALE) && f.readers.count(r) && !f.conflict) { f.conflict = true; f.where = r; }
+    }
+    uint8_t scan_loop(const Cmd& c, uint8_t st, FreezeScan& f) {
+        uint8_t acc = st;
+        for (int it = 0; it < 4; it++) {
+            uint8_t out = scan_cmds(*c.block, 0, acc, f);
+            scan_read(c.a, out, f);
+            if ((acc | out) == acc) break;
+            acc |= out;
+        }
+        return acc;
+    }
+    uint8_t scan_cmd(const Cmd& c, uint8_t st, FreezeScan& f) {
+        if (c.op == OP_WHILE) {
+            scan_read(c.a, st, f);
+            return scan_loop(c, st, f);
+        }
+        if (c.op == OP_IF) {
+            for (auto& cb : c.conds) scan_read(cb.first, st, f);
+            uint8_t out = 0;
+            for (auto& cb : c.conds) out |= scan_cmds(*cb.second, 0, st, f);
+            out |= c.else_block ? scan_cmds(*c.else_block, 0, st, f) : st;
+            return out;
+        }
+        if (!has_result(c.op) || !live(c)) return st;
+        uint32_t r[2];
+        int n;
+        cmd_reads(c, r, n);
+        for (int k = 0; k < n; k++) {
+            if (!f.readers.count(r[k])) continue;
+            if (is_alias_op(c.op)) { if (c.res != f.id) f.readers.insert(c.res); }
+            else scan_read(r[k], st, f);
+        }
+        if (c.res == f.id) return S_REBOUND;
+        if (f.sources.count(c.res) && (st & S_WINDOW)) st = uint8_t((st & ~S_WINDOW) | S_STALE);
+        return st;
+    }
+    uint8_t scan_cmds(const Block& b, size_t from, uint8_t st, FreezeScan& f) {
+        for (size_t i = from; i < b.cmds.size() && !f.conflict; i++) st = scan_cmd(b.cmds[i], st, f);
+        return st;
+    }
+
+    // `id` is bound to a view and is about to be frozen in front of command `from` of `blk` (frames_ = the blocks
+    // around it): refuse when a later read could tell the copy from the window
+    void check_freeze(uint32_t id, const Block& blk, size_t from) {
+        FreezeScan f;
+        f.id = id;
+        f.readers.insert(id);
+        std::vector<uint32_t> st{id};
+        while (!st.empty()) {
+            uint32_t x = st.back();
+            st.pop_back();
+            if (bind_[x].kind != Binding::ALIAS) continue;
+            const Cmd& c = *bind_[x].cmd;
+            if (f.sources.insert(c.a).second) st.push_back(c.a);
+            if (c.op == OP_CONCAT && f.sources.insert(c.b).second) st.push_back(c.b);
+        }
+        uint8_t state = scan_cmds(blk, from, S_WINDOW, f);
+        for (size_t d = frames_.size(); d-- > 0 && !f.conflict;) {
+            const Frame& fr = frames_[d];
+            if (fr.is_while) state = scan_loop(fr.blk->cmds[fr.idx], state, f);
+            state = scan_cmds(*fr.blk, fr.idx + 1, state, f);
+        }
+        for (auto d : prog_.dep) scan_read(d, state, f);
+        if (f.conflict)
+            fail("'" + name(id) + "' is a view when control flow joins and is read (through '" + name(f.where) +
+                 "') after its source changes; whether it still follows the source then depends on the path taken, "
+                 "which a lowered program cannot express -- make it a tensor of its own (Contigious) first");
+    }
+
+    void freeze_alias(uint32_t id, const Block& blk, size_t from) {
+        check_freeze(id, blk, from);
+        Node* n = resolve(id);
+        bind_value(id, n);   // pending: the next flush copies it into the id's own buffer
+    }
+
+    // in front of a While / If: ids that are views now and are assigned somewhere inside
+    void freeze_for_blocks(const std::vector<const Block*>& inner, const Block& blk, size_t at) {
+        for (const Block* b : inner) {
+            auto it = assigned_.find(b);
+            if (it == assigned_.end()) continue;
+            for (uint32_t id : it->second)
+                if (bind_[id].kind == Binding::ALIAS && info_[id].needed && info_[id].needs_buffer()) freeze_alias(id, blk, at);
+        }
+    }
+    // at the end of a block: ids it leaves behind as views
+    void freeze_at_end(const Block& blk) {
+        auto it = assigned_.find(&blk);
+        if (it == assigned_.end()) return;
+        for (uint32_t id : it->second)
+            if (bind_[id].kind == Binding::ALIAS && info_[id].needed && info_[id].needs_buffer()) freeze_alias(id, blk, blk.cmds.size());
+    }
 
     // ------------------------------------------------------------------ analysis
     void def(uint32_t id, int seg) {
@@ -886,6 +1023,9 @@ class Lowerer {
         if (a->kind == N_PIECE && a->pdim != 0) a = materialize_node(a);
         if (a->nops > opt_.fuse_limit && g_.dag_size(a) > opt_.fuse_limit) a = materialize_node(a);
         int buf = result_buffer(c.res, {V});
+        // `Sum a -> a` (a row of length 1): blocks of the reduce kernels read rows that other blocks already wrote
+        const bool overlaps = depends_on(a, buf);
+        if (overlaps) buf = temp_buffer(V);
         before_write(buf, {c.res});
         std::vector<StoreTask> parts;
         if (a->kind == N_PIECE) {
@@ -966,7 +1106,8 @@ class Lowerer {
             touch(buf, s.pos);
         }
         g_.buf_version[buf]++;
-        bind_own_buffer(c.res, buf, {V});
+        if (overlaps) bind_value(c.res, g_.load(buf, {V}, contiguous_view({V})));
+        else bind_own_buffer(c.res, buf, {V});
         cse[sum_key] = bind_[c.res].node;
         cse[g_.canon(sum_key)] = bind_[c.res].node;
     }
@@ -1015,6 +1156,12 @@ class Lowerer {
         MatOperand mb = matrix_operand(b);
         Shape rs{M, N};
         int buf = result_buffer(c.res, rs);
+        // `DotProduct v w -> v`: the kernels read A and B while other tiles of C are already being written (and a
+        // split k loop zeroes C first), so the product never lands in a buffer it reads from; it goes to a
+        // temporary and the id is bound to that (copied into the id's own buffer at the next flush if it needs one)
+        const bool overlaps = buf == ma.buf || buf == mb.buf;
+        const int own = buf;
+        if (overlaps) buf = temp_buffer(M * N);
         before_write(buf, {c.res});
         Step& s = push_step(Step::GEMM);
         s.gemm.a = ma.buf; s.gemm.b = mb.buf; s.gemm.c = buf;
@@ -1025,7 +1172,11 @@ class Lowerer {
         touch(mb.buf, s.pos);
         touch(buf, s.pos);
         g_.buf_version[buf]++;
-        bind_own_buffer(c.res, buf, rs);
+        if (overlaps) {
+            (void)own;
+            bind_value(c.res, g_.load(buf, rs, contiguous_view(rs)));
+        } else
+            bind_own_buffer(c.res, buf, rs);
         dot_cse_[dot_key] = bind_[c.res].node;
         // operands that were just written to memory are found under their new identity as well
         dot_cse_[{g_.canon(a), g_.canon(b)}] = bind_[c.res].node;
@@ -1063,6 +1214,16 @@ class Lowerer {
         return {n->buf, n->view.offset};
     }
 
+    // What was computed on one side of a control-flow boundary cannot be reused on the other by identity: an
+    // expression evaluated in front of a loop is out of date once the body has changed its operands, and one
+    // evaluated inside a body or a branch may never have been evaluated at all.  Forwarded nodes and remembered
+    // sums / products are only followed while the buffer they were written to keeps its version, so advancing every
+    // version cuts all of those links; ids keep their buffers (refresh_bindings rebinds them at the new version).
+    void forget_computed_values() {
+        for (auto& v : g_.buf_version) v++;
+        refresh_bindings();
+    }
+
     void refresh_bindings() {
         for (auto& b : bind_) {
             if (b.kind == Binding::VALUE && b.node) {
@@ -1075,7 +1236,8 @@ class Lowerer {
 
     // returns true when an EX was reached at this level
     bool lower_block(Block& blk, bool top) {
-        for (auto& c : blk.cmds) {
+        for (size_t ci = 0; ci < blk.cmds.size(); ci++) {
+            auto& c = blk.cmds[ci];
             if (c.op == OP_EX) {
                 flush_pending();
                 if (top) {
@@ -1087,6 +1249,7 @@ class Lowerer {
                 continue;
             }
             if (c.op == OP_WHILE) {
+                freeze_for_blocks({c.block.get()}, blk, ci);
                 flush_pending();
                 auto loc = condition_location(c.a);
                 consume(c.a);
@@ -1098,17 +1261,27 @@ class Lowerer {
                 s.body = std::make_unique<StepBlock>();
                 int first = pos_;
                 StepBlock* body = s.body.get();
+                forget_computed_values();
                 cur_ = body;
+                frames_.push_back({&blk, ci, true});
                 lower_block(*c.block, false);
+                freeze_at_end(*c.block);
+                frames_.pop_back();
                 flush_pending();
                 cur_ = saved;
                 loop_spans_.push_back({first, pos_});
                 auto loc2 = condition_location(c.a);
                 if (loc2 != loc) fail("While condition '" + name(c.a) + "' moves to another buffer inside the loop");
-                refresh_bindings();
+                forget_computed_values();
                 continue;
             }
             if (c.op == OP_IF) {
+                {
+                    std::vector<const Block*> inner;
+                    for (auto& cb : c.conds) inner.push_back(cb.second.get());
+                    if (c.else_block) inner.push_back(c.else_block.get());
+                    freeze_for_blocks(inner, blk, ci);
+                }
                 flush_pending();
                 StepBlock* saved = cur_;
                 std::vector<std::pair<int, int64_t>> locs;
@@ -1129,14 +1302,20 @@ class Lowerer {
                 for (size_t k = 0; k < c.conds.size(); k++) {
                     sp->branches[k].body = std::make_unique<StepBlock>();
                     cur_ = sp->branches[k].body.get();
+                    frames_.push_back({&blk, ci, false});
                     lower_block(*c.conds[k].second, false);
+                    freeze_at_end(*c.conds[k].second);
+                    frames_.pop_back();
                     flush_pending();
                     restore_after_branch(snapshot);
                 }
                 if (c.else_block) {
                     sp->else_body = std::make_unique<StepBlock>();
                     cur_ = sp->else_body.get();
+                    frames_.push_back({&blk, ci, false});
                     lower_block(*c.else_block, false);
+                    freeze_at_end(*c.else_block);
+                    frames_.pop_back();
                     flush_pending();
                     restore_after_branch(snapshot);
                 }
@@ -1164,7 +1343,7 @@ class Lowerer {
             } else
                 b = s;
         }
-        refresh_bindings();
+        forget_computed_values();
     }
 
     void finalize_results() {

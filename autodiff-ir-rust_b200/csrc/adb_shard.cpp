@@ -154,30 +154,116 @@ struct Sharder {
         fail(why);
     }
 
+    // Where control flow joins, the tags must hold whichever path ran: a loop body runs zero, one or many times, a
+    // branch is taken or not.  A partial value is the one state that an AllReduce placed by a single walk gets wrong
+    // there (inside a loop it would be summed again on every iteration; behind a branch that was not taken the
+    // value would still be partial, or be summed although it was already complete).  So partial values do not cross
+    // block boundaries: every partial id that a block reads or assigns is completed in front of the block, and every
+    // id that a block leaves partial is completed at its end when anything can still read it (the next iteration
+    // before it is assigned again, code outside the block, or the host).
+    struct BlockRefs {
+        std::map<uint32_t, int> reads;   // id -> reading commands inside (conditions and nested blocks included)
+        std::set<uint32_t> defs;         // ids assigned inside
+        std::set<uint32_t> exposed;      // ids read before the block itself has certainly assigned them
+    };
+    void gather(const Block& b, BlockRefs& out) {
+        std::set<uint32_t> defined;
+        auto rd = [&](uint32_t id) {
+            out.reads[id]++;
+            if (!defined.count(id)) out.exposed.insert(id);
+        };
+        for (auto& c : b.cmds) {
+            if (c.op == OP_WHILE || c.op == OP_IF) {
+                BlockRefs in;
+                if (c.op == OP_WHILE) {
+                    rd(c.a);
+                    gather(*c.block, in);
+                    in.reads[c.a]++;   // the condition is read again after every pass
+                    in.exposed.insert(c.a);
+                } else {
+                    for (auto& cb : c.conds) rd(cb.first);
+                    for (auto& cb : c.conds) gather(*cb.second, in);
+                    if (c.else_block) gather(*c.else_block, in);
+                }
+                for (auto& kv : in.reads) out.reads[kv.first] += kv.second;
+                for (auto id : in.exposed)
+                    if (!defined.count(id)) out.exposed.insert(id);
+                out.defs.insert(in.defs.begin(), in.defs.end());
+                continue;
+            }
+            if (!has_result(c.op) || !needed[c.res]) continue;
+            uint32_t r[2];
+            int n;
+            reads(c, r, n);
+            for (int k = 0; k < n; k++) rd(r[k]);
+            out.defs.insert(c.res);
+            defined.insert(c.res);
+        }
+    }
+    std::map<uint32_t, int> total_reads_;
+    bool have_totals_ = false;
+    void complete_before(const BlockRefs& br, std::vector<Cmd>& out) {
+        for (auto& kv : br.reads) resolve_partial(kv.first, out);
+        for (auto id : br.defs) resolve_partial(id, out);
+    }
+    void complete_at_end(Block& inner, const BlockRefs& br) {
+        if (!have_totals_) {
+            BlockRefs all;
+            gather(prog.main, all);
+            total_reads_ = all.reads;
+            have_totals_ = true;
+        }
+        for (auto id : br.defs) {
+            if (info[id].tag != T_PART) continue;
+            auto in = br.reads.find(id);
+            auto tot = total_reads_.find(id);
+            const int inside = in == br.reads.end() ? 0 : in->second, total = tot == total_reads_.end() ? 0 : tot->second;
+            if (br.exposed.count(id) || total > inside || is_dep[id]) {
+                inner.cmds.push_back(make_allreduce(id));
+                info[id].tag = T_REP;
+                prog.n_cmds++;
+            }
+        }
+    }
+
     void block(Block& b) {
         std::vector<Cmd> out;
         out.reserve(b.cmds.size() + 8);
         for (auto& c : b.cmds) {
             if (c.op == OP_WHILE) {
                 if (info[c.a].tag == T_SHARD) fail("loop condition '" + name(c.a) + "' is sharded");
-                resolve_partial(c.a, out);
+                BlockRefs br;
+                gather(*c.block, br);
+                br.reads[c.a]++;
+                br.exposed.insert(c.a);
+                complete_before(br, out);
                 block(*c.block);
-                // the condition is recomputed inside the body into the same id
-                if (info[c.a].tag == T_PART) {
-                    c.block->cmds.push_back(make_allreduce(c.a));
-                    info[c.a].tag = T_REP;
-                    prog.n_cmds++;
-                }
+                // (the condition is recomputed inside the body into the same id: it counts as read by the next pass)
+                complete_at_end(*c.block, br);
                 out.push_back(std::move(c));
                 continue;
             }
             if (c.op == OP_IF) {
+                BlockRefs all;
                 for (auto& cb : c.conds) {
                     if (info[cb.first].tag == T_SHARD) fail("condition '" + name(cb.first) + "' is sharded");
-                    resolve_partial(cb.first, out);
+                    all.reads[cb.first]++;
+                    gather(*cb.second, all);
                 }
-                for (auto& cb : c.conds) block(*cb.second);
-                if (c.else_block) block(*c.else_block);
+                if (c.else_block) gather(*c.else_block, all);
+                complete_before(all, out);
+                for (auto& cb : c.conds) {
+                    BlockRefs br;
+                    gather(*cb.second, br);
+                    block(*cb.second);
+                    complete_at_end(*cb.second, br);
+                }
+                if (c.else_block) {
+                    BlockRefs br;
+                    gather(*c.else_block, br);
+                    block(*c.else_block);
+                    complete_at_end(*c.else_block, br);
+                }
                 out.push_back(std::move(c));
                 continue;
             }
@@ -384,8 +470,10 @@ struct Sharder {
                 if (!ok) fail("View of '" + name(c.a) + "' cuts through the sharded axis");
                 c.dims[nd] = new_ext / world;
                 set(c.res, T_SHARD, nd, g, c);
-            } else
+            } else {
                 set(c.res, a.tag, 0, g, c);
+                if (a.tag == T_CONST) info[c.res].ldims = g;   // only uncut constants get this far: local = global shape
+            }
             return;
         }
         case OP_INDEX: {
@@ -396,8 +484,10 @@ struct Sharder {
             if (a.tag == T_SHARD) {
                 if (int(c.dim) == a.axis) fail("Index into the sharded axis of '" + name(c.a) + "'");
                 set(c.res, T_SHARD, a.axis - (int(c.dim) < a.axis ? 1 : 0), g, c);
-            } else
+            } else {
                 set(c.res, a.tag, 0, g, c);
+                if (a.tag == T_CONST) info[c.res].ldims = g;
+            }
             return;
         }
         case OP_PERMUTE: {
@@ -410,6 +500,7 @@ struct Sharder {
                 if (int(c.perm[i]) == a.axis) nd = int(i);
             }
             set(c.res, a.tag, a.tag == T_SHARD ? nd : 0, g, c);
+            if (a.tag == T_CONST) info[c.res].ldims = g;
             return;
         }
         case OP_BROADCAST: {
@@ -427,8 +518,10 @@ struct Sharder {
                 c.count = uint64_t(batch / world);
                 pending_origin_ = ord;
                 set(c.res, T_SHARD, int(c.dim), g, c);
-            } else
+            } else {
                 set(c.res, a.tag, 0, g, c);
+                if (a.tag == T_CONST) info[c.res].ldims = g;
+            }
             return;
         }
         case OP_CONCAT: {

@@ -175,3 +175,124 @@ def build_loop(seed: int):
         ad.execute()
         return {k: v.val().get() for k, v in st.items()}
     return prog
+
+
+def build_raw(seed: int):
+    """A random program written directly as IR commands (no frontend in between): ids are reused as results, op-assigns
+    hit ids that are views / permutes of other tensors, views are created inside branches, branches are not taken and
+    loops run zero times.  Square [n, n] tensors of small integers and a few additions / multiplications per path, so
+    every value is exact in fp32 and device and oracle must agree bit for bit.
+
+    Returns `prog(dev) -> {id: ValueData}`.  Only ids that are certainly defined are read: an id first assigned inside
+    a block is local to that block."""
+    IRP = adb.ir.IRProcedure
+
+    def prog(dev):
+        rng = np.random.default_rng(seed)
+        n = int(rng.integers(2, 5))
+        counter = [0]
+
+        def fresh(prefix="v"):
+            counter[0] += 1
+            return f"{prefix}{counter[0]}"
+
+        main = IRP("main")
+        mats = []
+        for _ in range(3):
+            id_ = fresh()
+            main.push(("CreateMat", rng.integers(-1, 3, n * n).astype(np.float32), [n, n], id_))
+            mats.append(id_)
+        one = fresh("k")
+        main.push(("CreateConstant", -1.0, one, [1]))
+        budget = {"mul": 3}   # multiplications per program: keeps values small enough to stay exact
+        # ids that an id may be a view of, transitively (never shrinks: a view command whose result is one of its own
+        # sources would make the alias chain cyclic, which no device can evaluate)
+        anc: dict = {}
+
+        def may_alias(res, a):
+            return res == a or res in anc.get(a, ())
+
+        def note_alias(res, a):
+            new = set(anc.get(a, ())) | {a}
+            anc.setdefault(res, set()).update(new)
+            for x, s in anc.items():
+                if res in s:
+                    s.update(new)
+
+        def emit(block, pool, depth):
+            """Appends random commands to `block`; `pool` = ids (shape [n, n]) that are defined at this point."""
+            pool = list(pool)
+            for _ in range(int(rng.integers(2, 7))):
+                kind = int(rng.integers(0, 10))
+                a = pool[int(rng.integers(0, len(pool)))]
+                b = pool[int(rng.integers(0, len(pool)))]
+                # results go to a fresh id or overwrite an existing one
+                res = fresh() if rng.random() < 0.5 else pool[int(rng.integers(0, len(pool)))]
+                if kind == 0:
+                    block.push(("ElwAdd", a, b, res))
+                elif kind == 1:
+                    if budget["mul"] <= 0:
+                        continue
+                    budget["mul"] -= 1
+                    block.push(("ElwMultiply", a, b, res))
+                elif kind == 2:
+                    block.push(("ElwAddEq", a, b))
+                    res = a
+                elif kind == 3:
+                    if budget["mul"] <= 0:
+                        continue
+                    budget["mul"] -= 1
+                    block.push(("ElwMultiplyEq", a, b))
+                    res = a
+                elif kind == 4:
+                    if may_alias(res, a):
+                        continue
+                    note_alias(res, a)
+                    block.push(("Permute", a, [1, 0], res))
+                elif kind == 5:
+                    if may_alias(res, a):
+                        continue
+                    note_alias(res, a)
+                    block.push(("View", a, [n, n], res))
+                elif kind == 6:
+                    block.push(("Contigious", a, res))
+                elif kind == 7:
+                    if budget["mul"] <= 0:
+                        continue
+                    budget["mul"] -= 1
+                    block.push(("DotProduct", a, b, res))
+                elif kind == 8 and depth < 2:
+                    # If on a flag that is 0 or 1 (optionally with an else block)
+                    flag = fresh("f")
+                    block.push(("CreateMat", np.array([float(rng.integers(0, 2))], np.float32), [1], flag))
+                    then = IRP(fresh("blk"))
+                    emit(then, pool, depth + 1)
+                    other = None
+                    if rng.random() < 0.4:
+                        other = IRP(fresh("blk"))
+                        emit(other, pool, depth + 1)
+                    block.push(("If", [(flag, then)], other))
+                    continue
+                elif kind == 9 and depth < 2:
+                    # While on a counter that starts at 0 .. 2 and is decremented at the end of the body
+                    cnt = fresh("c")
+                    block.push(("CreateMat", np.array([float(rng.integers(0, 3))], np.float32), [1], cnt))
+                    body = IRP(fresh("blk"))
+                    saved = budget["mul"]
+                    budget["mul"] = min(budget["mul"], 1)
+                    emit(body, pool, depth + 1)
+                    budget["mul"] = max(0, saved - 1)
+                    body.push(("ElwAddEq", cnt, one))
+                    block.push(("While", cnt, body))
+                    continue
+                else:
+                    continue
+                if res not in pool:
+                    pool.append(res)
+            return pool
+
+        pool = emit(main, mats, 0)
+        dep = list(dict.fromkeys(pool[-6:] + mats))
+        dev.execute(main, dep)
+        return {d: dev.get_tensor(d) for d in dep}
+    return prog

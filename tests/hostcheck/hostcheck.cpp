@@ -25,7 +25,8 @@
 // Invariants every plan must satisfy, whatever passes rewrote its step list:
 //   1. step positions increase in execution order (nested blocks lie between their parent and its successor);
 //   2. a buffer is alive at every step that touches it (external and whole-program buffers always are);
-//   3. buffers that are alive at the same time do not overlap in the arena.
+//   3. buffers that are alive at the same time do not overlap in the arena;
+//   5. a dot product never writes into one of its own operands.
 // Returns an empty string or a description of the first violation.
 static void step_buffers(const adb::Plan& plan, const adb::Step& s, std::vector<int>& bufs) {
     using adb::Step;
@@ -54,6 +55,8 @@ static std::string check_block(const adb::Plan& plan, const adb::StepBlock& blk,
         last_pos = s.pos;
         if ((s.kind == adb::Step::ELW || s.kind == adb::Step::REDUCE) && plan.kernels[size_t(s.kernel)].dead)
             return "step at " + std::to_string(s.pos) + " runs a kernel that was marked dead";
+        if (s.kind == adb::Step::GEMM && (s.gemm.c == s.gemm.a || s.gemm.c == s.gemm.b))
+            return "dot product at " + std::to_string(s.pos) + " writes into one of its operands";
         step_buffers(plan, s, bufs);
         for (int b : bufs) {
             if (b < 0 || size_t(b) >= plan.bufs.size()) return "step at " + std::to_string(s.pos) + " names buffer " + std::to_string(b);
@@ -196,6 +199,7 @@ int main(int argc, char** argv) {
                 }
             } catch (const std::exception& e) {
                 rejected++;
+                if (argc == 5) std::printf("rejected: %s\n", e.what());
             }
         }
     }

@@ -170,14 +170,15 @@ struct PlanInterp {
             const float* A = ptr(g.a, g.a_off);
             const float* B = ptr(g.b, g.b_off);
             float* C = ptr(g.c, g.c_off);
-            std::vector<float> res(size_t(g.M * g.N));
+            // C is written in place, element by element, and zeroed first as the split-k path of the GPU kernel does:
+            // a plan whose product lands in one of its own operands shows up as a wrong result here too
+            for (int64_t i = 0; i < g.M * g.N; i++) C[i] = 0.f;
             for (int64_t m = 0; m < g.M; m++)
                 for (int64_t n = 0; n < g.N; n++) {
                     double acc = 0;
                     for (int64_t kk = 0; kk < g.K; kk++) acc += double(A[m * g.a_rs + kk * g.a_cs]) * double(B[kk * g.b_rs + n * g.b_cs]);
-                    res[size_t(m * g.N + n)] = float(acc);
+                    C[m * g.N + n] = float(acc);
                 }
-            std::memcpy(C, res.data(), res.size() * 4);
             break;
         }
         case Step::UPLOAD: {

@@ -162,3 +162,111 @@ def test_random_loop_programs(hostcheck, tmp_path):
         for flags in (0, 1, 2):
             _compare(_interpret(hostcheck, tmp_path, dev.blobs[-1], flags, f"loop{seed}_{flags}"), by_id, 2e-4)
     assert ran >= 30
+
+
+REFUSAL = "is a view when control flow joins"
+
+
+def _interpret_or_refused(binary, tmp_path, blob, flags, tag):
+    """Interpreted results, or None when the lowering refused the program as path-dependent (a view that one path
+    rebinds while another path changes its source)."""
+    f = tmp_path / f"{tag}.adir"
+    f.write_bytes(blob)
+    r = subprocess.run([binary, str(flags | 8), "1", "0", str(f)], capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-3000:]
+    if "rejected:" in r.stdout:
+        assert REFUSAL in r.stdout, r.stdout
+        return None
+    assert "executed=1" in r.stdout, r.stdout
+    return _read_results(str(f) + ".out")
+
+
+def test_raw_ir_programs_with_reused_ids_and_views_across_blocks(hostcheck, tmp_path):
+    """Programs written as IR commands directly: result ids reused, op-assigns on views, views created inside
+    branches, branches not taken, loops that run zero times, products written onto their own operands.  Every
+    program either interprets to exactly the oracle's result or is refused with the one documented reason."""
+    refused = 0
+    seeds = range(120)
+    for seed in seeds:
+        dev = _Both()
+        kept = fuzz_programs.build_raw(seed)(dev)
+        for flags in (0, 2):
+            got = _interpret_or_refused(hostcheck, tmp_path, dev.blobs[-1], flags, f"raw{seed}_{flags}")
+            if got is None:
+                refused += 1
+                break
+            _compare(got, kept, 0.0)
+    assert refused <= len(seeds) // 4, refused
+
+
+def _raw(cmds, dep):
+    main = adb.ir.IRProcedure("main")
+    for c in cmds:
+        main.push(c)
+    return main, dep
+
+
+def _block(*cmds):
+    b = adb.ir.IRProcedure("blk")
+    for c in cmds:
+        b.push(c)
+    return b
+
+
+M4 = np.arange(16, dtype=np.float32).reshape(4, 4) - 5.0
+
+
+@pytest.mark.parametrize("count", [0, 1, 3])
+def test_op_assign_on_a_view_inside_a_loop_is_carried_around(hostcheck, tmp_path, count):
+    """v5 = Permute(v4); While c {v5 += v5; c += -1}: v5 doubles on every pass (and stays v4^T when the loop never runs)."""
+    proc, dep = _raw([("CreateMat", M4, [4, 4], "v4"), ("CreateMat", np.array([count], np.float32), [1], "c"),
+                      ("CreateConstant", -1.0, "k", [1]), ("Permute", "v4", [1, 0], "v5"),
+                      ("While", "c", _block(("ElwAddEq", "v5", "v5"), ("ElwAddEq", "c", "k")))], ["v5", "v4"])
+    dev = _Both()
+    dev.execute(proc, dep)
+    kept = {d: dev.get_tensor(d) for d in dep}
+    assert np.array_equal(kept["v5"].numpy().reshape(4, 4), M4.T * 2.0 ** count)
+    for flags in (0, 1, 2):
+        _compare(_interpret(hostcheck, tmp_path, dev.blobs[-1], flags, f"loopview{flags}"), kept, 0.0)
+
+
+@pytest.mark.parametrize("flag", [0.0, 1.0])
+def test_views_and_branches(hostcheck, tmp_path, flag):
+    """An op-assign on a view inside a branch that may not run, and a branch that turns a tensor into a view."""
+    proc, dep = _raw([("CreateMat", M4, [4, 4], "v4"), ("CreateMat", M4 * 2, [4, 4], "v2"),
+                      ("CreateMat", np.array([flag], np.float32), [1], "f"),
+                      ("View", "v4", [4, 4], "v5"), ("ElwAdd", "v2", "v2", "v6"),
+                      ("If", [("f", _block(("ElwMultiplyEq", "v5", "v5"), ("Permute", "v2", [1, 0], "v6")))], None),
+                      ("ElwAdd", "v5", "v6", "out")], ["out", "v5", "v6"])
+    dev = _Both()
+    dev.execute(proc, dep)
+    kept = {d: dev.get_tensor(d) for d in dep}
+    for flags in (0, 1, 2):
+        _compare(_interpret(hostcheck, tmp_path, dev.blobs[-1], flags, f"ifview{flags}"), kept, 0.0)
+
+
+def test_dot_product_onto_its_own_operand(hostcheck, tmp_path):
+    """`DotProduct v w -> v` at top level, in a branch and in a loop: the plan never lets a product land in a buffer
+    it reads (hostcheck's plan invariant) and the results match."""
+    W = (np.arange(16, dtype=np.float32).reshape(4, 4) % 3) - 1.0
+    proc, dep = _raw([("CreateMat", M4, [4, 4], "v"), ("CreateMat", W, [4, 4], "w"),
+                      ("CreateMat", np.array([1.0], np.float32), [1], "f"), ("CreateMat", np.array([2.0], np.float32), [1], "c"),
+                      ("CreateConstant", -1.0, "k", [1]),
+                      ("DotProduct", "v", "w", "v"),
+                      ("If", [("f", _block(("DotProduct", "w", "v", "v")))], None),
+                      ("While", "c", _block(("DotProduct", "v", "w", "v"), ("ElwAddEq", "c", "k")))], ["v"])
+    dev = _Both()
+    dev.execute(proc, dep)
+    kept = {d: dev.get_tensor(d) for d in dep}
+    for flags in (0, 1, 2):
+        _compare(_interpret(hostcheck, tmp_path, dev.blobs[-1], flags, f"dotself{flags}"), kept, 0.0)
+
+
+def test_path_dependent_view_is_refused(hostcheck, tmp_path):
+    """`If f {v1 = Permute(v3)}; v3 += v3; read v1`: whether v1 follows v3 depends on f; the lowering says so."""
+    proc, dep = _raw([("CreateMat", M4, [4, 4], "v1"), ("CreateMat", M4 * 2, [4, 4], "v3"),
+                      ("CreateMat", np.array([1.0], np.float32), [1], "f"),
+                      ("If", [("f", _block(("Permute", "v3", [1, 0], "v1")))], None),
+                      ("ElwAddEq", "v3", "v3"), ("ElwAdd", "v1", "v3", "out")], ["out"])
+    blob = adb.ir.serialize(proc, dep, inline_limit=1 << 40)[0]
+    assert _interpret_or_refused(hostcheck, tmp_path, blob, 0, "pathdep") is None

@@ -133,3 +133,138 @@ def test_named_batch_tensors_resolve_a_batch_that_equals_a_layer_width(tmp_path,
             ref = v.numpy()
             err = np.abs(got[k] - ref).max() / max(np.abs(ref).max(), 1e-30)
             assert err < 1e-5, (r, k, err)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Raw IR through the rewrite, ranks simulated by threads: each rank runs its rewritten program on an oracle of its own
+# and the AllReduce hooks meet at a barrier.  (The oracle runs outside the GIL; only the hooks take it.)
+def _run_ranks(proc, dep, world, batch):
+    import threading
+    from oracle.oracle import OracleDevice
+    blob, keep = adb.ir.serialize(proc, dep, inline_limit=1 << 40)
+    barrier = threading.Barrier(world)
+    slots = [None] * world
+    results = [None] * world
+    errors = []
+
+    def run(rank):
+        def allreduce(arr):
+            slots[rank] = arr.copy()
+            barrier.wait(timeout=60)
+            total = np.sum(np.stack(slots), axis=0, dtype=np.float32)
+            barrier.wait(timeout=60)
+            arr[:] = total
+        try:
+            dev = OracleDevice(allreduce=allreduce)
+            dev.execute_blob(adb.devices.shard_ir(blob, rank, world, batch))
+            results[rank] = {d: dev.get_tensor(d).numpy() for d in dep}
+        except Exception as e:      # noqa: BLE001 - reported below, and the other ranks must not wait forever
+            errors.append(e)
+            barrier.abort()
+
+    threads = [threading.Thread(target=run, args=(r,)) for r in range(world)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    one = OracleDevice()
+    one.execute_blob(blob)
+    want = {d: one.get_tensor(d).numpy() for d in dep}
+    del keep
+    return want, results
+
+
+def _close(want, results, tol=1e-5):
+    for got in results:
+        for k, ref in want.items():
+            err = np.abs(got[k] - ref).max() / max(np.abs(ref).max(), 1e-30)
+            assert err < tol, (k, err, got[k], ref)
+
+
+def _loop_carried_partial(iters):
+    """g is replicated when the loop starts and a per-rank partial sum when the body ends: the next pass reads it."""
+    B, F = 8, 3
+    rng = np.random.default_rng(11)
+    P = adb.ir.IRProcedure
+    main = P("main")
+    main.push(("CreateMat", (rng.standard_normal(B * F) / B).astype(np.float32), [B, F], "x"))
+    main.push(("CreateMat", rng.standard_normal(F).astype(np.float32), [F], "g"))
+    main.push(("CreateMat", np.zeros(F, np.float32), [F], "acc"))
+    main.push(("CreateMat", np.array([float(iters)], np.float32), [1], "cnt"))
+    main.push(("CreateConstant", -1.0, "k", [1]))
+    main.push(("Permute", "x", [1, 0], "xt"))
+    body = P("body")
+    body.push(("Exp2", "g", "y"))
+    body.push(("ElwAddEq", "acc", "y"))
+    body.push(("Sum", "xt", "g"))
+    body.push(("ElwAddEq", "cnt", "k"))
+    main.push(("While", "cnt", body))
+    return main, ["acc"], B      # (g is not kept: a kept partial value is completed where it is produced anyway)
+
+
+@pytest.mark.parametrize("iters", [0, 1, 3])
+def test_partial_value_carried_around_a_loop_is_completed_every_pass(iters):
+    proc, dep, B = _loop_carried_partial(iters)
+    want, results = _run_ranks(proc, dep, 2, B)
+    _close(want, results)
+
+
+@pytest.mark.parametrize("flag", [0.0, 1.0])
+def test_partial_value_from_a_branch_that_may_not_run(flag):
+    """`If f {g = Sum(xt)}; out = Exp2(g)`: behind the branch g must be complete whether or not it ran."""
+    B, F = 8, 3
+    rng = np.random.default_rng(12)
+    P = adb.ir.IRProcedure
+    main = P("main")
+    main.push(("CreateMat", (rng.standard_normal(B * F) / B).astype(np.float32), [B, F], "x"))
+    main.push(("CreateMat", rng.standard_normal(F).astype(np.float32), [F], "g"))
+    main.push(("CreateMat", np.array([flag], np.float32), [1], "f"))
+    main.push(("Permute", "x", [1, 0], "xt"))
+    then = P("then")
+    then.push(("Sum", "xt", "g"))
+    main.push(("If", [("f", then)], None))
+    main.push(("Exp2", "g", "out"))
+    want, results = _run_ranks(main, ["out"], 2, B)
+    _close(want, results)
+
+
+def test_partial_value_made_before_a_loop_is_not_summed_on_every_pass():
+    """g = Sum(xt) in front of the loop, read inside: the AllReduce belongs in front of the loop, once."""
+    B, F = 8, 3
+    rng = np.random.default_rng(13)
+    P = adb.ir.IRProcedure
+    main = P("main")
+    main.push(("CreateMat", (rng.standard_normal(B * F) / B).astype(np.float32), [B, F], "x"))
+    main.push(("CreateMat", np.zeros(F, np.float32), [F], "acc"))
+    main.push(("CreateMat", np.array([3.0], np.float32), [1], "cnt"))
+    main.push(("CreateConstant", -1.0, "k", [1]))
+    main.push(("Permute", "x", [1, 0], "xt"))
+    main.push(("Sum", "xt", "g"))
+    body = P("body")
+    body.push(("Exp2", "g", "y"))
+    body.push(("ElwAddEq", "acc", "y"))
+    body.push(("ElwAddEq", "cnt", "k"))
+    main.push(("While", "cnt", body))
+    want, results = _run_ranks(main, ["acc"], 2, B)
+    _close(want, results)
+
+
+def test_reshaped_constant_keeps_its_shape_under_the_rewrite():
+    """CreateConstant c[F]; View -> [F, 1]; Broadcast -> [F, 4]; multiplied with a parameter [F, 4]: nothing here has a
+    batch dimension, so the rewrite must leave it alone (and not refuse it)."""
+    B, F = 8, 3
+    rng = np.random.default_rng(14)
+    P = adb.ir.IRProcedure
+    main = P("main")
+    main.push(("CreateMat", rng.standard_normal(B * F).astype(np.float32), [B, F], "x"))
+    main.push(("CreateMat", rng.standard_normal(F * 4).astype(np.float32), [F, 4], "w"))
+    main.push(("CreateConstant", 0.5, "cv", [F]))
+    main.push(("View", "cv", [F, 1], "cv2"))
+    main.push(("Broadcast", "cv2", 1, 4, "cv3"))
+    main.push(("ElwMultiply", "cv3", "w", "ws"))
+    main.push(("DotProduct", "x", "ws", "y"))       # [B, 4], sharded
+    main.push(("Permute", "y", [1, 0], "yt"))
+    main.push(("Sum", "yt", "s"))                   # partial -> completed because it is kept
+    want, results = _run_ranks(main, ["s", "ws"], 2, B)
+    _close(want, results)
