@@ -52,6 +52,49 @@ def normal(seed: int, stream: int, n: int, std: float = 1.0, start: int = 0) -> 
     return (z * std).astype(np.float32)
 
 
+# A second generator for tensors too large to draw on the host in reasonable time (the full-size benchmark batch):
+# integer hashing only, so the same few lines run on numpy arrays and on torch tensors (CPU or CUDA) and give the
+# same bits everywhere; any rank can produce any row range of a tensor.  Element i of (seed, stream) takes three
+# 64-bit words  mix64(base + GOLDEN * (3 i + j + 1)),  j = 0..2  (mix64 = the splitmix64 finaliser); their twelve 16-bit
+# fields are summed (Irwin-Hall), which is exact in integers:  z = (sum - 12 * 32767.5) / 65536  has mean 0, variance
+# 1 - 2^-32 and the bell shape of a sum of twelve uniforms (support +-6).  It stands in for N(0, 1).
+GOLDEN = 0x9E3779B97F4A7C15
+_M1, _M2 = 0xBF58476D1CE4E5B9, 0x94D049BB133111EB
+
+
+def _mix64(z: np.ndarray) -> np.ndarray:
+    z = (z ^ (z >> np.uint64(30))) * np.uint64(_M1)
+    z = (z ^ (z >> np.uint64(27))) * np.uint64(_M2)
+    return z ^ (z >> np.uint64(31))
+
+
+def hash_base(seed: int, stream: int) -> int:
+    """Start of the counter space of (seed, stream) as a Python int in [0, 2^64)."""
+    with np.errstate(over="ignore"):
+        a = _mix64(np.array([(seed * GOLDEN + 0x1234567) % (1 << 64)], np.uint64))
+        b = _mix64(np.array([(int(a[0]) ^ ((stream + 1) * _M2)) % (1 << 64)], np.uint64))
+    return int(b[0])
+
+
+def hash_normal(seed: int, stream: int, n: int, std: float = 1.0, start: int = 0) -> np.ndarray:
+    """~N(0, std^2) as float32 (Irwin-Hall of twelve 16-bit uniforms); element i depends only on
+    (seed, stream, start + i).  Bit-identical to `bench.py`'s torch version of the same arithmetic."""
+    base = np.uint64(hash_base(seed, stream))
+    out = np.empty(n, np.float32)
+    step = 1 << 22
+    with np.errstate(over="ignore"):
+        for lo in range(0, n, step):
+            cnt = min(step, n - lo)
+            i = np.arange(start + lo, start + lo + cnt, dtype=np.uint64) * np.uint64(3)
+            total = np.zeros(cnt, np.int64)
+            for j in range(3):
+                w = _mix64(base + np.uint64(GOLDEN) * (i + np.uint64(j + 1)))
+                for f in range(4):
+                    total += ((w >> np.uint64(16 * f)) & np.uint64(0xFFFF)).astype(np.int64)
+            out[lo:lo + cnt] = ((total - 393210).astype(np.float32) * f32(1.0 / 65536.0)) * f32(std)
+    return out
+
+
 def _kept(names_values):
     return {k: v.get() for k, v in names_values.items()}
 

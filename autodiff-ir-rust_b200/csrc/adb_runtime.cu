@@ -910,6 +910,10 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
     }
 
     Executor ex(d, cp);
+    struct EventGuard {   // events go back to the pool however this function is left
+        Executor& e;
+        ~EventGuard() { e.release_events(); }
+    } event_guard{ex};
     d->exit_requested = false;
     d->upload_events.clear();
     d->prof.clear();
@@ -943,7 +947,6 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
     d->gemm.tc_launches = ex.tc_;  // graph replays launch the kernel without passing through gemm_launch
     if (int gs = gemm_check_status(d->gemm, d->stream)) {
         d->err = "tensor-core dot product gave up on a bounded wait (code " + std::to_string(gs) + "); results are invalid";
-        ex.release_events();
         return ADB_ERR_CUDA;
     }
     float ms_run = 0, ms_rb = 0;
@@ -990,7 +993,6 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
             }
         d->prof.clear();
     }
-    ex.release_events();
     (void)t_begin;
     return ADB_OK;
 }
@@ -1012,6 +1014,8 @@ static std::vector<std::string> config_shard_ids(const adb_config* cfg) {
     return ids;
 }
 
+void adb_destroy(adb_device* d);
+
 adb_status adb_create(const adb_config* cfg, adb_device** out) {
     if (!out) return ADB_ERR_INVALID;
     *out = nullptr;
@@ -1031,6 +1035,11 @@ adb_status adb_create(const adb_config* cfg, adb_device** out) {
         d->shard_ids = config_shard_ids(cfg);
     }
     if (d->ordinal < 0 || d->ordinal >= count) return ADB_ERR_INVALID;
+    // every failure past this point goes through adb_destroy, which releases whatever was created so far
+    auto give_up = [&](adb_status st) {
+        adb_destroy(d.release());
+        return st;
+    };
     try {
         ck(cudaSetDevice(d->ordinal), "cudaSetDevice");
         cudaDeviceProp prop;
@@ -1038,7 +1047,7 @@ adb_status adb_create(const adb_config* cfg, adb_device** out) {
         d->sm_count = prop.multiProcessorCount;
         if (prop.major < 10) {
             // the generated kernels and the tcgen05 GEMM are sm_100a only; no fallback path exists
-            return ADB_ERR_UNSUPPORTED;
+            return give_up(ADB_ERR_UNSUPPORTED);
         }
         ck(cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking), "cudaStreamCreate");
         ck(cudaStreamCreateWithFlags(&d->copy_stream, cudaStreamNonBlocking), "cudaStreamCreate");
@@ -1051,19 +1060,22 @@ adb_status adb_create(const adb_config* cfg, adb_device** out) {
         std::string gerr;
         if (!gemm_init(d->gemm, d->sm_count, gerr)) throw CudaFail{gerr};
         if (d->world > 1) {
-            if (!cfg->nccl_unique_id) return ADB_ERR_INVALID;
+            if (!cfg->nccl_unique_id) return give_up(ADB_ERR_INVALID);
             std::string nerr;
-            if (!g_nccl.load(nerr)) { return ADB_ERR_NCCL; }
+            if (!g_nccl.load(nerr)) return give_up(ADB_ERR_NCCL);
             ncclUniqueId uid;
             static_assert(sizeof(uid) == 128, "ncclUniqueId is 128 bytes");
             std::memcpy(&uid, cfg->nccl_unique_id, 128);
             // collectives that overlap dot products get 8 SMs (Executor::COMM_SMS): keep NCCL's kernels that small
             if (d->flags & ADB_FLAG_COMM_STREAM) setenv("NCCL_MAX_CTAS", "8", 0);
-            if (g_nccl.CommInitRank(&d->nccl_comm, d->world, uid, d->rank) != ncclSuccess) return ADB_ERR_NCCL;
+            if (g_nccl.CommInitRank(&d->nccl_comm, d->world, uid, d->rank) != ncclSuccess) {
+                d->nccl_comm = nullptr;
+                return give_up(ADB_ERR_NCCL);
+            }
         }
     } catch (CudaFail& f) {
         std::fprintf(stderr, "adb_create: %s\n", f.msg.c_str());
-        return ADB_ERR_CUDA;
+        return give_up(ADB_ERR_CUDA);
     }
     *out = d.release();
     return ADB_OK;
@@ -1233,6 +1245,13 @@ adb_status adb_shard_ir(const uint8_t* blob, size_t nbytes, const adb_config* cf
         set_err(err, err_cap, e.what());
         return ADB_ERR_INVALID;
     }
+}
+
+adb_status adb_inject_dot_status(adb_device* d, int code) {
+    if (!d || !d->gemm.status) return ADB_ERR_INVALID;
+    if (cudaSetDevice(d->ordinal) != cudaSuccess) return ADB_ERR_CUDA;
+    if (cudaMemcpyAsync(d->gemm.status, &code, sizeof(int), cudaMemcpyHostToDevice, d->stream) != cudaSuccess) return ADB_ERR_CUDA;
+    return cudaStreamSynchronize(d->stream) == cudaSuccess ? ADB_OK : ADB_ERR_CUDA;
 }
 
 adb_status adb_nccl_unique_id(void* out128) {

@@ -29,7 +29,7 @@ FLAG_NO_GRAPHS, FLAG_NO_FUSION, FLAG_SIMT_DOT, FLAG_PROFILE, FLAG_COMM_STREAM, F
 
 EXPORTS = ["adb_create", "adb_destroy", "adb_execute", "adb_get_tensor", "adb_get_tensor_device",
            "adb_dot_prod_shape", "adb_last_error", "adb_get_stats", "adb_dump_plan", "adb_lower_check",
-           "adb_shard_ir", "adb_nccl_unique_id", "adb_version", "adb_row_sum_noalloc"]
+           "adb_shard_ir", "adb_nccl_unique_id", "adb_version", "adb_row_sum_noalloc", "adb_inject_dot_status"]
 
 NOALLOC_MAX_PARTIALS = 1 << 20
 
@@ -110,6 +110,8 @@ def load_library():
     L.adb_row_sum_noalloc.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_void_p,
                                       ctypes.c_char_p, ctypes.c_size_t]
     L.adb_row_sum_noalloc.restype = ctypes.c_int
+    L.adb_inject_dot_status.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    L.adb_inject_dot_status.restype = ctypes.c_int
     _lib = L
     return L
 
@@ -261,6 +263,13 @@ class B200:
         s = AdbStats()
         self._L.adb_get_stats(self._h, ctypes.byref(s))
         return s.as_dict()
+
+    def inject_dot_status(self, code: int) -> None:
+        """Diagnostic: makes the next execute that runs a tensor-core dot product fail as if a bounded wait inside the
+        kernel had run out (`adb_inject_dot_status`)."""
+        rc = self._L.adb_inject_dot_status(self._h, int(code))
+        if rc != ADB_OK:
+            raise AdbError(rc, "adb_inject_dot_status failed")
 
     def dump_plan(self) -> str:
         n = self._L.adb_dump_plan(self._h, None, 0)

@@ -175,6 +175,12 @@ adb_status adb_lower_check(const uint8_t *blob, size_t nbytes, const adb_config 
 adb_status adb_shard_ir(const uint8_t *blob, size_t nbytes, const adb_config *cfg, uint8_t *out, size_t cap,
                         size_t *needed, char *err, size_t err_cap);
 
+/* Diagnostic (no reference counterpart): writes `code` into the status word through which the tensor-core dot
+ * kernels report a bounded wait that ran out.  The next adb_execute that launches such a kernel then fails with
+ * ADB_ERR_CUDA exactly as it would after a real time-out (and clears the word), which lets the host side of that
+ * error path be tested without a kernel that actually waits for something that never comes. */
+adb_status adb_inject_dot_status(adb_device *dev, int code);
+
 /* 128-byte NCCL unique id for adb_config.nccl_unique_id (rank 0 creates, the caller broadcasts it). */
 adb_status adb_nccl_unique_id(void *out128);
 

@@ -705,6 +705,14 @@ void *oracle_create(void) {
 void oracle_set_f64_acc(void *h, int on) { ((Oracle *)h)->f64_acc = on; }
 void oracle_set_allreduce(void *h, allreduce_fn fn, void *user) { Oracle *o = h; o->allreduce = fn; o->allreduce_user = user; }
 uint64_t oracle_cmds_executed(void *h) { return ((Oracle *)h)->cmds_executed; }
+/* Threads of the OpenMP loops.  A launcher may export OMP_NUM_THREADS=1 to its children (torch.distributed.run
+ * does); a caller that times the oracle as the CPU baseline sets the count it means and reports what it got. */
+#ifdef _OPENMP
+#include <omp.h>
+int oracle_set_threads(int n) { if (n > 0) omp_set_num_threads(n); return omp_get_max_threads(); }
+#else
+int oracle_set_threads(int n) { (void)n; return 1; }
+#endif
 
 void oracle_destroy(void *h) {
     Oracle *o = h;

@@ -46,8 +46,16 @@ def lib():
         L.oracle_set_allreduce.argtypes = [ctypes.c_void_p, _ALLREDUCE_FN, ctypes.c_void_p]
         L.oracle_cmds_executed.argtypes = [ctypes.c_void_p]
         L.oracle_cmds_executed.restype = ctypes.c_uint64
+        L.oracle_set_threads.argtypes = [ctypes.c_int]
+        L.oracle_set_threads.restype = ctypes.c_int
         _lib = L
     return _lib
+
+
+def set_threads(n: int = 0) -> int:
+    """Sets the number of OpenMP threads of the oracle's loops (n <= 0: leave it) and returns the count in force.
+    An inherited OMP_NUM_THREADS=1 (torch.distributed.run exports it) is overridden this way."""
+    return int(lib().oracle_set_threads(int(n)))
 
 
 def _pkg():

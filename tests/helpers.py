@@ -70,3 +70,44 @@ def run_both(program, **kw):
     got = program(b200(), **kw)
     assert set(want) == set(got)
     return want, got
+
+
+def c2_float64(inp, rows, cols):
+    """Config 2 in float64 with, per element, the scale an fp32 evaluation's error is measured in.
+
+    Returns {"a_grad": (value, sigma), "b_grad": (value, sigma)}.  sigma_i = eps32 x (the magnitude of every term of
+    the gradient, each weighted by how much its argument's rounding is amplified): the gradient is a sum of three
+    terms that can cancel, exp(-a) is evaluated as exp2(-a log2 e) (its relative error grows with |a|), the sigmoid's
+    argument a b + bias + 3 carries an absolute rounding error of eps (|a b| + 4), and cos(x) is evaluated as
+    sin(pi/2 - x) (absolute argument error eps (|x| + 4)).  An fp32 chain built from <= 2-ulp primitives stays within a
+    small multiple of sigma at EVERY element, including those far below the tensor's maximum."""
+    eps = float(np.finfo(np.float32).eps)
+    a = np.asarray(inp["a"], np.float64).reshape(rows, cols)
+    b = np.asarray(inp["b"], np.float64).reshape(rows, cols)
+    z = a * b + np.asarray(inp["bias"], np.float64)[None, :] + 3.0
+    S = 1.0 / (1.0 + np.exp(-z))
+    dS = S * (1.0 - S)
+    E = np.exp(-a)
+    R = 1.0 / (1.0 + b * b)
+    amp = 8.0 + 2.0 * np.abs(a * b) + 2.0 * np.abs(a)
+    a1, a2, a3 = 2.0 * S * dS * b * E, -S * S * E, np.sin(a) * R
+    ga = a1 + a2 + a3
+    sa = eps * ((np.abs(a1) + np.abs(a2)) * amp + 6.0 * np.abs(a3) + (np.abs(a) + 4.0) * R)
+    b1, b2, b3 = 2.0 * S * dS * a * E, np.cos(b), np.cos(a) * 2.0 * b * R * R
+    gb = b1 + b2 + b3
+    sb = eps * (np.abs(b1) * amp + 4.0 * np.abs(b2) + (np.abs(b) + 4.0) + 8.0 * np.abs(b3) + (np.abs(a) + 4.0) * np.abs(2.0 * b * R * R))
+    return {"a_grad": (ga, sa), "b_grad": (gb, sb)}
+
+
+def assert_chain_per_element(name, got, want, ref64, sigma):
+    """Per-element bound for a fused chain: at EVERY element the device's distance from float64 stays within one
+    error unit of that element (sigma, see `c2_float64`) and within three times the oracle's own worst distance; the
+    oracle (glibc primitives, <= 1 ulp each) sits at about 0.3 units, which also checks the scale."""
+    g = np.asarray(got.data, np.float64).reshape(ref64.shape)
+    w = np.asarray(want.data, np.float64).reshape(ref64.shape)
+    rd, ro = np.abs(g - ref64) / sigma, np.abs(w - ref64) / sigma
+    worst_d, worst_o = float(rd.max()), float(ro.max())
+    assert worst_o <= 0.6, f"{name}: the oracle itself is {worst_o:.2f} error units from float64 (scale too tight?)"
+    assert worst_d <= max(3.0 * worst_o, 1.0), (f"{name}: {worst_d:.2f} error units from float64 at element {int(rd.argmax())} "
+                                                f"(oracle: {worst_o:.2f})")
+    return worst_d, worst_o

@@ -123,3 +123,24 @@ def test_single_sm_kernel_splits_long_k_too(M, K, N, ta):
     ref = A.astype(np.float64) @ b.reshape(K, N).astype(np.float64)
     g = np.asarray(got.data, np.float64).reshape(M, N)
     assert np.abs(g - ref).max() / np.abs(ref).max() < 2e-5
+
+
+def test_a_dot_kernel_that_gave_up_is_reported_and_the_handle_stays_usable():
+    """The host side of the bounded-wait path: the status word the kernels write on a time-out is set from the host
+    (no kernel waits for anything), the next execute with a tensor-core product must fail with ADB_ERR_CUDA and name
+    the code, and the execute after that must succeed with correct numbers."""
+    from helpers import adb
+    dev = adb.devices.B200(0)
+    try:
+        prog = lambda d: adb.configs.c5_dot_loop(d, n=256, max_iters=2)   # noqa: E731
+        good = prog(dev)
+        assert dev.stats()["tc_gemm_launches"] > 0
+        dev.inject_dot_status(3)
+        with pytest.raises(adb.devices.AdbError) as e:
+            prog(dev)
+        assert e.value.status == 3 and "code 3" in str(e.value), str(e.value)
+        again = prog(dev)
+        for k in good:
+            np.testing.assert_array_equal(np.asarray(again[k].data), np.asarray(good[k].data))
+    finally:
+        dev.close()
