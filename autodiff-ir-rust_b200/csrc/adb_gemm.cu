@@ -21,6 +21,77 @@
 namespace adb {
 
 // ====================================================================================================
+// Element-wise epilogue (the reference's fused dot-product + element-wise kernel,
+// src/devices/opencl/kernels/fuse_dp_elw.rs:48-67: the chain runs on the accumulator before it is stored)
+// ====================================================================================================
+// Same arithmetic as the generated element-wise kernels: + and * are never contracted, 1/x and sqrt(|x|) are the
+// <= 1 ulp special-function forms unless correctly rounded ones are asked for.
+__device__ __forceinline__ float epi_rcp(float x) { float r; asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
+__device__ __forceinline__ float epi_sqrt(float x) { float r; asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
+
+__device__ __forceinline__ float epi_apply(int op, float v, float o, int exact) {
+    switch (op) {
+    case 0: return __fadd_rn(v, o);
+    case 1: return __fmul_rn(v, o);
+    case 2: return exp2f(v);
+    case 3: return log2f(v);
+    case 4: return sinf(v);
+    case 5: return exact ? __frcp_rn(v) : epi_rcp(v);
+    case 6: return exact ? __fsqrt_rn(fabsf(v)) : epi_sqrt(fabsf(v));
+    case 7: return v == 0.f ? 1.f : 0.f;
+    case 8: return v > 0.f ? 1.f : 0.f;
+    default: return v < 0.f ? 1.f : 0.f;
+    }
+}
+
+// the chain on one value (CUDA-core kernel)
+__device__ __forceinline__ float epi_chain1(const GemmEpilogue& e, float v, float cv) {
+    float saved = v;
+    for (int i = 0; i < e.n_ops; i++) {
+        const int kind = e.operand[i];
+        if (kind == 4) { saved = v; continue; }
+        const float o = kind == 1 ? e.c[i] : kind == 2 ? cv : kind == 3 ? saved : 0.f;
+        v = epi_apply(e.op[i], v, o, e.exact_div);
+    }
+    return v;
+}
+
+// the chain on 32 values held in registers; control flow depends only on the (warp-uniform) program
+__device__ __forceinline__ void epi_chain32(const GemmEpilogue& e, float (&v)[32], const float (&cv)[32]) {
+    float saved[32];
+#pragma unroll
+    for (int j = 0; j < 32; j++) saved[j] = v[j];
+    for (int i = 0; i < e.n_ops; i++) {
+        const int op = e.op[i], kind = e.operand[i], exact = e.exact_div;
+        const float c = e.c[i];
+        if (kind == 4) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) saved[j] = v[j];
+            continue;
+        }
+#define ADB_EPI_EACH(expr)                                                             \
+    _Pragma("unroll") for (int j = 0; j < 32; j++) {                                   \
+        const float o = kind == 1 ? c : kind == 2 ? cv[j] : kind == 3 ? saved[j] : 0.f; \
+        (void)o;                                                                        \
+        v[j] = (expr);                                                                  \
+    }
+        switch (op) {
+        case 0: ADB_EPI_EACH(__fadd_rn(v[j], o)) break;
+        case 1: ADB_EPI_EACH(__fmul_rn(v[j], o)) break;
+        case 2: ADB_EPI_EACH(exp2f(v[j])) break;
+        case 3: ADB_EPI_EACH(log2f(v[j])) break;
+        case 4: ADB_EPI_EACH(sinf(v[j])) break;
+        case 5: if (exact) { ADB_EPI_EACH(__frcp_rn(v[j])) } else { ADB_EPI_EACH(epi_rcp(v[j])) } break;
+        case 6: if (exact) { ADB_EPI_EACH(__fsqrt_rn(fabsf(v[j]))) } else { ADB_EPI_EACH(epi_sqrt(fabsf(v[j]))) } break;
+        case 7: ADB_EPI_EACH(v[j] == 0.f ? 1.f : 0.f) break;
+        case 8: ADB_EPI_EACH(v[j] > 0.f ? 1.f : 0.f) break;
+        default: ADB_EPI_EACH(v[j] < 0.f ? 1.f : 0.f) break;
+        }
+#undef ADB_EPI_EACH
+    }
+}
+
+// ====================================================================================================
 // CUDA-core path
 // ====================================================================================================
 // 64x64 tile per block, 4x4 outputs per thread, fp32 FMA with k ascending in every output element
@@ -28,7 +99,8 @@ namespace adb {
 template <int BM, int BN, int BK>
 __global__ void __launch_bounds__(256) adb_dot_simt(const float* __restrict__ A, const float* __restrict__ B,
                                                     float* __restrict__ C, long long M, long long N, long long K,
-                                                    long long a_rs, long long a_cs, long long b_rs, long long b_cs) {
+                                                    long long a_rs, long long a_cs, long long b_rs, long long b_cs,
+                                                    const GemmEpilogue epi) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Bs[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -77,7 +149,17 @@ __global__ void __launch_bounds__(256) adb_dot_simt(const float* __restrict__ A,
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             long long gn = n0 + tx * 4 + j;
-            if (gn < N) C[gm * N + gn] = acc[i][j];
+            if (gn >= N) continue;
+            float v = acc[i][j];
+            const long long at = gm * N + gn;
+            if (epi.mode == 1) {
+                for (int t = 0; t < epi.n_ops; t++) v = __fmul_rn(v, epi.c[t]);
+                C[at] = epi.accumulate ? __fadd_rn(C[at], v) : v;
+            } else if (epi.mode == 2) {
+                if (epi.store_raw) C[at] = v;
+                epi.out[at] = epi_chain1(epi, v, epi.colvec ? epi.colvec[gn] : 0.f);
+            } else
+                C[at] = v;
         }
     }
 }
@@ -118,6 +200,7 @@ struct Params {
     // the k loop of every tile is cut into k_splits ranges of kb_per_split k-blocks that different CTAs (clusters) work
     // on when there are few tiles and K is long; all of them then add into a zeroed C
     int k_splits = 1, kb_per_split = 0;
+    GemmEpilogue epi;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -210,6 +293,88 @@ __device__ __forceinline__ void tmem_load_32cols(uint32_t taddr, float* v) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
     for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+
+// 32 consecutive floats of one row: plain stores, reductions performed at the L2, or loads that are ordered
+// behind this thread's earlier reductions to the same addresses
+__device__ __forceinline__ void row_store32(float* dst, const float (&v)[32], int n_valid, bool vec) {
+    if (vec && n_valid == 32) {
+        float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+        for (int j = 0; j < 8; j++) d4[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; j++)
+            if (j < n_valid) dst[j] = v[j];
+    }
+}
+__device__ __forceinline__ void row_add32(float* dst, const float (&v)[32], int n_valid, bool vec) {
+    if (vec && n_valid == 32) {
+        // fire-and-forget fp32 adds performed at the L2 (round to nearest): no load latency in the epilogue and no
+        // extra registers; same-thread same-address ordering keeps them behind the stores of the first chunk
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * j), "f"(v[4 * j]), "f"(v[4 * j + 1]),
+                         "f"(v[4 * j + 2]), "f"(v[4 * j + 3]) : "memory");
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; j++)
+            if (j < n_valid) atomicAdd(dst + j, v[j]);
+    }
+}
+__device__ __forceinline__ void row_load32(const float* src, float (&v)[32], int n_valid, bool vec) {
+    if (vec && n_valid == 32) {
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            asm volatile("ld.relaxed.gpu.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v[4 * j]), "=f"(v[4 * j + 1]), "=f"(v[4 * j + 2]),
+                         "=f"(v[4 * j + 3]) : "l"(src + 4 * j) : "memory");
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            v[j] = 0.f;
+            if (j < n_valid) asm volatile("ld.relaxed.gpu.global.f32 %0, [%1];" : "=f"(v[j]) : "l"(src + j) : "memory");
+        }
+    }
+}
+
+// One 32-column slice of one row of a finished accumulation chunk goes to memory.  `first`: the chunk opens the k
+// range of its tile and nobody else works on the tile (it may overwrite C); `last`: it closes the range (the sum is
+// complete once it is added).
+__device__ __forceinline__ void epilogue_slice(const Params& p, int row, int col0, float (&v)[32], bool first, bool last, bool vec_c,
+                                               bool vec_out) {
+    if (row >= p.M || col0 >= p.N) return;
+    const int n_valid = min(32, p.N - col0);
+    float* crow = p.C + (size_t)row * p.N + col0;
+    const GemmEpilogue& e = p.epi;
+    if (e.mode == 1) {
+        // scaling commutes with the summation over k: every partial product is scaled, then stored or added
+        for (int t = 0; t < e.n_ops; t++) {
+            const float c = e.c[t];
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] = __fmul_rn(v[j], c);
+        }
+        if (first && !e.accumulate) row_store32(crow, v, n_valid, vec_c);
+        else row_add32(crow, v, n_valid, vec_c);
+        return;
+    }
+    if (e.mode == 2 && last) {
+        if (!first) {
+            // the earlier chunks of this tile were added to C by this very thread: read the running sum back (L2)
+            float run[32];
+            row_load32(crow, run, n_valid, vec_c);
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] = __fadd_rn(run[j], v[j]);
+        }
+        if (e.store_raw) row_store32(crow, v, n_valid, vec_c);
+        float cv[32];
+#pragma unroll
+        for (int j = 0; j < 32; j++) cv[j] = (e.colvec && j < n_valid) ? __ldg(e.colvec + col0 + j) : 0.f;
+        epi_chain32(e, v, cv);
+        row_store32(e.out + (size_t)row * p.N + col0, v, n_valid, vec_out);
+        return;
+    }
+    if (first) row_store32(crow, v, n_valid, vec_c);
+    else row_add32(crow, v, n_valid, vec_c);
 }
 
 // A_MN / B_MN: the operand is contiguous along M (resp. N) in global memory instead of along K.
@@ -370,48 +535,27 @@ adb_dot_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         uint32_t chunk_no = 0;
         bool ok = true;
         const bool vec_ok = (p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+        const bool vec_out = (p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.epi.out) & 15) == 0);
         for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
             const int tile = unit / p.k_splits;
             const int kb_begin = (unit % p.k_splits) * p.kb_per_split, kb_stop = min(kb_begin + p.kb_per_split, p.k_blocks);
             const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
             const int row = m0 + q * 32 + lane;
-            float* crow = p.C + (size_t)row * p.N;
             for (int kb0 = kb_begin; kb0 < kb_stop && ok; kb0 += CHUNK_KB, chunk_no++) {
                 const int acc = chunk_no & 1;
                 const uint32_t acc_ph = (chunk_no >> 1) & 1;
                 // first chunk of the tile overwrites C, later ones add to it (split k ranges: C is zeroed, all add)
                 const bool first = kb0 == 0 && p.k_splits == 1;
+                const bool last = kb0 + CHUNK_KB >= p.k_blocks && p.k_splits == 1;   // the sum of the tile is complete after this chunk
                 if (!mbar_wait_warp(bar_acc_full(acc), acc_ph, stop, p.status, TIMEOUT_ACC_FULL)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (p.epi.mode == 2 && last && !first) __threadfence();   // the running sum is read back below
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; c++) {
                     float v[32];
                     tmem_load_32cols(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, v);
                     const int col0 = n0 + c * 32;
-                    if (row < p.M && col0 < p.N) {
-                        if (vec_ok && col0 + 32 <= p.N) {
-                            float4* dst = reinterpret_cast<float4*>(crow + col0);
-                            if (first) {
-#pragma unroll
-                                for (int j = 0; j < 8; j++) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                            } else {
-                                // fire-and-forget fp32 adds performed at the L2 (round to nearest): no load latency
-                                // in the epilogue and no extra registers; same-thread same-address ordering keeps
-                                // them behind the stores of the first chunk
-#pragma unroll
-                                for (int j = 0; j < 8; j++)
-                                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "f"(v[4 * j]),
-                                                 "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3]) : "memory");
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; j++)
-                                if (col0 + j < p.N) {
-                                    if (first) crow[col0 + j] = v[j];
-                                    else atomicAdd(crow + col0 + j, v[j]);
-                                }
-                        }
-                    }
+                    epilogue_slice(p, row, col0, v, first, last, vec_ok, vec_out);
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
@@ -667,46 +811,28 @@ adb_dot_tc_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         uint32_t chunk_no = 0;
         bool ok = true;
         const bool vec_ok = (p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+        const bool vec_out = (p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.epi.out) & 15) == 0);
         for (int unit = cluster_id; unit < total_units && ok; unit += num_clusters) {
             const int tile = unit / p.k_splits;
             const int kb_begin = (unit % p.k_splits) * p.kb_per_split, kb_stop = min(kb_begin + p.kb_per_split, p.k_blocks);
             const int m0 = (tile / p.tiles_n) * (2 * BM) + (int)rank * BM, n0 = (tile % p.tiles_n) * BN;
             const int row = m0 + q * 32 + lane;
-            float* crow = p.C + (size_t)row * p.N;
             for (int kb0 = kb_begin; kb0 < kb_stop && ok; kb0 += CHUNK_KB, chunk_no++) {
                 const int acc = chunk_no & 1;
                 const uint32_t acc_ph = (chunk_no >> 1) & 1;
                 // the first chunk of a tile overwrites C, later ones add to it; with split k ranges nobody knows who
                 // is first, so C was zeroed and everybody adds
                 const bool first = kb0 == 0 && p.k_splits == 1;
+                const bool last = kb0 + CHUNK_KB >= p.k_blocks && p.k_splits == 1;   // the sum of the tile is complete after this chunk
                 if (!mbar_wait_warp(bar_acc_full(acc), acc_ph, stop, p.status, TIMEOUT_ACC_FULL)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (p.epi.mode == 2 && last && !first) __threadfence();   // the running sum is read back below
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; c++) {
                     float v[32];
                     tmem_load_32cols(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, v);
                     const int col0 = n0 + c * 32;
-                    if (row < p.M && col0 < p.N) {
-                        if (vec_ok && col0 + 32 <= p.N) {
-                            float4* dst = reinterpret_cast<float4*>(crow + col0);
-                            if (first) {
-#pragma unroll
-                                for (int j = 0; j < 8; j++) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 8; j++)
-                                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "f"(v[4 * j]),
-                                                 "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3]) : "memory");
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; j++)
-                                if (col0 + j < p.N) {
-                                    if (first) crow[col0 + j] = v[j];
-                                    else atomicAdd(crow + col0 + j, v[j]);
-                                }
-                        }
-                    }
+                    epilogue_slice(p, row, col0, v, first, last, vec_ok, vec_out);
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
@@ -820,13 +946,17 @@ static bool plan_k_split(tc::Params& p, long long tiles, int workers, const Gemm
     using namespace tc;
     p.k_splits = 1;
     p.kb_per_split = p.k_blocks;
+    // a chain that runs on the finished sum needs one owner per tile
+    if (a.epi.mode == 2) return true;
     if (tiles * 2 > workers || p.k_blocks < 2 * CHUNK_KB) return true;
     const long long want = workers / tiles;
     long long per = (p.k_blocks + want - 1) / want;
     per = (per + CHUNK_KB - 1) / CHUNK_KB * CHUNK_KB;
     p.kb_per_split = (int)per;
     p.k_splits = (int)((p.k_blocks + per - 1) / per);
-    if (p.k_splits > 1 && cudaMemsetAsync(a.C, 0, size_t(a.M) * size_t(a.N) * sizeof(float), stream) != cudaSuccess) {
+    // (a product that is added to what C holds must not clear it: every range adds anyway)
+    if (p.k_splits > 1 && !(a.epi.mode == 1 && a.epi.accumulate) &&
+        cudaMemsetAsync(a.C, 0, size_t(a.M) * size_t(a.N) * sizeof(float), stream) != cudaSuccess) {
         err = "cudaMemsetAsync(C)";
         return false;
     }
@@ -854,6 +984,7 @@ int gemm_launch(GemmContext& ctx, const GemmArgs& a, cudaStream_t stream, std::s
                          : encode(enc, &mb, a.B, a.K, a.N, a.b_cs, paired ? pair::BNH : BN, false));
         if (ok) {
             Params p;
+            p.epi = a.epi;
             p.C = a.C;
             p.M = (int)a.M; p.N = (int)a.N; p.K = (int)a.K;
             p.tiles_m = (int)((a.M + BM - 1) / BM);
@@ -899,7 +1030,7 @@ int gemm_launch(GemmContext& ctx, const GemmArgs& a, cudaStream_t stream, std::s
     }
     dim3 grid((unsigned)((a.N + 63) / 64), (unsigned)((a.M + 63) / 64));
     if (grid.y > 65535) { err = "M too large for the SIMT dot kernel"; return -1; }
-    adb_dot_simt<64, 64, 16><<<grid, 256, 0, stream>>>(a.A, a.B, a.C, a.M, a.N, a.K, a.a_rs, a.a_cs, a.b_rs, a.b_cs);
+    adb_dot_simt<64, 64, 16><<<grid, 256, 0, stream>>>(a.A, a.B, a.C, a.M, a.N, a.K, a.a_rs, a.a_cs, a.b_rs, a.b_cs, a.epi);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { err = cudaGetErrorString(e); return -1; }
     return 1;

@@ -8,6 +8,22 @@
 
 namespace adb {
 
+// Element-wise work on the product while it is still in registers (see Step::Gemm in adb_plan.hpp): a chain
+// v = acc; v = op_i(v, operand_i).  Passed to the kernels by value.
+constexpr int GEMM_EPI_MAX_OPS = 12;
+struct GemmEpilogue {
+    int mode = 0;                 // 0 none, 1 scale (every partial product; optionally added to C), 2 chain on the finished sum
+    int accumulate = 0;           // mode 1: C += scaled product instead of C = scaled product
+    int store_raw = 1;            // mode 2: also write the plain product to C
+    int exact_div = 0;            // 1/x and sqrt correctly rounded instead of the <= 1 ulp hardware forms
+    int n_ops = 0;
+    float* out = nullptr;         // mode 2: row-major [M,N] destination of the chain (may equal C when store_raw is 0)
+    const float* colvec = nullptr;  // N values indexed by the column
+    unsigned char op[GEMM_EPI_MAX_OPS] = {};       // EOp
+    unsigned char operand[GEMM_EPI_MAX_OPS] = {};  // 0 none, 1 constant, 2 column vector, 3 saved value, 4 save the running value
+    float c[GEMM_EPI_MAX_OPS] = {};
+};
+
 struct GemmArgs {
     const float* A = nullptr;
     const float* B = nullptr;
@@ -17,6 +33,7 @@ struct GemmArgs {
     bool force_simt = false;
     bool no_pair = false;  // keep the tensor-core kernel on one SM per tile
     int reserve_sms = 0;   // leave this many SMs to a kernel running beside the product (a collective on another stream)
+    GemmEpilogue epi;
 };
 
 struct GemmContext {

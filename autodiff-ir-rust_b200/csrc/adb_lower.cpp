@@ -103,6 +103,7 @@ class Lowerer {
         finalize_results();
         plan_.n_steps = pos_;
         fuse_reductions();
+        if (!opt_.no_fusion && !opt_.no_dot_epilogue) fuse_dot_epilogues(plan_.main);
         plan_arena();
     }
 
@@ -1391,7 +1392,13 @@ class Lowerer {
             for (auto& ph : k.phases) wr.push_back(ph.dst.buf);
             break;
         }
-        case Step::GEMM: rd = {s.gemm.a, s.gemm.b}; wr = {s.gemm.c}; break;
+        case Step::GEMM:
+            rd = {s.gemm.a, s.gemm.b};
+            wr = {s.gemm.c};
+            if (s.gemm.accumulate) rd.push_back(s.gemm.c);
+            if (s.gemm.colvec >= 0) rd.push_back(s.gemm.colvec);
+            if (s.gemm.out >= 0) wr.push_back(s.gemm.out);
+            break;
         case Step::UPLOAD: wr = {s.buf}; break;
         case Step::ALLREDUCE: rd = {s.buf}; wr = {s.buf}; break;
         default: break;
@@ -1960,6 +1967,285 @@ class Lowerer {
         return true;
     }
 
+    // ------------------------------------------------------------------ element-wise work folded into dot products
+    // The reference fuses a dot product with the element-wise kernels that follow it (`DPElwExpr`,
+    // src/kernel/fusion/dp_elw.rs:13-150) and then drops buffers that only live inside the fused region
+    // (src/kernel/alloc/alloc_temp_opt.rs:37-122).  Here: an output of an element-wise kernel that is a chain
+    // v = product; v = op(v, constant | bias[column] | v itself) moves into the dot product's epilogue, where the
+    // accumulator is still in registers.  Three shapes come out of it (Step::Gemm):
+    //   out = chain(product)                       Linear + bias + activation: the activation never re-reads the product
+    //   t = c1 * c2 * product                      the scaled gradient that an all-reduce wants: no scale pass
+    //   W = W + c1 * c2 * product                  the SGD update: the gradient never exists in memory
+    // A kernel whose outputs all moved away disappears; otherwise it is pruned to what is left.
+    bool all_readers(const StepBlock& blk, int buf, const Step* except, int& n) const {
+        std::vector<int> rd, wr;
+        for (auto& st : blk.steps) {
+            if (&st != except) {
+                step_rw(st, rd, wr);
+                for (int b : rd) n += b == buf;
+                if ((st.kind == Step::WHILE && st.cond_buf == buf)) n++;
+                for (auto& br : st.branches) n += br.cond_buf == buf;
+            }
+            if (st.body) all_readers(*st.body, buf, except, n);
+            for (auto& br : st.branches) all_readers(*br.body, buf, except, n);
+            if (st.else_body) all_readers(*st.else_body, buf, except, n);
+        }
+        return n > 0;
+    }
+    bool buffer_escapes(int buf) const {
+        if (plan_.bufs[size_t(buf)].persistent || plan_.bufs[size_t(buf)].external) return true;
+        for (auto& r : plan_.results) if (r.buf == buf) return true;
+        return false;
+    }
+
+    // drops SSA values and operands that no output, side sum or phase of `k` uses any more
+    static void prune_kernel(KernelSpec& k) {
+        std::vector<char> live(k.ssa.size(), 0);
+        std::vector<int> st;
+        for (auto& o : k.outs) st.push_back(o.ssa);
+        for (auto& r : k.reds) st.push_back(r.ssa);
+        for (auto& ph : k.phases) st.push_back(ph.ssa);
+        while (!st.empty()) {
+            int i = st.back();
+            st.pop_back();
+            if (i < 0 || live[size_t(i)]) continue;
+            live[size_t(i)] = 1;
+            if (k.ssa[size_t(i)].kind == Ssa::OP) { st.push_back(k.ssa[size_t(i)].a); st.push_back(k.ssa[size_t(i)].b); }
+        }
+        std::vector<int> in_map(k.ins.size(), -1), ssa_map(k.ssa.size(), -1);
+        std::vector<Operand> ins;
+        std::vector<Ssa> ssa;
+        for (size_t i = 0; i < k.ssa.size(); i++) {
+            if (!live[i]) continue;
+            Ssa v = k.ssa[i];
+            if (v.kind == Ssa::LOAD) {
+                if (in_map[size_t(v.operand)] < 0) { ins.push_back(k.ins[size_t(v.operand)]); in_map[size_t(v.operand)] = int(ins.size()) - 1; }
+                v.operand = in_map[size_t(v.operand)];
+            } else if (v.kind == Ssa::OP) {
+                v.a = ssa_map[size_t(v.a)];
+                if (v.b >= 0) v.b = ssa_map[size_t(v.b)];
+            }
+            ssa.push_back(v);
+            ssa_map[i] = int(ssa.size()) - 1;
+        }
+        for (auto& o : k.outs) o.ssa = ssa_map[size_t(o.ssa)];
+        for (auto& r : k.reds) r.ssa = ssa_map[size_t(r.ssa)];
+        for (auto& ph : k.phases) ph.ssa = ssa_map[size_t(ph.ssa)];
+        k.ins.swap(ins);
+        k.ssa.swap(ssa);
+    }
+
+    struct EpiChain {
+        std::vector<Step::Gemm::EpiOp> ops;
+        int colvec = -1;
+        int64_t colvec_off = 0;
+        bool acc_mat = false;      // the chain ends with "+ destination" (in-place accumulate)
+        bool ok = false;
+    };
+
+    // the value `idx` of kernel `k` as a chain over the load of `cb` (identity access over M*N elements)
+    bool chain_of(const KernelSpec& k, int idx, int cb, int64_t M, int64_t N, const Operand& dst, EpiChain& out, int depth = 0) const {
+        if (depth > 64) return false;
+        const Ssa& v = k.ssa[size_t(idx)];
+        auto is_product = [&](int i) {
+            const Ssa& x = k.ssa[size_t(i)];
+            if (x.kind != Ssa::LOAD) return false;
+            const Operand& o = k.ins[size_t(x.operand)];
+            std::vector<Sub> want;
+            if (M * N > 1) want.push_back({M * N, 1});
+            std::vector<Sub> have = o.subs;
+            canon_subs(have);
+            return o.buf == cb && o.offset == 0 && have == want;
+        };
+        if (v.kind == Ssa::LOAD) return is_product(idx);
+        if (v.kind != Ssa::OP) return false;
+        Step::Gemm::EpiOp op;
+        op.op = v.op;
+        if (!eop_is_binary(v.op)) {
+            if (!chain_of(k, v.a, cb, M, N, dst, out, depth + 1)) return false;
+            op.operand = 0;
+            out.ops.push_back(op);
+            return true;
+        }
+        if (v.a == v.b) {   // x op x
+            if (!chain_of(k, v.a, cb, M, N, dst, out, depth + 1)) return false;
+            if (v.op == E_ADD) {   // x + x is 2 x, exactly
+                op.op = E_MUL;
+                op.operand = 1;
+                op.c = 2.0f;
+                out.ops.push_back(op);
+                return true;
+            }
+            Step::Gemm::EpiOp save;
+            save.operand = 4;
+            out.ops.push_back(save);
+            op.operand = 3;
+            out.ops.push_back(op);
+            return true;
+        }
+        // which side carries the product?
+        auto side_operand = [&](int i, Step::Gemm::EpiOp& o2, bool& is_acc, EpiChain& out) {
+            const Ssa& x = k.ssa[size_t(i)];
+            is_acc = false;
+            if (x.kind == Ssa::CONST) { o2.operand = 1; o2.c = x.c; return true; }
+            if (x.kind != Ssa::LOAD) return false;
+            const Operand& o = k.ins[size_t(x.operand)];
+            std::vector<Sub> have = o.subs;
+            canon_subs(have);
+            std::vector<Sub> colv;
+            if (M > 1) colv.push_back({M, 0});
+            if (N > 1) colv.push_back({N, 1});
+            canon_subs(colv);
+            if (o.buf != cb && have == colv && N > 1) {
+                if (out.colvec >= 0 && (out.colvec != o.buf || out.colvec_off != o.offset)) return false;
+                out.colvec = o.buf;
+                out.colvec_off = o.offset;
+                o2.operand = 2;
+                return true;
+            }
+            std::vector<Sub> full;
+            if (M * N > 1) full.push_back({M * N, 1});
+            std::vector<Sub> dsubs = dst.subs;
+            canon_subs(dsubs);
+            if (o.buf == dst.buf && o.offset == dst.offset && have == full && dsubs == full) { is_acc = true; return true; }
+            return false;
+        };
+        for (int t = 0; t < 2; t++) {
+            const int chain_side = t == 0 ? v.a : v.b, other = t == 0 ? v.b : v.a;
+            EpiChain trial = out;
+            bool is_acc = false;
+            Step::Gemm::EpiOp o2 = op;
+            if (!side_operand(other, o2, is_acc, trial)) continue;
+            if (!chain_of(k, chain_side, cb, M, N, dst, trial, depth + 1)) continue;
+            if (is_acc) {
+                if (v.op != E_ADD || depth != 0 || trial.acc_mat) continue;   // only "destination + chain" at the very end
+                trial.acc_mat = true;
+            } else
+                trial.ops.push_back(o2);
+            out = trial;
+            return true;
+        }
+        return false;
+    }
+
+    void fuse_dot_epilogues(StepBlock& blk) {
+        for (auto& s : blk.steps) {
+            if (s.body) fuse_dot_epilogues(*s.body);
+            for (auto& br : s.branches) fuse_dot_epilogues(*br.body);
+            if (s.else_body) fuse_dot_epilogues(*s.else_body);
+        }
+        auto& steps = blk.steps;
+        std::vector<int> rd, wr;
+        for (size_t gi = 0; gi < steps.size(); gi++) {
+            if (steps[gi].kind != Step::GEMM || steps[gi].gemm.epi != Step::Gemm::EPI_NONE || steps[gi].gemm.c_off != 0) continue;
+            const int cb = steps[gi].gemm.c;
+            const int64_t M = steps[gi].gemm.M, N = steps[gi].gemm.N;
+            if (M * N <= 0) continue;
+            // the first step behind the product that reads it
+            size_t ei = 0;
+            bool found = false;
+            for (size_t j = gi + 1; j < steps.size() && j - gi <= 64; j++) {
+                if (is_barrier(steps[j])) break;
+                step_rw(steps[j], rd, wr);
+                const bool reads = std::find(rd.begin(), rd.end(), cb) != rd.end();
+                const bool writes = std::find(wr.begin(), wr.end(), cb) != wr.end();
+                if (reads) { found = !writes; ei = j; break; }
+                if (writes) break;
+            }
+            if (!found || steps[ei].kind != Step::ELW) continue;
+            KernelSpec& k = plan_.kernels[size_t(steps[ei].kernel)];
+            if (k.type != KernelSpec::ELW || !k.reds.empty() || k.n != M * N) continue;
+            // one output at a time (several parameters of equal size share one update kernel)
+            for (size_t oi = 0; oi < k.outs.size(); oi++) {
+                const KernelSpec::Out o = k.outs[oi];
+                std::vector<Sub> dsubs = o.dst.subs, full;
+                canon_subs(dsubs);
+                if (M * N > 1) full.push_back({M * N, 1});
+                if (dsubs != full) continue;
+                EpiChain ch;
+                if (!chain_of(k, o.ssa, cb, M, N, o.dst, ch)) continue;
+                if (ch.ops.empty() && !ch.acc_mat) continue;
+                if (ch.ops.size() > 12) continue;
+                bool scale_only = true;
+                for (auto& op : ch.ops) scale_only = scale_only && op.op == E_MUL && op.operand == 1;
+                if (ch.acc_mat && !scale_only) continue;
+                // who else reads the plain product?
+                int other_readers = 0;
+                all_readers(plan_.main, cb, nullptr, other_readers);
+                // (this kernel counts once however many of its outputs read it: look at its other outputs)
+                bool k_still_reads = false;
+                for (size_t q = 0; q < k.outs.size(); q++) {
+                    if (q == oi) continue;
+                    EpiChain dummy;
+                    std::vector<int> stq{k.outs[q].ssa};
+                    std::vector<char> seen(k.ssa.size(), 0);
+                    while (!stq.empty()) {
+                        int i = stq.back();
+                        stq.pop_back();
+                        if (i < 0 || seen[size_t(i)]) continue;
+                        seen[size_t(i)] = 1;
+                        const Ssa& x = k.ssa[size_t(i)];
+                        if (x.kind == Ssa::LOAD && k.ins[size_t(x.operand)].buf == cb) k_still_reads = true;
+                        if (x.kind == Ssa::OP) { stq.push_back(x.a); stq.push_back(x.b); }
+                    }
+                }
+                const bool raw_needed = buffer_escapes(cb) || other_readers > 1 || k_still_reads;
+                if (scale_only && raw_needed) continue;   // the scaled product replaces the plain one: nobody may want the latter
+                // few tiles and a long k loop: the dot kernels would split k over the SMs, which a chain on the finished
+                // sum rules out (one owner per tile) -- the split is worth more than the saved pass
+                if (!scale_only && ((M + 255) / 256) * ((N + 255) / 256) * 4 <= opt_.sm_count && steps[gi].gemm.K >= 2048) continue;
+                // the output's value appears at the product's position instead of the kernel's: nothing in between may
+                // look at the destination, overwrite the bias, or -- when the kernel itself goes away -- mind the move
+                bool hoist_ok = true;
+                for (size_t j = gi + 1; j < ei && hoist_ok; j++) {
+                    step_rw(steps[j], rd, wr);
+                    for (int b : rd) if (b == o.dst.buf) hoist_ok = false;
+                    for (int b : wr) if (b == o.dst.buf || b == ch.colvec) hoist_ok = false;
+                }
+                // the kernel's other inputs are not needed by the epilogue, and the destination must not be one of the
+                // product's own operands
+                if (o.dst.buf == steps[gi].gemm.a || o.dst.buf == steps[gi].gemm.b) hoist_ok = false;
+                if (!hoist_ok) continue;
+
+                Step::Gemm& g = steps[gi].gemm;
+                g.ops = ch.ops;
+                g.colvec = ch.colvec;
+                g.colvec_off = ch.colvec_off;
+                if (scale_only) {
+                    g.epi = Step::Gemm::EPI_SCALE;
+                    g.accumulate = ch.acc_mat;
+                    g.c = o.dst.buf;
+                    g.c_off = o.dst.offset;
+                    touch(g.c, steps[gi].pos);
+                    plan_.bufs[size_t(cb)].first = INT_MAX;
+                    plan_.bufs[size_t(cb)].last = -1;
+                } else {
+                    g.epi = Step::Gemm::EPI_CHAIN;
+                    g.store_raw = raw_needed;
+                    g.out = o.dst.buf;
+                    g.out_off = o.dst.offset;
+                    touch(g.out, steps[gi].pos);
+                    if (g.colvec >= 0) touch(g.colvec, steps[gi].pos);
+                    if (!raw_needed) {
+                        // partial sums accumulate in the destination itself; the last chunk overwrites them with the chain
+                        g.c = g.out;
+                        g.c_off = g.out_off;
+                        plan_.bufs[size_t(cb)].first = INT_MAX;
+                        plan_.bufs[size_t(cb)].last = -1;
+                    }
+                }
+                k.outs.erase(k.outs.begin() + long(oi));
+                break;   // one epilogue per product
+            }
+            if (steps[gi].gemm.epi == Step::Gemm::EPI_NONE) continue;
+            if (k.outs.empty()) {
+                k.dead = true;
+                steps.erase(steps.begin() + long(ei));
+            } else
+                prune_kernel(k);
+        }
+    }
+
     // ------------------------------------------------------------------ arena
     void plan_arena() {
         auto& bufs = plan_.bufs;
@@ -2080,6 +2366,20 @@ static void dump_block(const Plan& p, const StepBlock& b, int ind, bool src, std
             o << pad << "#" << s.pos << " gemm " << p.bufs[s.gemm.c].name << "[" << s.gemm.M << "," << s.gemm.N << "] = "
               << p.bufs[s.gemm.a].name << "+" << s.gemm.a_off << "(" << s.gemm.a_rs << "," << s.gemm.a_cs << ") . "
               << p.bufs[s.gemm.b].name << "+" << s.gemm.b_off << "(" << s.gemm.b_rs << "," << s.gemm.b_cs << ") K=" << s.gemm.K << "\n";
+            if (s.gemm.epi != Step::Gemm::EPI_NONE) {
+                o << pad << "    epilogue: ";
+                if (s.gemm.epi == Step::Gemm::EPI_SCALE) o << p.bufs[s.gemm.c].name << (s.gemm.accumulate ? " += " : " = ") << "product";
+                else o << p.bufs[s.gemm.out].name << "+" << s.gemm.out_off << " = product";
+                for (auto& op : s.gemm.ops) {
+                    if (op.operand == 4) { o << " ; save"; continue; }
+                    o << " ; " << eop_name(op.op);
+                    if (op.operand == 1) o << " " << op.c;
+                    else if (op.operand == 2) o << " " << p.bufs[s.gemm.colvec].name << "[col]";
+                    else if (op.operand == 3) o << " saved";
+                }
+                if (s.gemm.epi == Step::Gemm::EPI_CHAIN) o << (s.gemm.store_raw ? "  (plain product kept in " + p.bufs[s.gemm.c].name + ")" : "  (plain product not kept)");
+                o << "\n";
+            }
             break;
         case Step::UPLOAD:
             o << pad << "#" << s.pos << " upload " << p.bufs[s.buf].name << " n=" << s.nelem << "\n";

@@ -105,6 +105,31 @@ struct Step {
         int64_t M = 0, N = 0, K = 0;
         int64_t a_off = 0, b_off = 0, c_off = 0;
         int64_t a_rs = 0, a_cs = 0, b_rs = 0, b_cs = 0;
+        // Element-wise work on the product, done while the accumulator is still in registers (the reference's
+        // `DPElwExpr`, src/kernel/fusion/dp_elw.rs:13-150 / src/devices/opencl/kernels/fuse_dp_elw.rs:48-67): a
+        // chain  v = acc; v = op_i(v, operand_i)  whose operands are constants, one vector indexed by the column
+        // (a bias broadcast over the rows) or a value saved earlier in the chain.
+        //   EPI_SCALE  every op is a multiplication by a constant: the chain commutes with the summation over k, so
+        //              it is applied to every partial product.  With `accumulate` the scaled product is ADDED to what
+        //              C already holds (`W += -lr * (x^T . g)`: the gradient never exists in memory,
+        //              src/kernel/alloc/alloc_temp_opt.rs:37-122).
+        //   EPI_CHAIN  any chain, applied once to the finished sum; the result goes to `out` (row-major [M,N]); the
+        //              plain product is still written to C when `store_raw` (something else reads it).  With
+        //              store_raw off, C and out are the same buffer.
+        enum EpiMode : uint8_t { EPI_NONE = 0, EPI_SCALE = 1, EPI_CHAIN = 2 };
+        struct EpiOp {
+            EOp op = E_ADD;
+            uint8_t operand = 0;   // 0 none (unary), 1 constant, 2 column vector, 3 saved value; 4 = "save the running value"
+            float c = 0.f;
+        };
+        EpiMode epi = EPI_NONE;
+        bool accumulate = false;
+        bool store_raw = true;
+        int out = -1;              // EPI_CHAIN: destination of the chain
+        int64_t out_off = 0;
+        int colvec = -1;           // the column-indexed vector (N elements, contiguous)
+        int64_t colvec_off = 0;
+        std::vector<EpiOp> ops;
     } gemm;
     // UPLOAD: payload slot -> buffer; ALLREDUCE: buffer range
     int buf = -1;
@@ -160,6 +185,7 @@ struct LowerOptions {
     bool no_fusion = false;
     bool no_reduce_fusion = false;  // keep every Sum in a kernel of its own
     bool fuse_small_sums = false;   // fold sums into element-wise kernels of any size (the thresholds only exist for speed)
+    bool no_dot_epilogue = false;   // keep element-wise kernels behind dot products apart from them
     bool exact_div = false;
     int64_t fuse_limit = 768;  // largest expression DAG fused into one kernel
     int rank = 0, world = 1;

@@ -357,6 +357,21 @@ class Executor {
             a.force_simt = (d_->flags & ADB_FLAG_SIMT_DOT) != 0;
             a.no_pair = (d_->flags & ADB_FLAG_SINGLE_SM_DOT) != 0;
             a.reserve_sms = gemm_reserve_;
+            if (g.epi != Step::Gemm::EPI_NONE) {
+                a.epi.mode = int(g.epi);
+                a.epi.accumulate = g.accumulate ? 1 : 0;
+                a.epi.store_raw = g.store_raw ? 1 : 0;
+                a.epi.exact_div = plan_.exact_div ? 1 : 0;
+                a.epi.n_ops = int(g.ops.size());
+                if (a.epi.n_ops > GEMM_EPI_MAX_OPS) throw CudaFail{"internal: dot-product epilogue too long"};
+                for (int i = 0; i < a.epi.n_ops; i++) {
+                    a.epi.op[i] = (unsigned char)g.ops[size_t(i)].op;
+                    a.epi.operand[i] = g.ops[size_t(i)].operand;
+                    a.epi.c[i] = g.ops[size_t(i)].c;
+                }
+                a.epi.out = g.out >= 0 ? buf_ptr(g.out, g.out_off) : nullptr;
+                a.epi.colvec = g.colvec >= 0 ? buf_ptr(g.colvec, g.colvec_off) : nullptr;
+            }
             std::string e;
             const unsigned long long tc0 = d_->gemm.tc_total;
             int n = gemm_launch(d_->gemm, a, cur_stream_, e);
@@ -476,7 +491,11 @@ class Executor {
             for (auto& o : k.outs) bufs.push_back(o.dst.buf);
             break;
         }
-        case Step::GEMM: bufs = {s.gemm.a, s.gemm.b, s.gemm.c}; break;
+        case Step::GEMM:
+            bufs = {s.gemm.a, s.gemm.b, s.gemm.c};
+            if (s.gemm.out >= 0) bufs.push_back(s.gemm.out);
+            if (s.gemm.colvec >= 0) bufs.push_back(s.gemm.colvec);
+            break;
         case Step::UPLOAD: case Step::ALLREDUCE: bufs = {s.buf}; break;
         default: break;
         }

@@ -5,7 +5,8 @@
 //   hostcheck <flags> <world> <shard_batch> <blob files ...>
 //
 // flags: bit 0 no fusion, bit 1 fold small sums, bit 2 correctly rounded division, bit 3 also execute every plan on
-// the CPU (plan_interp.hpp) and write the kept tensors to <blob file>.out.
+// the CPU (plan_interp.hpp) and write the kept tensors to <blob file>.out, bit 4 keep element-wise kernels out of the
+// dot products' epilogues.
 // Malformed blobs must be rejected with an exception (counted), never crash.  Every plan that does come out is
 // checked against the invariants below (step order, buffer lifetimes, arena placement).
 #include <algorithm>
@@ -40,7 +41,11 @@ static void step_buffers(const adb::Plan& plan, const adb::Step& s, std::vector<
         for (auto& ph : k.phases) bufs.push_back(ph.dst.buf);
         break;
     }
-    case Step::GEMM: bufs = {s.gemm.a, s.gemm.b, s.gemm.c}; break;
+    case Step::GEMM:
+        bufs = {s.gemm.a, s.gemm.b, s.gemm.c};
+        if (s.gemm.out >= 0) bufs.push_back(s.gemm.out);
+        if (s.gemm.colvec >= 0) bufs.push_back(s.gemm.colvec);
+        break;
     case Step::UPLOAD: case Step::ALLREDUCE: bufs = {s.buf}; break;
     case Step::WHILE: bufs = {s.cond_buf}; break;
     case Step::IF: for (auto& br : s.branches) bufs.push_back(br.cond_buf); break;
@@ -55,7 +60,7 @@ static std::string check_block(const adb::Plan& plan, const adb::StepBlock& blk,
         last_pos = s.pos;
         if ((s.kind == adb::Step::ELW || s.kind == adb::Step::REDUCE) && plan.kernels[size_t(s.kernel)].dead)
             return "step at " + std::to_string(s.pos) + " runs a kernel that was marked dead";
-        if (s.kind == adb::Step::GEMM && (s.gemm.c == s.gemm.a || s.gemm.c == s.gemm.b))
+        if (s.kind == adb::Step::GEMM && (s.gemm.c == s.gemm.a || s.gemm.c == s.gemm.b || (s.gemm.out >= 0 && (s.gemm.out == s.gemm.a || s.gemm.out == s.gemm.b))))
             return "dot product at " + std::to_string(s.pos) + " writes into one of its operands";
         step_buffers(plan, s, bufs);
         for (int b : bufs) {
@@ -158,6 +163,7 @@ int main(int argc, char** argv) {
                 opt.no_fusion = flags & 1;
                 opt.fuse_small_sums = flags & 2;
                 opt.exact_div = flags & 4;
+                opt.no_dot_epilogue = flags & 16;
                 opt.rank = rank;
                 opt.world = world;
                 if (world > 1 && batch) adb::shard_program(prog, rank, world, batch);

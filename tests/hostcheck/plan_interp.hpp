@@ -170,14 +170,31 @@ struct PlanInterp {
             const float* A = ptr(g.a, g.a_off);
             const float* B = ptr(g.b, g.b_off);
             float* C = ptr(g.c, g.c_off);
-            // C is written in place, element by element, and zeroed first as the split-k path of the GPU kernel does:
-            // a plan whose product lands in one of its own operands shows up as a wrong result here too
-            for (int64_t i = 0; i < g.M * g.N; i++) C[i] = 0.f;
+            // C is written in place, element by element; a plan whose product lands in one of its own operands shows
+            // up as a wrong result here too.  A plain product zeroes C first, as the split-k path of the GPU kernel does.
+            if (!(g.epi == Step::Gemm::EPI_SCALE && g.accumulate))
+                for (int64_t i = 0; i < g.M * g.N; i++) C[i] = 0.f;
+            float* out = g.out >= 0 ? ptr(g.out, g.out_off) : nullptr;
+            const float* colvec = g.colvec >= 0 ? ptr(g.colvec, g.colvec_off) : nullptr;
             for (int64_t m = 0; m < g.M; m++)
                 for (int64_t n = 0; n < g.N; n++) {
                     double acc = 0;
                     for (int64_t kk = 0; kk < g.K; kk++) acc += double(A[m * g.a_rs + kk * g.a_cs]) * double(B[kk * g.b_rs + n * g.b_cs]);
-                    C[m * g.N + n] = float(acc);
+                    volatile float v = float(acc);
+                    if (g.epi == Step::Gemm::EPI_SCALE) {
+                        for (auto& op : g.ops) v = v * op.c;
+                        C[m * g.N + n] = g.accumulate ? C[m * g.N + n] + v : v;
+                    } else if (g.epi == Step::Gemm::EPI_CHAIN) {
+                        if (g.store_raw) C[m * g.N + n] = v;
+                        volatile float saved = v;
+                        for (auto& op : g.ops) {
+                            if (op.operand == 4) { saved = v; continue; }
+                            const float o = op.operand == 1 ? op.c : op.operand == 2 ? colvec[n] : op.operand == 3 ? float(saved) : 0.f;
+                            v = apply(op.op, v, o);
+                        }
+                        out[m * g.N + n] = v;
+                    } else
+                        C[m * g.N + n] = v;
                 }
             break;
         }

@@ -1,0 +1,140 @@
+"""Element-wise work folded into the dot product's epilogue (the reference's `DPElwExpr`,
+src/kernel/fusion/dp_elw.rs:13-150): bias + activation on the finished sum, the scaled product, and the in-place
+`W += c * (A . B)` -- every operand layout, ragged edges, k loops of several accumulation chunks, split k ranges --
+against float64, and against the same program with the fusion left out."""
+import numpy as np
+import pytest
+
+from helpers import ad, adb, b200, oracle, assert_rel
+
+pytestmark = pytest.mark.gpu
+RNG = np.random.default_rng(41)
+_simt = None
+
+
+def _device(kind):
+    global _simt
+    if kind == "tc":
+        return b200()
+    if _simt is None:
+        _simt = adb.devices.B200(0, flags=adb.devices.FLAG_SIMT_DOT)
+    return _simt
+
+
+def _operands(M, K, N, ta, tb):
+    a = RNG.standard_normal(M * K).astype(np.float32)
+    b = (RNG.standard_normal(K * N) / np.sqrt(K)).astype(np.float32)
+    A64 = (a.reshape(K, M).T if ta else a.reshape(M, K)).astype(np.float64)
+    B64 = (b.reshape(N, K).T if tb else b.reshape(K, N)).astype(np.float64)
+    return a, b, A64, B64
+
+
+def _tensors(a, b, M, K, N, ta, tb):
+    A = ad.tensor(a, [K, M] if ta else [M, K])
+    B = ad.tensor(b, [N, K] if tb else [K, N])
+    return (A.t() if ta else A), (B.t() if tb else B)
+
+
+@pytest.mark.parametrize("kind", ["tc", "simt"])
+@pytest.mark.parametrize("keep_product", [False, True], ids=["activation-only", "product-kept-too"])
+@pytest.mark.parametrize("M,K,N,ta,tb", [(256, 512, 512, False, False), (1536, 4096, 1800, False, False), (2304, 2500, 1000, True, False),
+                                         (2048, 3200, 1160, False, True), (128, 1024, 256, False, False), (520, 96, 260, True, True),
+                                         (384, 4096, 1000, False, False)])
+def test_bias_and_sigmoid_run_in_the_epilogue(M, K, N, ta, tb, keep_product, kind):
+    if kind == "simt" and M * K * N > 1 << 28:
+        pytest.skip("CUDA-core kernel: small cases only")
+    # few tiles and a long k loop: the kernels split k over the SMs instead, which rules out a chain on the finished sum
+    split_instead = ((M + 255) // 256) * ((N + 255) // 256) * 4 <= 148 and K >= 2048
+    a, b, A64, B64 = _operands(M, K, N, ta, tb)
+    bias = RNG.standard_normal(N).astype(np.float32)
+    dev = _device(kind)
+    ad.set_device(dev)
+    ad.eager_dep_opt()
+    A, B = _tensors(a, b, M, K, N, ta, tb)
+    z = ad.dot(A, B)
+    y = (z + ad.tensor(bias, [N])).sigmoid()
+    y.forward()
+    y.val().keep()
+    if keep_product:
+        z.val().keep()
+    ad.execute()
+    plan = dev.dump_plan()
+    assert ("epilogue:" in plan and "recip" in plan) == (not split_instead), plan
+    assert ("plain product kept" in plan) == (keep_product and not split_instead), plan
+    zr = A64 @ B64
+    yr = 1.0 / (1.0 + np.exp(-(zr + bias.astype(np.float64))))
+    got = np.asarray(y.val().get().data, np.float64).reshape(M, N)
+    # the sigmoid's slope is at most 1/4: an error of 1e-4 |z|max in z moves y by less than that
+    assert np.abs(got - yr).max() < 1e-4 * max(1.0, np.abs(zr).max())
+    if keep_product:
+        gz = np.asarray(z.val().get().data, np.float64).reshape(M, N)
+        assert np.abs(gz - zr).max() / np.abs(zr).max() < 2e-5
+
+
+def test_epilogue_agrees_with_the_unfused_program_and_the_oracle():
+    """relu-like chain with a saved value (x * (x > 0)) and a squared product (x * x): chains that need the running
+    value twice."""
+    M, K, N = 320, 1536, 200
+    a, b, A64, B64 = _operands(M, K, N, False, False)
+    bias = RNG.standard_normal(N).astype(np.float32)
+
+    def prog(dev):
+        ad.set_device(dev)
+        ad.eager_dep_opt()
+        A, B = _tensors(a, b, M, K, N, False, False)
+        z = ad.dot(A, B) + ad.tensor(bias, [N])
+        y = (z * z).forward()
+        y.keep()
+        ad.execute()
+        return {"y": y.get()}
+    want = prog(oracle())
+    got = prog(b200())
+    assert "save" in b200().dump_plan()
+    assert_rel("y", got["y"], want["y"], 1e-4)
+
+
+@pytest.mark.parametrize("kind", ["tc", "simt"])
+@pytest.mark.parametrize("B,K2,N", [(4096, 512, 384), (8192, 256, 256), (3000, 200, 1000), (65536, 128, 256), (512, 640, 520)])
+def test_sgd_update_runs_in_the_epilogue(B, K2, N, kind):
+    """`W += -1 * (lr * dot(x^T, g))`: the gradient is never written; long k loops add chunk after chunk (and range
+    after range, when k is split over the SMs) straight into W, which must not be cleared first."""
+    if kind == "simt" and B * K2 * N > 1 << 28:
+        pytest.skip("CUDA-core kernel: small cases only")
+    x = RNG.standard_normal(B * K2).astype(np.float32)
+    g = (RNG.standard_normal(B * N) / np.sqrt(B)).astype(np.float32)
+    w0 = RNG.standard_normal(K2 * N).astype(np.float32)
+    lr = 0.25
+    dev = _device(kind)
+    ad.set_device(dev)
+    ad.eager_dep_opt()
+    w = ad.tensor(w0, [K2, N])
+    X = ad.tensor(x, [B, K2])
+    G = ad.tensor(g, [B, N])
+    w += -1.0 * (lr * ad.dot(X.t(), G))
+    w.forward()
+    w.val().keep()
+    ad.execute()
+    plan = dev.dump_plan()
+    assert "+= product" in plan, plan
+    assert dev.stats()["kernel_launches"] <= 2       # the dot product (and the clearing it must NOT do is a memset, not a kernel)
+    ref = w0.reshape(K2, N).astype(np.float64) - lr * (x.reshape(B, K2).astype(np.float64).T @ g.reshape(B, N).astype(np.float64))
+    got = np.asarray(w.val().get().data, np.float64).reshape(K2, N)
+    assert np.abs(got - ref).max() / np.abs(ref).max() < 2e-5
+
+
+@pytest.mark.parametrize("B,K2,N", [(4096, 512, 384), (16384, 256, 256)])
+def test_scaled_product_is_written_directly(B, K2, N):
+    """`t = -1 * (lr * dot(x^T, g))` kept as a tensor of its own (what an all-reduce consumes): no scale pass."""
+    x = RNG.standard_normal(B * K2).astype(np.float32)
+    g = (RNG.standard_normal(B * N) / np.sqrt(B)).astype(np.float32)
+    dev = b200()
+    ad.set_device(dev)
+    ad.eager_dep_opt()
+    t = (-1.0 * (0.5 * ad.dot(ad.tensor(x, [B, K2]).t(), ad.tensor(g, [B, N])))).forward()
+    t.keep()
+    ad.execute()
+    assert "= product ; *" in dev.dump_plan(), dev.dump_plan()
+    assert dev.stats()["kernel_launches"] == 1
+    ref = -0.5 * (x.reshape(B, K2).astype(np.float64).T @ g.reshape(B, N).astype(np.float64))
+    got = np.asarray(t.get().data, np.float64).reshape(K2, N)
+    assert np.abs(got - ref).max() / np.abs(ref).max() < 2e-5
