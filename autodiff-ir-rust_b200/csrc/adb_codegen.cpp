@@ -35,90 +35,10 @@ thread_local bool g_exact_div = false;
 // 1/x and sqrt(x) through the special-function unit: rcp.approx.f32 / sqrt.approx.f32 keep subnormal inputs and
 // results and are within 1 ulp, inside the 2-ulp bound the element-wise primitives are held to; the correctly
 // rounded forms cost 10 and 11 issue slots per element in kernels that are issue-bound
-// Helper functions spliced in front of every generated kernel.
-//
-// 1/x and sqrt(x) go through the special-function unit: rcp.approx.f32 / sqrt.approx.f32 keep subnormal inputs and
-// results and are within 1 ulp, inside the 2-ulp bound the element-wise primitives are held to; the correctly
-// rounded forms cost 10 and 11 issue slots per element in kernels that are issue-bound.
-//
-// Two lanes at a time: sm_100 has fp32 instructions that work on a pair of values held in a 64-bit register
-// (add / mul / fma .f32x2, each lane rounded to nearest exactly like the scalar form).  The fused kernels are bound by
-// instruction issue, not by memory, so the four lanes of a 128-bit access are carried as two such pairs and every
-// + and * costs half an issue slot per element.
-//
-// Sine: Cody-Waite reduction by pi/2 in three parts (the first product cancels exactly against x, the other two are
-// single fused roundings), then a degree-7 odd polynomial for sin or a degree-8 even one for cos on [-pi/4, pi/4],
-// chosen by the quadrant.  Within 1.7 ulp of the true value for |x| <= 2^20 (CUDA's sinf: 2 ulp), at about half the
-// issue slots; larger arguments, infinities and NaN take CUDA's sinf.
-std::string helpers() {
-    std::string h;
-    if (!g_exact_div)
-        h += "__device__ __forceinline__ float adb_rcp(float x) { float r; asm(\"rcp.approx.f32 %0, %1;\" : \"=f\"(r) : \"f\"(x)); return r; }\n"
-             "__device__ __forceinline__ float adb_sqrt(float x) { float r; asm(\"sqrt.approx.f32 %0, %1;\" : \"=f\"(r) : \"f\"(x)); return r; }\n";
-    h += R"ADB(typedef unsigned long long adb_f2;   // two fp32 lanes in one 64-bit register
-__device__ __forceinline__ adb_f2 adb_pack(float a, float b) { adb_f2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b)); return r; }
-__device__ __forceinline__ float adb_lo(adb_f2 v) { float a, b; asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); return a; }
-__device__ __forceinline__ float adb_hi(adb_f2 v) { float a, b; asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); return b; }
-__device__ __forceinline__ adb_f2 adb_add2(adb_f2 a, adb_f2 b) { adb_f2 r; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
-__device__ __forceinline__ adb_f2 adb_mul2(adb_f2 a, adb_f2 b) { adb_f2 r; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
-__device__ __forceinline__ adb_f2 adb_fma2(adb_f2 a, adb_f2 b, adb_f2 c) { adb_f2 r; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c)); return r; }
-#define ADB_BOTH(bits) ((adb_f2(bits) << 32) | adb_f2(bits))
-// 2/pi, pi/2 in three parts, 1.5 * 2^23 (adding it rounds to the nearest integer and leaves that integer in the low bits)
-#define ADB_2OPI 0x3f22f983u
-#define ADB_HPA 0x3fc90fdbu
-#define ADB_HPB 0xb33bbd2eu
-#define ADB_HPC 0xa6f72cedu
-#define ADB_MAGIC 0x4b400000u
-#define ADB_NMAGIC 0xcb400000u
-// sin r = r + r^3 (S0 + S1 r^2 + S2 r^4),  cos r = 1 + r^2 (D0 + D1 r^2 + D2 r^4 + D3 r^6)  on |r| <= pi/4
-#define ADB_S0 0xbe2aaaa3u
-#define ADB_S1 0x3c088397u
-#define ADB_S2 0xb94c9fb6u
-#define ADB_D0 0xbf000000u
-#define ADB_D1 0x3d2aaa9eu
-#define ADB_D2 0xbab603efu
-#define ADB_D3 0x37cc88ffu
-__device__ __forceinline__ float adb_sin_finish(float rs, float rc, unsigned q) {
-    const float y = (q & 1u) ? rc : rs;
-    return __uint_as_float(__float_as_uint(y) ^ ((q << 30) & 0x80000000u));
-}
-__device__ __forceinline__ float adb_sin(float x) {
-    if (!(fabsf(x) <= 1048576.0f)) return sinf(x);
-    const float qf = __fmaf_rn(x, __uint_as_float(ADB_2OPI), __uint_as_float(ADB_MAGIC));
-    const float nq = __fadd_rn(__uint_as_float(ADB_MAGIC), -qf);
-    float r = __fmaf_rn(nq, __uint_as_float(ADB_HPA), x);
-    r = __fmaf_rn(nq, __uint_as_float(ADB_HPB), r);
-    r = __fmaf_rn(nq, __uint_as_float(ADB_HPC), r);
-    const float s = __fmul_rn(r, r);
-    float ps = __fmaf_rn(__uint_as_float(ADB_S2), s, __uint_as_float(ADB_S1));
-    ps = __fmaf_rn(ps, s, __uint_as_float(ADB_S0));
-    const float rs = __fmaf_rn(__fmul_rn(s, r), ps, r);
-    float pc = __fmaf_rn(__uint_as_float(ADB_D3), s, __uint_as_float(ADB_D2));
-    pc = __fmaf_rn(pc, s, __uint_as_float(ADB_D1));
-    pc = __fmaf_rn(pc, s, __uint_as_float(ADB_D0));
-    const float rc = __fmaf_rn(s, pc, 1.0f);
-    return adb_sin_finish(rs, rc, __float_as_uint(qf));
-}
-__device__ __forceinline__ adb_f2 adb_sin2(adb_f2 x) {
-    const float x0 = adb_lo(x), x1 = adb_hi(x);
-    if (!(fmaxf(fabsf(x0), fabsf(x1)) <= 1048576.0f) || x0 != x0 || x1 != x1) return adb_pack(sinf(x0), sinf(x1));
-    const adb_f2 qf = adb_fma2(x, ADB_BOTH(ADB_2OPI), ADB_BOTH(ADB_MAGIC));
-    const adb_f2 nq = adb_add2(qf, ADB_BOTH(ADB_NMAGIC)) ^ 0x8000000080000000ull;
-    adb_f2 r = adb_fma2(nq, ADB_BOTH(ADB_HPA), x);
-    r = adb_fma2(nq, ADB_BOTH(ADB_HPB), r);
-    r = adb_fma2(nq, ADB_BOTH(ADB_HPC), r);
-    const adb_f2 s = adb_mul2(r, r);
-    adb_f2 ps = adb_fma2(ADB_BOTH(ADB_S2), s, ADB_BOTH(ADB_S1));
-    ps = adb_fma2(ps, s, ADB_BOTH(ADB_S0));
-    const adb_f2 rs = adb_fma2(adb_mul2(s, r), ps, r);
-    adb_f2 pc = adb_fma2(ADB_BOTH(ADB_D3), s, ADB_BOTH(ADB_D2));
-    pc = adb_fma2(pc, s, ADB_BOTH(ADB_D1));
-    pc = adb_fma2(pc, s, ADB_BOTH(ADB_D0));
-    const adb_f2 rc = adb_fma2(s, pc, ADB_BOTH(0x3f800000u));
-    return adb_pack(adb_sin_finish(adb_lo(rs), adb_lo(rc), (unsigned)qf), adb_sin_finish(adb_hi(rs), adb_hi(rc), (unsigned)(qf >> 32)));
-}
-)ADB";
-    return h;
+const char* helpers() {
+    if (g_exact_div) return "";
+    return "__device__ __forceinline__ float adb_rcp(float x) { float r; asm(\"rcp.approx.f32 %0, %1;\" : \"=f\"(r) : \"f\"(x)); return r; }\n"
+           "__device__ __forceinline__ float adb_sqrt(float x) { float r; asm(\"sqrt.approx.f32 %0, %1;\" : \"=f\"(r) : \"f\"(x)); return r; }\n";
 }
 
 std::string hexf(float v) {
@@ -185,74 +105,41 @@ Access classify(const std::vector<Sub>& subs, int64_t offset, int vec, bool is_s
 // can the innermost digit of every operand hold 4 consecutive lanes?
 bool lanes_ok(const std::vector<Sub>& subs) { return subs.empty() || subs.back().size % 4 == 0; }
 
-// 64-bit literal holding the same fp32 constant in both lanes
-std::string hex2(float v) {
-    uint32_t bits;
-    std::memcpy(&bits, &v, 4);
-    char buf[48];
-    std::snprintf(buf, sizeof buf, "0x%08x%08xull", bits, bits);
-    return buf;
-}
-
-std::string scalar_op(const Ssa& s, const std::string& a, const std::string& b) {
-    switch (s.op) {
-    case E_ADD: return "__fadd_rn(" + a + ", " + b + ")";
-    case E_MUL: return "__fmul_rn(" + a + ", " + b + ")";
-    case E_EXP2: return "exp2f(" + a + ")";
-    case E_LOG2: return "log2f(" + a + ")";
-    case E_SIN: return "adb_sin(" + a + ")";
-    case E_RECIP: return std::string(g_exact_div ? "__frcp_rn(" : "adb_rcp(") + a + ")";
-    case E_SQRT: return std::string(g_exact_div ? "__fsqrt_rn(fabsf(" : "adb_sqrt(fabsf(") + a + "))";
-    case E_EQZ: return "(" + a + " == 0.0f ? 1.0f : 0.0f)";
-    case E_GTZ: return "(" + a + " > 0.0f ? 1.0f : 0.0f)";
-    case E_LTZ: return "(" + a + " < 0.0f ? 1.0f : 0.0f)";
-    }
-    return "0.0f";
-}
-
-// The straight-line body.  Every value i exists per lane as `v<i>_<l>`; with four lanes the additions,
-// multiplications and sines work on lane pairs (`p<i>_0` = lanes 0, 1 and `p<i>_1` = lanes 2, 3), the per-lane names
-// are views of the pairs.
 void emit_ssa(std::ostringstream& o, const KernelSpec& k, int vec, const std::vector<std::string>& load_names,
               const std::vector<Access>& acc, const char* ind, const std::vector<char>* need = nullptr) {
     static const char L[4] = {'x', 'y', 'z', 'w'};
-    const bool pairs = vec == 4;
     for (size_t i = 0; i < k.ssa.size(); i++) {
         if (need && !(*need)[i]) continue;
         const Ssa& s = k.ssa[i];
-        const std::string vi = "v" + std::to_string(i) + "_", pi = "p" + std::to_string(i) + "_";
-        auto lane_value = [&](int l) -> std::string {
+        for (int l = 0; l < vec; l++) {
+            std::string lhs = "v" + std::to_string(i) + "_" + std::to_string(l);
+            o << ind << "const float " << lhs << " = ";
             if (s.kind == Ssa::LOAD) {
                 const std::string& nm = load_names[s.operand];
-                if (vec == 1 || acc[s.operand].mode == Access::SCALAR) return nm;
-                if (acc[s.operand].mode == Access::VEC4) return nm + "." + L[l];
-                return nm + "_" + std::to_string(l);
-            }
-            if (s.kind == Ssa::CONST) return hexf(s.c);
-            if (s.kind == Ssa::RED) return "red" + std::to_string(s.operand);
-            return scalar_op(s, "v" + std::to_string(s.a) + "_" + std::to_string(l), s.b >= 0 ? "v" + std::to_string(s.b) + "_" + std::to_string(l) : "");
-        };
-        if (!pairs) {
-            for (int l = 0; l < vec; l++) o << ind << "const float " << vi << l << " = " << lane_value(l) << ";\n";
-            continue;
-        }
-        const bool pair_op = s.kind == Ssa::OP && (s.op == E_ADD || s.op == E_MUL || s.op == E_SIN);
-        for (int h = 0; h < 2; h++) {
-            const std::string a = "p" + std::to_string(s.a) + "_" + std::to_string(h), b = "p" + std::to_string(s.b) + "_" + std::to_string(h);
-            if (pair_op) {
-                o << ind << "const adb_f2 " << pi << h << " = ";
-                if (s.op == E_ADD) o << "adb_add2(" << a << ", " << b << ")";
-                else if (s.op == E_MUL) o << "adb_mul2(" << a << ", " << b << ")";
-                else o << "adb_sin2(" << a << ")";
-                o << ";\n";
-                o << ind << "const float " << vi << 2 * h << " = adb_lo(" << pi << h << "), " << vi << 2 * h + 1 << " = adb_hi(" << pi << h << ");\n";
+                if (vec == 1 || acc[s.operand].mode == Access::SCALAR) o << nm;
+                else if (acc[s.operand].mode == Access::VEC4) o << nm << "." << L[l];
+                else o << nm << "_" << l;
             } else if (s.kind == Ssa::CONST) {
-                o << ind << "const adb_f2 " << pi << h << " = " << hex2(s.c) << ";\n";
-                o << ind << "const float " << vi << 2 * h << " = " << hexf(s.c) << ", " << vi << 2 * h + 1 << " = " << hexf(s.c) << ";\n";
+                o << hexf(s.c);
+            } else if (s.kind == Ssa::RED) {
+                o << "red" << s.operand;
             } else {
-                o << ind << "const float " << vi << 2 * h << " = " << lane_value(2 * h) << ", " << vi << 2 * h + 1 << " = " << lane_value(2 * h + 1) << ";\n";
-                o << ind << "const adb_f2 " << pi << h << " = adb_pack(" << vi << 2 * h << ", " << vi << 2 * h + 1 << ");\n";
+                std::string a = "v" + std::to_string(s.a) + "_" + std::to_string(l);
+                std::string b = s.b >= 0 ? "v" + std::to_string(s.b) + "_" + std::to_string(l) : "";
+                switch (s.op) {
+                case E_ADD: o << "__fadd_rn(" << a << ", " << b << ")"; break;
+                case E_MUL: o << "__fmul_rn(" << a << ", " << b << ")"; break;
+                case E_EXP2: o << "exp2f(" << a << ")"; break;
+                case E_LOG2: o << "log2f(" << a << ")"; break;
+                case E_SIN: o << "sinf(" << a << ")"; break;
+                case E_RECIP: o << (g_exact_div ? "__frcp_rn(" : "adb_rcp(") << a << ")"; break;
+                case E_SQRT: o << (g_exact_div ? "__fsqrt_rn(fabsf(" : "adb_sqrt(fabsf(") << a << "))"; break;
+                case E_EQZ: o << "(" << a << " == 0.0f ? 1.0f : 0.0f)"; break;
+                case E_GTZ: o << "(" << a << " > 0.0f ? 1.0f : 0.0f)"; break;
+                case E_LTZ: o << "(" << a << " < 0.0f ? 1.0f : 0.0f)"; break;
+                }
             }
+            o << ";\n";
         }
     }
 }
