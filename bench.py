@@ -39,6 +39,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+emit = print   # replaced in main(): writes to the real stdout
 METRIC = "mlp_train_steps_per_s"
 UNIT = "steps/s"
 BATCH = 65536
@@ -327,14 +328,17 @@ def run_ours(args):
         line["other_configs"] = bench_small_configs(adb, pk)
         line["cpu_baseline"] = cpu_baseline_c4(adb, widths, batch, args)
     if rank == 0:
-        print(json.dumps(line))
+        emit(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 
 
-def parity_vs_one_gpu(adb, args, rank, world, new_handle, barrier, pbatch=8192, steps=2):
-    """The N-GPU path against one GPU on identical data: `steps` training steps at global batch `pbatch` (full widths),
-    sharded over all ranks, then once more on rank 0's GPU alone.  Only the order of the batch summations differs."""
+def parity_vs_one_gpu(adb, args, rank, world, new_handle, barrier, pbatch=16384, steps=2, lr=1.0):
+    """The N-GPU path against one GPU on identical data: `steps` training steps at global batch `pbatch` (full widths;
+    a batch that differs from every layer width, so that batch tensors are recognised by their shape), sharded over all
+    ranks, then once more on rank 0's GPU alone.  Only the order of the batch summations differs.  The learning rate is
+    1.0 instead of the benchmark's 1e-3: at 1e-3 two steps move the first layers by about one ulp and the comparison of
+    the updates would be a comparison of rounding noise."""
     import torch
     import torch.distributed as dist
     cfg = adb.configs
@@ -363,7 +367,7 @@ def parity_vs_one_gpu(adb, args, rank, world, new_handle, barrier, pbatch=8192, 
             net.insert(nn.LinearWithWeights(ws[i], bs[i]))
             if i < L - 1:
                 net.insert(nn.Sigmoid())
-        opt = nn.SGD(net.params(), 1e-3)
+        opt = nn.SGD(net.params(), lr)
         box = {}
 
         def body(_):
@@ -391,7 +395,7 @@ def parity_vs_one_gpu(adb, args, rank, world, new_handle, barrier, pbatch=8192, 
         one = run(solo, 0, pbatch, None)
         solo.close()
         small0 = {k: np.asarray(small[k], np.float64) for k in ("w3", "b3", "b0")}
-        out = {"batch": pbatch, "steps": steps, "loss_n": float(many["loss"][0]), "loss_1": float(one["loss"][0]),
+        out = {"batch": pbatch, "steps": steps, "lr": lr, "loss_n": float(many["loss"][0]), "loss_1": float(one["loss"][0]),
                "loss_rel": float(abs(many["loss"][0] - one["loss"][0]) / abs(one["loss"][0]))}
         worst = 0.0
         for k in ("w3", "b3", "b0"):
@@ -604,7 +608,7 @@ def run_reference(args):
                        "global_batch": args.batch},
             "cpu_baseline": best,
             "e2e": {"value": best["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line))
+    emit(json.dumps(line))
 
 
 def run_case(args):
@@ -691,9 +695,9 @@ def run_case(args):
             out["top_GBps"] = st["top_bytes"] / st["top_ms"] / 1e6
         if st["elw_ms"] > 0:
             out["elw_GBps"] = st["elw_bytes"] / st["elw_ms"] / 1e6
-        print(json.dumps(out))
+        emit(json.dumps(out))
     if args.dump_plan:
-        print(dev.dump_plan())
+        emit(dev.dump_plan())
     dev.close()
 
 
@@ -722,6 +726,17 @@ def main():
     ap.add_argument("--no-profile-flag", action="store_true")
     ap.add_argument("--dump-plan", action="store_true")
     args = ap.parse_args()
+    # Native libraries write to file descriptor 1 behind Python's back (NCCL announces its version there when a
+    # communicator is created); stdout must carry the one JSON line and nothing else, so everything is sent to stderr
+    # while the benchmark runs and only `emit` writes to the real stdout.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    global emit
+
+    def emit(line):
+        sys.stdout.flush()
+        os.write(real_stdout, (line + "\n").encode())
     if args.case:
         if args.batch is None:
             args.batch = 64
