@@ -200,8 +200,98 @@ int elw_vec_impl(const KernelSpec& k) {
 
 void gen_elw_red(KernelSpec& k);
 
+// Materialised axis swap (`x.t().contigious()`, `x.permute(0, 2, 1)` made contiguous, with or without element-wise work
+// on the way): the reference's Movement kernel reads with the permuted index expression, one scattered 4-byte load per
+// element (src/devices/opencl/kernels/movement.rs:7-46).  When the one input is contiguous along an axis P that is not
+// the output's innermost axis Q, a 64 x 64 tile of the (P, Q) plane goes through shared memory instead: 128-bit loads
+// along P, 128-bit stores along Q, every other axis is a batch index.  Returns false when the kernel is not of that form.
+bool gen_transpose(KernelSpec& k) {
+    if (k.ins.size() != 1 || k.outs.empty() || !k.reds.empty() || k.n < (int64_t(1) << 16)) return false;
+    for (auto& v : k.ssa)
+        if (v.kind == Ssa::RED) return false;
+    std::vector<Sub> full;
+    full.push_back({k.n, 1});
+    for (auto& o : k.outs) {
+        std::vector<Sub> d = o.dst.subs;
+        canon_subs(d);
+        if (d != full) return false;
+    }
+    const std::vector<Sub>& dg = k.ins[0].subs;   // digits over the output's linear index, outermost first
+    if (dg.size() < 2) return false;
+    const size_t qi = dg.size() - 1;
+    const int64_t Q = dg[qi].size, SQ = dg[qi].stride;
+    if (SQ <= 1 || Q < 32) return false;
+    size_t pi = dg.size();
+    for (size_t t = 0; t + 1 < dg.size(); t++)
+        if (dg[t].stride == 1 && dg[t].size >= 32) pi = t;
+    if (pi == dg.size()) return false;
+    const int64_t P = dg[pi].size;
+    // 128-bit accesses need 4-element alignment of every row start on both sides
+    std::vector<int64_t> ostride(dg.size(), 1);
+    for (size_t t = dg.size() - 1; t-- > 0;) ostride[t] = ostride[t + 1] * dg[t + 1].size;
+    bool vec_ok = P % 4 == 0 && Q % 4 == 0 && SQ % 4 == 0 && k.ins[0].offset % 4 == 0 && ostride[pi] % 4 == 0;
+    for (size_t t = 0; t < dg.size(); t++)
+        if (t != pi && t != qi && (dg[t].stride % 4 || ostride[t] % 4)) vec_ok = false;
+    for (auto& o : k.outs)
+        if (o.dst.offset % 4) vec_ok = false;
+    if (!vec_ok) return false;
+    int64_t batch = 1;
+    for (size_t t = 0; t < dg.size(); t++)
+        if (t != pi && t != qi) batch *= dg[t].size;
+    const int64_t tiles_p = (P + 63) / 64, tiles_q = (Q + 63) / 64;
+    k.tr_tiles = tiles_p * tiles_q * batch;
+    k.vec = 4;
+    k.threads = 256;
+    k.wide_index = true;
+
+    std::ostringstream o;
+    o << helpers() << "struct Args { const float* in[1]; float* out[" << k.outs.size() << "]; long long n; };\n";
+    o << "extern \"C\" __global__ void __launch_bounds__(256) @ENTRY@(const __grid_constant__ Args a) {\n";
+    // tile[q][p]; the 128-bit column slots of row q are rotated by an XOR with (q / 4) % 8, so rows stay 128-bit aligned
+    // for the writes and the transposed reads (rows 4 apart, same column) spread over the banks (2-way at worst)
+    o << "  __shared__ __align__(16) float tile[64][64];\n";
+    o << "  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;   // 16 x 16 threads, 4 values each way\n";
+    o << "  for (long long t = blockIdx.x; t < " << k.tr_tiles << "ll; t += gridDim.x) {\n";
+    o << "    long long r = t;\n";
+    o << "    const int q0 = int(r % " << tiles_q << ") * 64; r /= " << tiles_q << ";\n";
+    o << "    const int p0 = int(r % " << tiles_p << ") * 64; r /= " << tiles_p << ";\n";
+    o << "    long long ib = 0, ob = 0;\n";
+    for (size_t t = dg.size(); t-- > 0;) {
+        if (t == pi || t == qi) continue;
+        o << "    { const long long d = r % " << dg[t].size << "; r /= " << dg[t].size << "; ib += d * " << dg[t].stride << "ll; ob += d * "
+          << ostride[t] << "ll; }\n";
+    }
+    // read: thread (tx, ty) loads 4 consecutive p for rows q = ty, ty + 16, ...
+    o << "    for (int j = ty; j < 64; j += 16) {\n";
+    o << "      const int q = q0 + j, p = p0 + tx * 4;\n";
+    o << "      if (q < " << Q << " && p < " << P << ")\n";
+    o << "        *reinterpret_cast<float4*>(&tile[j][(tx * 4) ^ (((j >> 2) & 7) << 2)]) = *reinterpret_cast<const float4*>(a.in[0] + ib + (long long)q * " << SQ << "ll + p);\n";
+    o << "    }\n";
+    o << "    __syncthreads();\n";
+    // write: thread (tx, ty) stores 4 consecutive q for rows p = ty, ty + 16, ...
+    o << "    for (int j = ty; j < 64; j += 16) {\n";
+    o << "      const int p = p0 + j, q = q0 + tx * 4;\n";
+    o << "      if (p < " << P << " && q < " << Q << ") {\n";
+    for (int l = 0; l < 4; l++) o << "        const float t_" << l << " = tile[tx * 4 + " << l << "][j ^ ((tx & 7) << 2)];\n";
+    std::vector<std::string> names{"t"};
+    std::vector<Access> acc(1);
+    acc[0].mode = Access::GATHER;   // emit_ssa reads lane l of a gathered operand as <name>_<l>
+    emit_ssa(o, k, 4, names, acc, "        ");
+    for (size_t i = 0; i < k.outs.size(); i++) {
+        const std::string v = "v" + std::to_string(k.outs[i].ssa);
+        o << "        *reinterpret_cast<float4*>(a.out[" << i << "] + ob + (long long)p * " << ostride[pi] << "ll + q) = make_float4(" << v << "_0, " << v
+          << "_1, " << v << "_2, " << v << "_3);\n";
+    }
+    o << "      }\n    }\n";
+    o << "    __syncthreads();\n";
+    o << "  }\n}\n";
+    finish(k, o.str(), "adb_transpose");
+    return true;
+}
+
 void gen_elw(KernelSpec& k) {
     if (!k.reds.empty()) { gen_elw_red(k); return; }
+    if (gen_transpose(k)) return;
     std::vector<const Operand*> ops;
     for (auto& i : k.ins) ops.push_back(&i);
     for (auto& o : k.outs) ops.push_back(&o.dst);

@@ -940,20 +940,38 @@ static bool tma_ok(const float* p, long long unit_len, long long other_stride) {
     return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && other_stride % 4 == 0 && other_stride > 0;
 }
 
-// Few tiles and a long k loop: cut k so that every SM (pair) has work.  Ranges are whole 1024-element accumulation
-// chunks; the partial products meet in a zeroed C through the adds the epilogue performs anyway.
+// Few tiles, or a last wave that leaves most SMs (pairs) idle, and a long k loop: cut k into ranges that different
+// workers accumulate.  Ranges are whole 1024-element accumulation chunks; the partial products meet in a zeroed C through
+// the adds the epilogue performs anyway.  The split is chosen by a small cost model: waves of units times the k-blocks
+// of one unit, plus what the extra passes over C cost; it must beat the unsplit launch by 8 % to be taken.
 static bool plan_k_split(tc::Params& p, long long tiles, int workers, const GemmArgs& a, cudaStream_t stream, std::string& err) {
     using namespace tc;
     p.k_splits = 1;
     p.kb_per_split = p.k_blocks;
     // a chain that runs on the finished sum needs one owner per tile
     if (a.epi.mode == 2) return true;
-    if (tiles * 2 > workers || p.k_blocks < 2 * CHUNK_KB) return true;
-    const long long want = workers / tiles;
-    long long per = (p.k_blocks + want - 1) / want;
-    per = (per + CHUNK_KB - 1) / CHUNK_KB * CHUNK_KB;
-    p.kb_per_split = (int)per;
-    p.k_splits = (int)((p.k_blocks + per - 1) / per);
+    if (p.k_blocks < 2 * CHUNK_KB || workers <= 0) return true;
+    auto cost = [&](long long per, long long splits) {
+        const long long units = tiles * splits, waves = (units + workers - 1) / workers;
+        // every extra range adds one more read-modify-write of its C tile at the L2 (~2 k-blocks of time) and the launch
+        // gains a memset
+        return double(waves) * double(per) + (splits > 1 ? 2.0 * double(splits) + 8.0 : 0.0);
+    };
+    const double base = cost(p.k_blocks, 1);
+    double best = base;
+    long long best_per = p.k_blocks;
+    const long long max_splits = std::min<long long>(p.k_blocks / CHUNK_KB, 64);
+    for (long long want = 2; want <= max_splits; want++) {
+        long long per = (p.k_blocks + want - 1) / want;
+        per = (per + CHUNK_KB - 1) / CHUNK_KB * CHUNK_KB;
+        const long long splits = (p.k_blocks + per - 1) / per;
+        if (splits < 2) continue;
+        const double c = cost(per, splits);
+        if (c < best) { best = c; best_per = per; }
+    }
+    if (best > 0.92 * base) return true;
+    p.kb_per_split = (int)best_per;
+    p.k_splits = (int)((p.k_blocks + best_per - 1) / best_per);
     // (a product that is added to what C holds must not clear it: every range adds anyway)
     if (p.k_splits > 1 && !(a.epi.mode == 1 && a.epi.accumulate) &&
         cudaMemsetAsync(a.C, 0, size_t(a.M) * size_t(a.N) * sizeof(float), stream) != cudaSuccess) {

@@ -1136,6 +1136,34 @@ class Lowerer {
         return {m->buf, 0, n->shape[1], 1};
     }
 
+    // The tensor-core kernels fetch operands with TMA, which wants one unit stride and the other stride a multiple of four
+    // elements (16 bytes).  A big operand that misses that (1001 columns, a slice starting at an odd column) is copied
+    // once into a temporary whose rows are padded to a multiple of four; the padding is never read (the tensor map
+    // knows the true extent).  Without it the product would fall back to the CUDA-core kernel, ten times slower.
+    MatOperand aligned_operand(Node* n, const MatOperand& m, int64_t flops) {
+        const bool unit_r = m.rs == 1, unit_c = m.cs == 1;
+        const int64_t other = unit_c ? m.rs : m.cs;
+        const bool ok = (unit_r || unit_c) && other % 4 == 0 && m.off % 4 == 0;
+        if (ok || flops < (int64_t(1) << 24) || opt_.no_fusion) return m;
+        n = g_.canon(n);
+        const int64_t rows = n->shape[0], cols = n->shape[1];
+        if (rows < 32 || cols < 8) return m;
+        // keep the operand's majorness when it has one (a transposed view stays a transposed copy: no strided gather)
+        const bool col_major = unit_r && !unit_c;
+        const int64_t ld = ((col_major ? rows : cols) + 3) / 4 * 4;
+        const int buf = temp_buffer(col_major ? cols * ld : rows * ld);
+        View v;
+        v.offset = 0;
+        v.dims.resize(2);
+        if (rows > 1) v.dims[0].push_back({rows, col_major ? 1 : ld});
+        if (cols > 1) v.dims[1].push_back({cols, col_major ? ld : 1});
+        std::vector<StoreTask> tasks;
+        collect_stores(n, buf, v, tasks);
+        emit_stores(tasks);
+        g_.buf_version[buf]++;
+        return {buf, 0, col_major ? 1 : ld, col_major ? ld : 1};
+    }
+
     void lower_dot(const Cmd& c) {
         Node* a = resolve(c.a);
         Node* b = resolve(c.b);
@@ -1155,6 +1183,10 @@ class Lowerer {
         }
         MatOperand ma = matrix_operand(a);
         MatOperand mb = matrix_operand(b);
+        if (M >= 32 && N >= 32 && K >= 8) {
+            ma = aligned_operand(a, ma, M * N * K);
+            mb = aligned_operand(b, mb, M * N * K);
+        }
         Shape rs{M, N};
         int buf = result_buffer(c.res, rs);
         // `DotProduct v w -> v`: the kernels read A and B while other tiles of C are already being written (and a

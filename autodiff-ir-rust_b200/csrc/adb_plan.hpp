@@ -91,6 +91,7 @@ struct KernelSpec {
     int jit2 = -1;          // REDUCE: second-pass kernel
     int scratch = -1;       // REDUCE two-pass: buffer holding the partial sums
     bool wide_index = false;
+    int64_t tr_tiles = 0;   // ELW generated as a shared-memory tiled axis swap: number of 64 x 64 tiles (one block each, grid-stride)
 };
 
 struct StepBlock;

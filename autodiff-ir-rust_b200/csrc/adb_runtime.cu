@@ -293,6 +293,8 @@ class Executor {
             // element-wise pass with side sums: 2-d launch over [p2, q2]
             grid.x = unsigned((k.q2 + 32 * k.vec - 1) / (32 * k.vec));
             grid.y = unsigned((k.p2 + k.row_chunk - 1) / k.row_chunk);
+        } else if (k.type == KernelSpec::ELW && k.tr_tiles > 0) {
+            grid.x = unsigned(std::max<int64_t>(1, std::min<int64_t>(k.tr_tiles, cap * 4)));
         } else if (k.type == KernelSpec::ELW) {
             int64_t nv = k.n / k.vec;
             grid.x = unsigned(std::max<int64_t>(1, std::min<int64_t>((nv + 255) / 256, cap)));

@@ -144,3 +144,18 @@ def test_a_dot_kernel_that_gave_up_is_reported_and_the_handle_stays_usable():
             np.testing.assert_array_equal(np.asarray(again[k].data), np.asarray(good[k].data))
     finally:
         dev.close()
+
+
+@pytest.mark.parametrize("M,K,N", [(512, 1024, 1001), (384, 1001, 512), (1001, 515, 260)])
+def test_rows_that_are_not_a_multiple_of_four_are_padded_not_demoted(M, K, N):
+    """1001 columns: TMA cannot fetch rows that start on odd 4-byte boundaries, so the operand is copied once into a
+    temporary with padded rows and the product still runs on the tensor cores (it used to fall back to the CUDA-core
+    kernel)."""
+    a = RNG.standard_normal(M * K).astype(np.float32)
+    b = RNG.standard_normal(K * N).astype(np.float32)
+    dev = _device("pair")
+    got = _dot(dev, a, b, False, False, M, K, N)
+    assert dev.stats()["tc_gemm_launches"] == 1, dev.dump_plan()
+    ref = a.reshape(M, K).astype(np.float64) @ b.reshape(K, N).astype(np.float64)
+    g = np.asarray(got.data, np.float64).reshape(M, N)
+    assert np.abs(g - ref).max() / np.abs(ref).max() < 2e-5

@@ -60,6 +60,26 @@ def test_permute_contiguous(shape, perm):
     np.testing.assert_array_equal(np.asarray(got["p"].data).reshape(got["p"].dim), a.reshape(shape).transpose(perm))
 
 
+@pytest.mark.parametrize("shape,perm", [((512, 768), [1, 0]), ((520, 388), [1, 0]), ((8, 256, 320), [0, 2, 1]), ((128, 64, 96), [2, 0, 1]),
+                                         ((6, 132, 4, 100), [0, 3, 2, 1]), ((96, 2048), [1, 0])])
+def test_large_permutes_go_through_the_tiled_transpose(shape, perm):
+    """Axis swaps of at least 2^16 elements whose source is contiguous along an axis that is not the result's innermost
+    one are copied through 64 x 64 shared-memory tiles (adb_transpose_*), with element-wise work on the way: bit-exact,
+    ragged tile edges included."""
+    from helpers import b200
+    a = rnd(*shape)
+
+    def build():
+        t = ad.tensor(a, list(shape))
+        p = t.permute(perm)
+        return {"p": p.contigious(), "q": (p * 3.0 + 1.0)}
+    want, got = _run(build)
+    assert "adb_transpose_" in b200().dump_plan(), b200().dump_plan()
+    np.testing.assert_array_equal(np.asarray(got["p"].data).reshape(got["p"].dim), a.reshape(shape).transpose(perm))
+    np.testing.assert_array_equal(np.asarray(got["q"].data).reshape(got["q"].dim),
+                                  a.reshape(shape).transpose(perm) * np.float32(3.0) + np.float32(1.0))
+
+
 def test_view_of_permuted_needs_copy():
     a = rnd(6, 10)
 
