@@ -104,6 +104,7 @@ class Lowerer {
         plan_.n_steps = pos_;
         fuse_reductions();
         if (!opt_.no_fusion && !opt_.no_dot_epilogue) fuse_dot_epilogues(plan_.main);
+        if (!opt_.no_fusion) drop_unread_outputs();
         plan_arena();
     }
 
@@ -2275,6 +2276,66 @@ class Lowerer {
                 steps.erase(steps.begin() + long(ei));
             } else
                 prune_kernel(k);
+        }
+    }
+
+    // ------------------------------------------------------------------ outputs nobody reads
+    // A value can be written to a temporary because one consumer needed it in memory and then lose that consumer to a
+    // later pass (or never have had one: the zero padding that Index backward concatenates and a slice cuts away
+    // again).  An element-wise output into a temporary that no step of the whole plan reads is dropped; a kernel that
+    // is left without outputs goes with it.
+    void collect_reads(const StepBlock& blk, std::vector<char>& read) const {
+        std::vector<int> rd, wr;
+        for (auto& st : blk.steps) {
+            step_rw(st, rd, wr);
+            for (int b : rd) read[size_t(b)] = 1;
+            if (st.kind == Step::WHILE) read[size_t(st.cond_buf)] = 1;
+            for (auto& br : st.branches) read[size_t(br.cond_buf)] = 1;
+            if (st.body) collect_reads(*st.body, read);
+            for (auto& br : st.branches) collect_reads(*br.body, read);
+            if (st.else_body) collect_reads(*st.else_body, read);
+        }
+    }
+    bool drop_in_block(StepBlock& blk, const std::vector<char>& read) {
+        bool changed = false;
+        for (auto& st : blk.steps) {
+            if (st.body) changed |= drop_in_block(*st.body, read);
+            for (auto& br : st.branches) changed |= drop_in_block(*br.body, read);
+            if (st.else_body) changed |= drop_in_block(*st.else_body, read);
+        }
+        for (size_t i = 0; i < blk.steps.size();) {
+            Step& st = blk.steps[i];
+            if (st.kind != Step::ELW) { i++; continue; }
+            KernelSpec& k = plan_.kernels[size_t(st.kernel)];
+            if (k.type != KernelSpec::ELW || !k.reds.empty()) { i++; continue; }
+            const size_t before = k.outs.size();
+            for (size_t o = 0; o < k.outs.size();) {
+                const int b = k.outs[o].dst.buf;
+                // (two outputs may share a buffer: the other halves of a concatenation keep it alive through `read`)
+                bool result = plan_.bufs[size_t(b)].external;
+                for (auto& r : plan_.results) result = result || r.buf == b;
+                // (a buffer that lives for the whole program but is neither read by any step nor handed back is as dead
+                //  as a temporary: ids that views of kept tensors refer to get such buffers)
+                if (!read[size_t(b)] && !result) k.outs.erase(k.outs.begin() + long(o));
+                else o++;
+            }
+            if (k.outs.size() == before) { i++; continue; }
+            changed = true;
+            if (k.outs.empty()) {
+                k.dead = true;
+                blk.steps.erase(blk.steps.begin() + long(i));
+            } else {
+                prune_kernel(k);
+                i++;
+            }
+        }
+        return changed;
+    }
+    void drop_unread_outputs() {
+        for (int round = 0; round < 8; round++) {
+            std::vector<char> read(plan_.bufs.size(), 0);
+            collect_reads(plan_.main, read);
+            if (!drop_in_block(plan_.main, read)) break;
         }
     }
 
