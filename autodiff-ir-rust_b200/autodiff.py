@@ -784,6 +784,46 @@ def dot(a: Tensor, b: Tensor) -> Tensor:
     return Tensor(DotProductNode(a, b))
 
 
+class BatchDotNode(Node):
+    """Batched matrix product [B, M, K] x [B, K, N] -> [B, M, N] (IR extension `BatchDot`).  Upstream lists batched
+    matmul as missing (TODO.md:22) and runs attention as one 2-d `dot` per head (src/nn/transformer.rs:10-18); the
+    gradients follow DotProductNode slice by slice: dA = g . B^T, dB = A^T . g with the last two axes swapped."""
+
+    def __init__(self, left, right):
+        self.left, self.right = left, right
+        self._val = None
+
+    def forward(self):
+        v = self.val()
+        if v is not None:
+            return v
+        left, right = self.left.forward(), self.right.forward()
+        assert len(left.dim) == 3 and len(right.dim) == 3, "bmm needs 3d operands"
+        assert left.dim[0] == right.dim[0], "bmm operands differ in their batch size"
+        assert left.dim[2] == right.dim[1], "A's last dimension must equal B's second dimension"
+        id_ = self._val.id if self._val is not None else ir_b_id()
+        ir_b_add(("BatchDot", left.id, right.id, id_))
+        res = Value([left.dim[0], left.dim[1], right.dim[2]], id_)
+        self._val = res.clone()
+        return res
+
+    def dim(self): return [self.left.dim()[0], self.left.dim()[1], self.right.dim()[2]]
+
+    def val(self):
+        if self.left.val() is None or self.right.val() is None:
+            return None
+        return None if self._val is None else self._val.clone()
+
+    def backward(self, grad):
+        g = grad.to_node()
+        self.left.n.backward(bmm(g, self.right.permute([0, 2, 1])).forward())
+        self.right.n.backward(bmm(self.left.permute([0, 2, 1]), g).forward())
+
+
+def bmm(a: Tensor, b: Tensor) -> Tensor:
+    return Tensor(BatchDotNode(a, b))
+
+
 # --------------------------------------------------------------------------------------
 # data-movement nodes (src/graph/data)
 # --------------------------------------------------------------------------------------

@@ -100,9 +100,13 @@ template <int BM, int BN, int BK>
 __global__ void __launch_bounds__(256) adb_dot_simt(const float* __restrict__ A, const float* __restrict__ B,
                                                     float* __restrict__ C, long long M, long long N, long long K,
                                                     long long a_rs, long long a_cs, long long b_rs, long long b_cs,
-                                                    const GemmEpilogue epi) {
+                                                    long long a_bs, long long b_bs, long long c_bs, const GemmEpilogue epi) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Bs[BK][BN + 4];
+    // batched product: one slice per blockIdx.z
+    A += (long long)blockIdx.z * a_bs;
+    B += (long long)blockIdx.z * b_bs;
+    C += (long long)blockIdx.z * c_bs;
     const int tid = threadIdx.x;
     const int tx = tid % 16, ty = tid / 16;
     const long long m0 = (long long)blockIdx.y * BM, n0 = (long long)blockIdx.x * BN;
@@ -981,7 +985,40 @@ static bool plan_k_split(tc::Params& p, long long tiles, int workers, const Gemm
     return true;
 }
 
+static int gemm_launch_one(GemmContext& ctx, const GemmArgs& a, cudaStream_t stream, std::string& err);
+
 int gemm_launch(GemmContext& ctx, const GemmArgs& a, cudaStream_t stream, std::string& err) {
+    if (a.batch <= 1) return gemm_launch_one(ctx, a, stream, err);
+    if (a.M <= 0 || a.N <= 0) return 0;
+    // Batched product.  Slices that are big enough for the tensor-core kernel to pay (and few enough to launch one by
+    // one) run as separate launches; everything else -- the many small products of attention heads -- is one launch of
+    // the CUDA-core kernel with the slice index in blockIdx.z.
+    const bool big = double(a.M) * double(a.N) * double(a.K) >= double(1 << 24) && a.batch <= 64 && !a.force_simt;
+    if (big) {
+        int n = 0;
+        for (int64_t s = 0; s < a.batch; s++) {
+            GemmArgs one = a;
+            one.batch = 1;
+            one.A = a.A + s * a.a_bs;
+            one.B = a.B + s * a.b_bs;
+            one.C = a.C + s * a.c_bs;
+            if (one.epi.out) one.epi.out = a.epi.out + s * a.c_bs;
+            const int r = gemm_launch_one(ctx, one, stream, err);
+            if (r < 0) return r;
+            n += r;
+        }
+        return n;
+    }
+    if (a.batch > 65535) { err = "batched dot product: more than 65535 slices"; return -1; }
+    dim3 grid((unsigned)((a.N + 63) / 64), (unsigned)((a.M + 63) / 64), (unsigned)a.batch);
+    if (grid.y > 65535) { err = "M too large for the SIMT dot kernel"; return -1; }
+    adb_dot_simt<64, 64, 16><<<grid, 256, 0, stream>>>(a.A, a.B, a.C, a.M, a.N, a.K, a.a_rs, a.a_cs, a.b_rs, a.b_cs, a.a_bs, a.b_bs, a.c_bs, a.epi);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { err = cudaGetErrorString(e); return -1; }
+    return 1;
+}
+
+static int gemm_launch_one(GemmContext& ctx, const GemmArgs& a, cudaStream_t stream, std::string& err) {
     if (a.M <= 0 || a.N <= 0) return 0;
     bool use_tc = ctx.tc_ready && !a.force_simt && a.K >= 8 && a.M >= 32 && a.N >= 32 &&
                   (double)a.M * (double)a.N * (double)a.K >= double(1 << 21) && a.M < (1ll << 31) && a.N < (1ll << 31) &&
@@ -1048,7 +1085,7 @@ int gemm_launch(GemmContext& ctx, const GemmArgs& a, cudaStream_t stream, std::s
     }
     dim3 grid((unsigned)((a.N + 63) / 64), (unsigned)((a.M + 63) / 64));
     if (grid.y > 65535) { err = "M too large for the SIMT dot kernel"; return -1; }
-    adb_dot_simt<64, 64, 16><<<grid, 256, 0, stream>>>(a.A, a.B, a.C, a.M, a.N, a.K, a.a_rs, a.a_cs, a.b_rs, a.b_cs, a.epi);
+    adb_dot_simt<64, 64, 16><<<grid, 256, 0, stream>>>(a.A, a.B, a.C, a.M, a.N, a.K, a.a_rs, a.a_cs, a.b_rs, a.b_cs, 0, 0, 0, a.epi);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { err = cudaGetErrorString(e); return -1; }
     return 1;

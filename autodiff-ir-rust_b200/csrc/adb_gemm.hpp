@@ -30,6 +30,7 @@ struct GemmArgs {
     float* C = nullptr;  // row-major [M,N], leading dimension N
     int64_t M = 0, N = 0, K = 0;
     int64_t a_rs = 0, a_cs = 0, b_rs = 0, b_cs = 0;  // element strides of A[m,k] and B[k,n]
+    int64_t batch = 1, a_bs = 0, b_bs = 0, c_bs = 0; // batched product: slices this many elements apart
     bool force_simt = false;
     bool no_pair = false;  // keep the tensor-core kernel on one SM per tile
     int reserve_sms = 0;   // leave this many SMs to a kernel running beside the product (a collective on another stream)

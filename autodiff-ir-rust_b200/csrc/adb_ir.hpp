@@ -19,6 +19,7 @@ enum Op : uint8_t {
     OP_EXP2 = 18, OP_LOG2 = 19, OP_SIN = 20, OP_RECIP = 21, OP_SQRT = 22,
     OP_WHILE = 23, OP_IF = 24, OP_EX = 25, OP_HEADING = 26, OP_ALLREDUCE = 27,
     OP_MAX = 28,  // extension: row maximum of a 2-d tensor, same shape contract as OP_SUM
+    OP_BATCH_DOT = 29,  // extension: [B,M,K] x [B,K,N] -> [B,M,N]
 };
 
 enum PayloadKind : uint8_t { PAYLOAD_INLINE = 0, PAYLOAD_HOST = 1, PAYLOAD_DEVICE = 2 };
@@ -118,7 +119,7 @@ inline void parse_cmd(Reader& r, Program& prog, Cmd& c, int depth) {
         break;
     }
     case OP_CREATE_CONST: c.res = id(); c.cval = r.get<float>(); c.dims = read_dims(r); break;
-    case OP_MUL: case OP_ADD: case OP_DOT: c.a = id(); c.b = id(); c.res = id(); break;
+    case OP_MUL: case OP_ADD: case OP_DOT: case OP_BATCH_DOT: c.a = id(); c.b = id(); c.res = id(); break;
     case OP_MUL_EQ: case OP_ADD_EQ: c.a = id(); c.b = id(); c.res = c.a; break;
     case OP_EQZ: case OP_GTZ: case OP_LTZ: case OP_SUM: case OP_MAX: case OP_CONTIG:
     case OP_EXP2: case OP_LOG2: case OP_SIN: case OP_RECIP: case OP_SQRT:
@@ -219,7 +220,7 @@ inline void write_cmd(Writer& w, const Cmd& c, std::vector<std::pair<size_t, con
         w.put<uint64_t>(c.payload); w.put<uint64_t>(c.count);
         break;
     case OP_CREATE_CONST: w.put<uint32_t>(c.res); w.put<float>(c.cval); w.dims(c.dims); break;
-    case OP_MUL: case OP_ADD: case OP_DOT: w.put<uint32_t>(c.a); w.put<uint32_t>(c.b); w.put<uint32_t>(c.res); break;
+    case OP_MUL: case OP_ADD: case OP_DOT: case OP_BATCH_DOT: w.put<uint32_t>(c.a); w.put<uint32_t>(c.b); w.put<uint32_t>(c.res); break;
     case OP_MUL_EQ: case OP_ADD_EQ: w.put<uint32_t>(c.a); w.put<uint32_t>(c.b); break;
     case OP_EQZ: case OP_GTZ: case OP_LTZ: case OP_SUM: case OP_MAX: case OP_CONTIG:
     case OP_EXP2: case OP_LOG2: case OP_SIN: case OP_RECIP: case OP_SQRT:

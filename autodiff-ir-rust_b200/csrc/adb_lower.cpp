@@ -58,7 +58,7 @@ bool has_result(uint8_t op) {
 void cmd_reads(const Cmd& c, uint32_t out[2], int& n) {
     n = 0;
     switch (c.op) {
-    case OP_MUL: case OP_ADD: case OP_DOT: case OP_CONCAT: case OP_MUL_EQ: case OP_ADD_EQ:
+    case OP_MUL: case OP_ADD: case OP_DOT: case OP_BATCH_DOT: case OP_CONCAT: case OP_MUL_EQ: case OP_ADD_EQ:
         out[n++] = c.a; out[n++] = c.b; break;
     case OP_EQZ: case OP_GTZ: case OP_LTZ: case OP_SUM: case OP_MAX: case OP_CONTIG: case OP_EXP2: case OP_LOG2:
     case OP_SIN: case OP_RECIP: case OP_SQRT: case OP_VIEW: case OP_INDEX: case OP_PERMUTE:
@@ -928,6 +928,7 @@ class Lowerer {
         case OP_SUM: return lower_sum(c, 0);
         case OP_MAX: return lower_sum(c, 1);
         case OP_DOT: return lower_dot(c);
+        case OP_BATCH_DOT: return lower_batch_dot(c);
         case OP_ALLREDUCE: return lower_allreduce(c);
         default: fail("internal: unexpected command in straight-line code");
         }
@@ -1214,6 +1215,57 @@ class Lowerer {
         dot_cse_[dot_key] = bind_[c.res].node;
         // operands that were just written to memory are found under their new identity as well
         dot_cse_[{g_.canon(a), g_.canon(b)}] = bind_[c.res].node;
+    }
+
+    // BatchDot (extension; the reference lists batched matmul as missing, TODO.md:22, and runs one 2-d DotProduct per
+    // attention head, src/nn/transformer.rs:10-18): [B,M,K] x [B,K,N] -> [B,M,N] as ONE step; the slices of an operand
+    // are a fixed number of elements apart, so transposed / permuted operands need no copy as long as every axis of
+    // the view is a single stride.
+    void lower_batch_dot(const Cmd& c) {
+        Node* a = resolve(c.a);
+        Node* b = resolve(c.b);
+        if (a->shape.size() != 3 || b->shape.size() != 3) fail("BatchDot needs 3-d operands");
+        if (a->shape[0] != b->shape[0]) fail("BatchDot operands differ in their batch size");
+        if (a->shape[2] != b->shape[1]) fail("A's last dimension must equal B's second dimension");
+        const int64_t B = a->shape[0], M = a->shape[1], K = a->shape[2], N = b->shape[2];
+        consume(c.a);
+        consume(c.b);
+        struct Op3 { int buf; int64_t off, bs, rs, cs; };
+        auto operand = [&](Node* n) -> Op3 {
+            n = g_.canon(n);
+            bool ok = n->kind == N_LOAD;
+            for (int d = 0; ok && d < 3; d++) ok = n->view.dims[size_t(d)].size() <= 1;
+            if (ok) {
+                auto st = [&](int d) { return n->view.dims[size_t(d)].empty() ? int64_t(0) : n->view.dims[size_t(d)][0].stride; };
+                int64_t bs = st(0), rs = st(1), cs = st(2);
+                if ((rs == 0 && n->shape[1] > 1) || (cs == 0 && n->shape[2] > 1)) ok = false;
+                if (ok) {
+                    if (n->shape[1] == 1) rs = n->shape[2] * (cs ? cs : 1);
+                    if (n->shape[2] == 1) cs = 1;
+                    return {n->buf, n->view.offset, bs, rs, cs};
+                }
+            }
+            Node* m = materialize_node(n);
+            return {m->buf, 0, n->shape[1] * n->shape[2], n->shape[2], 1};
+        };
+        Op3 oa = operand(a), ob = operand(b);
+        Shape rs{B, M, N};
+        int buf = result_buffer(c.res, rs);
+        const bool overlaps = buf == oa.buf || buf == ob.buf;
+        if (overlaps) buf = temp_buffer(B * M * N);
+        before_write(buf, {c.res});
+        Step& s = push_step(Step::GEMM);
+        s.gemm.a = oa.buf; s.gemm.b = ob.buf; s.gemm.c = buf;
+        s.gemm.M = M; s.gemm.N = N; s.gemm.K = K;
+        s.gemm.a_off = oa.off; s.gemm.b_off = ob.off; s.gemm.c_off = 0;
+        s.gemm.a_rs = oa.rs; s.gemm.a_cs = oa.cs; s.gemm.b_rs = ob.rs; s.gemm.b_cs = ob.cs;
+        s.gemm.batch = B; s.gemm.a_bs = oa.bs; s.gemm.b_bs = ob.bs; s.gemm.c_bs = M * N;
+        touch(oa.buf, s.pos);
+        touch(ob.buf, s.pos);
+        touch(buf, s.pos);
+        g_.buf_version[buf]++;
+        if (overlaps) bind_value(c.res, g_.load(buf, rs, contiguous_view(rs)));
+        else bind_own_buffer(c.res, buf, rs);
     }
 
     void lower_allreduce(const Cmd& c) {
@@ -2170,7 +2222,7 @@ class Lowerer {
         auto& steps = blk.steps;
         std::vector<int> rd, wr;
         for (size_t gi = 0; gi < steps.size(); gi++) {
-            if (steps[gi].kind != Step::GEMM || steps[gi].gemm.epi != Step::Gemm::EPI_NONE || steps[gi].gemm.c_off != 0) continue;
+            if (steps[gi].kind != Step::GEMM || steps[gi].gemm.epi != Step::Gemm::EPI_NONE || steps[gi].gemm.c_off != 0 || steps[gi].gemm.batch != 1) continue;
             const int cb = steps[gi].gemm.c;
             const int64_t M = steps[gi].gemm.M, N = steps[gi].gemm.N;
             if (M * N <= 0) continue;
@@ -2456,7 +2508,7 @@ static void dump_block(const Plan& p, const StepBlock& b, int ind, bool src, std
             break;
         }
         case Step::GEMM:
-            o << pad << "#" << s.pos << " gemm " << p.bufs[s.gemm.c].name << "[" << s.gemm.M << "," << s.gemm.N << "] = "
+            o << pad << "#" << s.pos << (s.gemm.batch > 1 ? " gemm x" + std::to_string(s.gemm.batch) + " " : " gemm ") << p.bufs[s.gemm.c].name << "[" << s.gemm.M << "," << s.gemm.N << "] = "
               << p.bufs[s.gemm.a].name << "+" << s.gemm.a_off << "(" << s.gemm.a_rs << "," << s.gemm.a_cs << ") . "
               << p.bufs[s.gemm.b].name << "+" << s.gemm.b_off << "(" << s.gemm.b_rs << "," << s.gemm.b_cs << ") K=" << s.gemm.K << "\n";
             if (s.gemm.epi != Step::Gemm::EPI_NONE) {

@@ -106,6 +106,8 @@ struct Step {
         int64_t M = 0, N = 0, K = 0;
         int64_t a_off = 0, b_off = 0, c_off = 0;
         int64_t a_rs = 0, a_cs = 0, b_rs = 0, b_cs = 0;
+        // batched product (BatchDot): `batch` independent products, operand / result slices this many elements apart
+        int64_t batch = 1, a_bs = 0, b_bs = 0, c_bs = 0;
         // Element-wise work on the product, done while the accumulator is still in registers (the reference's
         // `DPElwExpr`, src/kernel/fusion/dp_elw.rs:13-150 / src/devices/opencl/kernels/fuse_dp_elw.rs:48-67): a
         // chain  v = acc; v = op_i(v, operand_i)  whose operands are constants, one vector indexed by the column

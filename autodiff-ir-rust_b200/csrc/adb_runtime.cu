@@ -336,7 +336,7 @@ class Executor {
         r.kernel = s.kernel;
         r.e0 = event();
         r.e1 = event();
-        r.work = s.kind == Step::GEMM ? 2.0 * double(s.gemm.M) * double(s.gemm.N) * double(s.gemm.K)
+        r.work = s.kind == Step::GEMM ? 2.0 * double(s.gemm.M) * double(s.gemm.N) * double(s.gemm.K) * double(s.gemm.batch)
                : s.kind == Step::ALLREDUCE ? 4.0 * double(s.nelem)
                : kernel_bytes(plan_.kernels[s.kernel]);
         ck(cudaEventRecord(r.e0, cur_stream_), "event");
@@ -356,6 +356,7 @@ class Executor {
             a.A = buf_ptr(g.a, g.a_off); a.B = buf_ptr(g.b, g.b_off); a.C = buf_ptr(g.c, g.c_off);
             a.M = g.M; a.N = g.N; a.K = g.K;
             a.a_rs = g.a_rs; a.a_cs = g.a_cs; a.b_rs = g.b_rs; a.b_cs = g.b_cs;
+            a.batch = g.batch; a.a_bs = g.a_bs; a.b_bs = g.b_bs; a.c_bs = g.c_bs;
             a.force_simt = (d_->flags & ADB_FLAG_SIMT_DOT) != 0;
             a.no_pair = (d_->flags & ADB_FLAG_SINGLE_SM_DOT) != 0;
             a.reserve_sms = gemm_reserve_;

@@ -68,7 +68,7 @@ struct Sharder {
     static void reads(const Cmd& c, uint32_t out[2], int& n) {
         n = 0;
         switch (c.op) {
-        case OP_MUL: case OP_ADD: case OP_DOT: case OP_CONCAT: case OP_MUL_EQ: case OP_ADD_EQ: out[n++] = c.a; out[n++] = c.b; break;
+        case OP_MUL: case OP_ADD: case OP_DOT: case OP_BATCH_DOT: case OP_CONCAT: case OP_MUL_EQ: case OP_ADD_EQ: out[n++] = c.a; out[n++] = c.b; break;
         case OP_EQZ: case OP_GTZ: case OP_LTZ: case OP_SUM: case OP_MAX: case OP_CONTIG: case OP_EXP2: case OP_LOG2: case OP_SIN:
         case OP_RECIP: case OP_SQRT: case OP_VIEW: case OP_INDEX: case OP_PERMUTE: case OP_BROADCAST: case OP_ALLREDUCE:
             out[n++] = c.a; break;
@@ -451,6 +451,19 @@ struct Sharder {
                 if (a.tag == T_SHARD && a.origin >= 0) redecide(a, -1, "DotProduct operand is a broadcast along the batch");
                 fail("DotProduct of '" + name(c.a) + "' and '" + name(c.b) + "' cannot be split over the batch");
             }
+            return;
+        }
+        case OP_BATCH_DOT: {
+            resolve_partial(c.a, out);
+            resolve_partial(c.b, out);
+            Info a = info[c.a], b = info[c.b];
+            if (a.dims.size() != 3 || b.dims.size() != 3) fail("BatchDot needs 3-d operands");
+            std::vector<int64_t> g{a.dims[0], a.dims[1], b.dims[2]};
+            const bool a_rep = a.tag == T_REP || a.tag == T_CONST, b_rep = b.tag == T_REP || b.tag == T_CONST;
+            // the slices are independent: both operands cut along the slice axis stay cut, anything else is refused
+            if (a_rep && b_rep) set(c.res, T_REP, 0, g, c);
+            else if (a.tag == T_SHARD && b.tag == T_SHARD && a.axis == 0 && b.axis == 0) set(c.res, T_SHARD, 0, g, c);
+            else fail("BatchDot of '" + name(c.a) + "' and '" + name(c.b) + "' cannot be split over the batch");
             return;
         }
         case OP_VIEW: {

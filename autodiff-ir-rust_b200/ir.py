@@ -37,6 +37,9 @@ OPC = {
     # extension: row maximum of a 2-d tensor, same shape contract as Sum (the reference's kernel layer names
     # `ReduceOp::Max`, src/kernel/kernel_decl.rs:77, but no IR command reaches it)
     "Max": 28,
+    # extension: batched matrix product [B, M, K] x [B, K, N] -> [B, M, N] (the reference lists it as missing,
+    # TODO.md:22; its attention runs one 2-d DotProduct per head, src/nn/transformer.rs:10-18)
+    "BatchDot": 29,
 }
 
 PAYLOAD_INLINE = 0   # u64 = byte offset of the data inside the blob
@@ -183,7 +186,7 @@ class _Writer:
             self.u32(self.idx(id_))
             self.f32(contents)
             self.dims(dim)
-        elif k in ("ElwMultiply", "ElwAdd", "DotProduct"):
+        elif k in ("ElwMultiply", "ElwAdd", "DotProduct", "BatchDot"):
             self.u32(self.idx(c[1])); self.u32(self.idx(c[2])); self.u32(self.idx(c[3]))
         elif k in ("ElwMultiplyEq", "ElwAddEq"):
             self.u32(self.idx(c[1])); self.u32(self.idx(c[2]))

@@ -142,7 +142,7 @@ static int parse_cmd(Oracle *o, Rd *r, Cmd *c, int depth) {
           else { snprintf(o->err, sizeof o->err, "oracle: device-resident payload unsupported"); return -1; } }
         break;
     case 2: c->res = r32(r); c->cval = rf32(r); rdims(r, c); break;
-    case 3: case 4: case 11: c->a = r32(r); c->b = r32(r); c->res = r32(r); break;
+    case 3: case 4: case 11: case 29: c->a = r32(r); c->b = r32(r); c->res = r32(r); break;
     case 5: case 6: c->a = r32(r); c->b = r32(r); c->res = c->a; break;
     case 7: case 8: case 9: case 10: case 17: case 18: case 19: case 20: case 21: case 22: case 28:
         c->a = r32(r); c->res = r32(r); break;
@@ -214,7 +214,7 @@ static void scan_uses(Oracle *o, Proc *p, int top, uint32_t outer_pos) {
         uint32_t pos = top ? i : outer_pos;
         c->pos = pos;
         switch (c->op) {
-        case 3: case 4: case 11: case 14: mark_use(o, c->a, pos); mark_use(o, c->b, pos); break;
+        case 3: case 4: case 11: case 14: case 29: mark_use(o, c->a, pos); mark_use(o, c->b, pos); break;
         case 5: case 6: mark_use(o, c->a, pos); mark_use(o, c->b, pos); break;
         case 7: case 8: case 9: case 10: case 12: case 13: case 15: case 16: case 17:
         case 18: case 19: case 20: case 21: case 22: case 27: case 28:
@@ -585,6 +585,35 @@ static int exec_cmd(Oracle *o, Cmd *c) {
         if (ob) pool_free(b);
         uint64_t dims[2] = { M, N };
         bind_buf(o, c->res, out, dims, 2);
+        return 0;
+    }
+    case 29: { /* BatchDot (extension): [B,M,K] x [B,K,N] -> [B,M,N], every slice as DotProduct: k ascending, fp32 */
+        if (check_defined(o, c->a) || check_defined(o, c->b)) return -1;
+        const Var *va = &V[c->a], *vb = &V[c->b];
+        if (va->nd != 3 || vb->nd != 3 || va->dims[0] != vb->dims[0] || va->dims[2] != vb->dims[1]) {
+            snprintf(o->err, sizeof o->err, "oracle: BatchDot shape mismatch"); return -1;
+        }
+        uint64_t B = va->dims[0], M = va->dims[1], K = va->dims[2], N = vb->dims[2];
+        int oa, ob;
+        float *a = materialize(o, c->a, &oa);
+        float *b = materialize(o, c->b, &ob);
+        float *out = pool_alloc((size_t)(B * M * N));
+#pragma omp parallel for schedule(static) collapse(2) if (B * M * N * K > 65536)
+        for (uint64_t s = 0; s < B; s++)
+            for (uint64_t i = 0; i < M; i++) {
+                float *cr = out + (s * M + i) * N;
+                for (uint64_t j = 0; j < N; j++) cr[j] = 0.0f;
+                for (uint64_t k = 0; k < K; k++) {
+                    const float av = a[(s * M + i) * K + k];
+                    const float *br = b + (s * K + k) * N;
+                    if (o->f64_acc) { for (uint64_t j = 0; j < N; j++) cr[j] = (float)((double)cr[j] + (double)av * (double)br[j]); }
+                    else for (uint64_t j = 0; j < N; j++) cr[j] += av * br[j];
+                }
+            }
+        if (oa) pool_free(a);
+        if (ob) pool_free(b);
+        uint64_t dims[3] = { B, M, N };
+        bind_buf(o, c->res, out, dims, 3);
         return 0;
     }
     case 12: case 13: case 15: case 16: { /* aliases */

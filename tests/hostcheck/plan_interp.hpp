@@ -167,14 +167,15 @@ struct PlanInterp {
         case Step::ELW: case Step::REDUCE: run_kernel(plan.kernels[size_t(s.kernel)]); break;
         case Step::GEMM: {
             const auto& g = s.gemm;
-            const float* A = ptr(g.a, g.a_off);
-            const float* B = ptr(g.b, g.b_off);
-            float* C = ptr(g.c, g.c_off);
+          for (int64_t slice = 0; slice < g.batch; slice++) {
+            const float* A = ptr(g.a, g.a_off) + slice * g.a_bs;
+            const float* B = ptr(g.b, g.b_off) + slice * g.b_bs;
+            float* C = ptr(g.c, g.c_off) + slice * g.c_bs;
             // C is written in place, element by element; a plan whose product lands in one of its own operands shows
             // up as a wrong result here too.  A plain product zeroes C first, as the split-k path of the GPU kernel does.
             if (!(g.epi == Step::Gemm::EPI_SCALE && g.accumulate))
                 for (int64_t i = 0; i < g.M * g.N; i++) C[i] = 0.f;
-            float* out = g.out >= 0 ? ptr(g.out, g.out_off) : nullptr;
+            float* out = g.out >= 0 ? ptr(g.out, g.out_off) + slice * g.c_bs : nullptr;
             const float* colvec = g.colvec >= 0 ? ptr(g.colvec, g.colvec_off) : nullptr;
             for (int64_t m = 0; m < g.M; m++)
                 for (int64_t n = 0; n < g.N; n++) {
@@ -196,6 +197,7 @@ struct PlanInterp {
                     } else
                         C[m * g.N + n] = v;
                 }
+          }
             break;
         }
         case Step::UPLOAD: {

@@ -138,3 +138,30 @@ def test_scaled_product_is_written_directly(B, K2, N):
     ref = -0.5 * (x.reshape(B, K2).astype(np.float64).T @ g.reshape(B, N).astype(np.float64))
     got = np.asarray(t.get().data, np.float64).reshape(K2, N)
     assert np.abs(got - ref).max() / np.abs(ref).max() < 2e-5
+
+
+@pytest.mark.parametrize("B,S,D", [(6, 10, 4), (16, 128, 64), (96, 256, 64), (4, 1024, 512)])
+def test_batched_product_with_gradients(B, S, D):
+    """BatchDot (attention-shaped: scores = Q K^T, out = scores V, and both gradients): many small slices run as one
+    launch of the CUDA-core kernel, few large ones on the tensor cores; against the oracle."""
+    rng = np.random.default_rng(B * 1000 + S)
+    q, k, v = ((rng.standard_normal(B * S * D) / np.sqrt(D)).astype(np.float32) for _ in range(3))
+
+    def prog(dev):
+        ad.set_device(dev)
+        ad.eager_dep_opt()
+        Q, K, V = (ad.tensor(x, [B, S, D]) for x in (q, k, v))
+        out = ad.bmm(ad.bmm(Q, K.permute([0, 2, 1])) * (1.0 / np.sqrt(D)), V)
+        loss = (out * out).sum(2).sum(1).sum(0)
+        loss.forward()
+        loss.backward()
+        keep = {"out": out.val(), "dq": Q.grad(), "dk": K.grad(), "dv": V.grad()}
+        for t in keep.values():
+            t.keep()
+        ad.execute()
+        return {n: t.get() for n, t in keep.items()}
+    want = prog(oracle())
+    got = prog(b200())
+    assert "gemm x%d" % B in b200().dump_plan()
+    for name in want:
+        assert_rel(name, got[name], want[name], 1e-4)
