@@ -20,7 +20,7 @@ every N draws its rows of the same [65536, 4096] / [65536, 1000] tensors, so the
 the loss of the same training run.  At N > 1 the line also carries `parity_vs_n1`: two steps at a reduced batch run
 sharded over the N GPUs and once more on rank 0's GPU alone, with the relative difference of loss and parameters.
 
-    python bench.py --case c2|c3|c5|dot|ln|c4|transpose ...   # one program a few times on cuda:0, for profilers
+    python bench.py --case c2|c3|c5|dot|ln|c4|transpose|prims ...   # one program a few times on cuda:0, for profilers
 """
 from __future__ import annotations
 
@@ -663,6 +663,27 @@ def run_case(args):
             inp = {k: DP(v.data_ptr(), v.numel(), v) for k, v in w.items()}
             inp["x"], inp["t"] = px, pt
             cfg.c4_mlp_train(dev, batch=args.batch, widths=widths, steps=args.iters, inputs=inp, execute=False)
+        elif args.case == "prims":
+            # one kernel per primitive over 2^25 elements (instruction cost per element from the profiler's counters)
+            n = 1 << 25
+            x, px = resident(n)
+            keep.append(x)
+            ad.set_device(dev)
+            ad.eager_dep_opt()
+            t = ad.tensor(px, [n])
+            prims = {"add": lambda t: t + 1.0, "mul": lambda t: t * t, "exp2": lambda t: t.exp2(), "log2": lambda t: (t * t + 1.0).log2(),
+                     "sin": lambda t: t.sin(), "recip": lambda t: (t * t + 1.0).recip(), "sqrt": lambda t: t.sqrt(),
+                     "greater": lambda t: t.more_than(ad.constant(0.5, [n])), "sigmoid": lambda t: t.sigmoid()}
+            for name, f in prims.items():
+                ad.set_device(dev)
+                ad.eager_dep_opt()
+                t = ad.tensor(px, [n])
+                y = f(t).contigious().forward()
+                y.keep()
+                ad.execute()
+                emit(json.dumps({"primitive": name, "kernel": [l for l in dev.dump_plan().splitlines() if "adb_elw" in l][0].split()[-1],
+                                 "device_ms": dev.stats()["device_ms"]}))
+            continue
         elif args.case == "transpose":
             # x.t().contigious() of [m, n] (or the (0, 2, 1) permute of [batch, m, n] with --batch > 1)
             lead = [args.batch] if args.batch > 1 else []
@@ -713,7 +734,7 @@ def main():
     ap.add_argument("--skip-extras", action="store_true")
     ap.add_argument("--dev-flags", type=int, default=None, help="extra ADB_FLAG_* bits of the timed handle (default 0: graph replay)")
     # single-program runner (profilers)
-    ap.add_argument("--case", default=None, choices=["c2", "c3", "c4", "c5", "dot", "ln", "transpose"])
+    ap.add_argument("--case", default=None, choices=["c2", "c3", "c4", "c5", "dot", "ln", "transpose", "prims"])
     ap.add_argument("--size", type=int, default=8192)
     ap.add_argument("--n", type=int, default=1024)
     ap.add_argument("--m", type=int, default=4096)
