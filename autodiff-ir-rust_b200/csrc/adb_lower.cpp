@@ -1006,8 +1006,13 @@ class Lowerer {
     void lower_sum(const Cmd& c, int red_op) {
         Node* a = resolve(c.a);
         if (a->shape.size() != 2) fail(std::string("Reduce (") + (red_op ? "max" : "sum") + ") node needs dim=2 ('" + name(c.a) + "')");
-        int64_t V = a->shape[0], R = a->shape[1];
         consume(c.a);
+        lower_sum_node(c, a, red_op);
+    }
+
+    // the row reduction of a 2-d value `a` into the id c.res (also used by matrix-vector products)
+    void lower_sum_node(const Cmd& c, Node* a, int red_op) {
+        int64_t V = a->shape[0], R = a->shape[1];
         if (a->kind == N_CONST && (red_op == 1 || a->cval == 0.0f)) {
             after_op(c.res, g_.constant(a->cval, {V}));   // maximum of a constant row; sum of zeros
             return;
@@ -1175,6 +1180,29 @@ class Lowerer {
         int64_t M = a->shape[0], K = a->shape[1], N = b->shape[1];
         consume(c.a);
         consume(c.b);
+        // Matrix times vector (or vector times matrix) is a row sum of products: one pass over the matrix at memory
+        // speed through the reduce kernels, instead of a tile kernel that would keep one column of its tiles busy.
+        // (Summation order differs from the dot kernels' k-ascending one, like every other reduction here.)
+        if ((N == 1 || M == 1) && M * N * K >= (int64_t(1) << 16) && K > 1 && !opt_.no_fusion) {
+            Node* summand = nullptr;
+            if (N == 1) {
+                Node* row = g_.reshape(b, {1, K});
+                if (!row) row = g_.reshape(materialize_node(b), {1, K});
+                Node* rep = row ? g_.broadcast(row, 0, M) : nullptr;
+                if (rep) summand = g_.op2(E_MUL, a, rep);
+            } else {
+                Node* bt = g_.permute(b, {1, 0});
+                Node* rep = g_.broadcast(a, 0, N);
+                if (bt && rep) summand = g_.op2(E_MUL, rep, bt);
+            }
+            if (summand) {
+                lower_sum_node(c, summand, 0);
+                Node* r = g_.reshape(resolve(c.res), {M, N});
+                if (!r) fail("internal: matrix-vector result cannot be reshaped");
+                bind_value(c.res, r);
+                return;
+            }
+        }
         std::pair<Node*, Node*> dot_key{a, b};
         {
             auto it = dot_cse_.find(dot_key);

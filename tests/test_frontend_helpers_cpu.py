@@ -45,3 +45,25 @@ def test_helpers_lower_for_the_device():
     y = RNG.standard_normal(64 * 48).astype(np.float32)
     helper_program(dev, y, y[::-1].copy(), [64, 48])
     assert dev.plan.startswith("plan:")
+
+
+def test_hash_generator_is_the_same_on_numpy_and_torch_and_keyed_by_global_index():
+    """The benchmark's batch generator: integer hashing only, so the numpy version (configs.hash_normal) and the torch
+    version (bench.hash_normal_torch) give the same bits, and any slice of a tensor can be drawn on its own -- what lets
+    every rank of every N train on the same global batch."""
+    import importlib
+    import os
+    import sys
+    import numpy as np
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import bench
+    adb = importlib.import_module("autodiff-ir-rust_b200")
+    cfg = adb.configs
+    whole = cfg.hash_normal(3, 0, 50_000)
+    part = cfg.hash_normal(3, 0, 10_000, start=20_000)
+    np.testing.assert_array_equal(whole[20_000:30_000], part)
+    t = bench.hash_normal_torch(cfg, 3, 0, 20_000, 10_000, "cpu").numpy()
+    np.testing.assert_array_equal(t, part)
+    assert not np.array_equal(cfg.hash_normal(3, 1, 1000), cfg.hash_normal(3, 0, 1000))
+    big = cfg.hash_normal(7, 2, 1 << 20)
+    assert abs(float(big.mean())) < 5e-3 and abs(float(big.std()) - 1.0) < 5e-3

@@ -159,3 +159,20 @@ def test_rows_that_are_not_a_multiple_of_four_are_padded_not_demoted(M, K, N):
     ref = a.reshape(M, K).astype(np.float64) @ b.reshape(K, N).astype(np.float64)
     g = np.asarray(got.data, np.float64).reshape(M, N)
     assert np.abs(g - ref).max() / np.abs(ref).max() < 2e-5
+
+
+@pytest.mark.parametrize("M,K,N,ta", [(8192, 8192, 1, False), (1, 8192, 8192, False), (4096, 3000, 1, True), (1, 512, 1000, False)])
+def test_matrix_vector_products_run_as_row_sums(M, K, N, ta):
+    """N = 1 or M = 1: one pass over the matrix through the reduce kernels (row sums of products) instead of a tile
+    kernel; against float64."""
+    a = RNG.standard_normal(M * K).astype(np.float32)
+    b = RNG.standard_normal(K * N).astype(np.float32)
+    dev = _device("pair")
+    got = _dot(dev, a, b, ta, False, M, K, N)
+    plan = dev.dump_plan()
+    assert "gemm" not in plan and ("adb_rowsum_" in plan or "adb_colsum_" in plan), plan
+    A = a.reshape(K, M).T if ta else a.reshape(M, K)
+    ref = A.astype(np.float64) @ b.reshape(K, N).astype(np.float64)
+    g = np.asarray(got.data, np.float64).reshape(M, N)
+    assert got.dim == [M, N]
+    assert np.abs(g - ref).max() / np.abs(ref).max() < 1e-5

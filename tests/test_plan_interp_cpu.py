@@ -270,3 +270,18 @@ def test_path_dependent_view_is_refused(hostcheck, tmp_path):
                       ("ElwAddEq", "v3", "v3"), ("ElwAdd", "v1", "v3", "out")], ["out"])
     blob = adb.ir.serialize(proc, dep, inline_limit=1 << 40)[0]
     assert _interpret_or_refused(hostcheck, tmp_path, blob, 0, "pathdep") is None
+
+
+@pytest.mark.parametrize("M,K,N", [(300, 256, 1), (1, 300, 260)])
+def test_matrix_vector_products_through_the_reduce_kernels(hostcheck, tmp_path, M, K, N):
+    rng = np.random.default_rng(M + N)
+    dev = _Both()
+    ad.set_device(dev)
+    ad.eager_dep_opt()
+    a = ad.tensor(rng.standard_normal(M * K).astype(np.float32), [M, K])
+    b = ad.tensor(rng.standard_normal(K * N).astype(np.float32), [K, N])
+    y = (ad.dot(a, b) * 2.0).forward()
+    y.keep()
+    ad.execute()
+    for flags in (0, 2):
+        _compare(_interpret(hostcheck, tmp_path, dev.blobs[-1], flags, f"mv{flags}"), {y.id: y.get()}, 1e-5)
