@@ -2445,7 +2445,33 @@ class Lowerer {
         struct Placed { int64_t off, size; int first, last; };
         std::vector<Placed> placed;
         int64_t top = 0;
+        // Kept tensors first, side by side, when they are small: the host then reads all of them back with one copy
+        // (a program like the README's MLP step keeps eight tensors of a few floats each; eight copies of a few bytes
+        // cost more than the kernels that made them).
+        std::vector<char> is_result(bufs.size(), 0);
+        {
+            int64_t total = 0;
+            std::vector<int> res;
+            for (auto& r : plan_.results)
+                if (r.buf >= 0 && !bufs[size_t(r.buf)].external && !is_result[size_t(r.buf)]) {
+                    is_result[size_t(r.buf)] = 1;
+                    res.push_back(r.buf);
+                    total += ((bufs[size_t(r.buf)].numel * 4 + 255) / 256) * 256;
+                }
+            if (!res.empty() && total <= (int64_t(1) << 20)) {
+                for (int i : res) {
+                    auto& b = bufs[size_t(i)];
+                    const int64_t size = ((b.numel * 4 + 255) / 256) * 256;
+                    b.arena_off = top;
+                    placed.push_back({top, size, INT_MIN, INT_MAX});
+                    top += size;
+                }
+                plan_.results_bytes = top;
+            } else
+                std::fill(is_result.begin(), is_result.end(), 0);
+        }
         for (int i : order) {
+            if (is_result[size_t(i)]) continue;
             auto& b = bufs[i];
             int first = b.persistent ? INT_MIN : b.first;
             int last = b.persistent ? INT_MAX : b.last;

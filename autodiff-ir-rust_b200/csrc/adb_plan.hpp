@@ -178,6 +178,7 @@ struct Plan {
     std::vector<PayloadSlot> payloads;
     std::vector<ResultInfo> results;
     int64_t arena_bytes = 0;
+    int64_t results_bytes = 0;   // > 0: the kept tensors' buffers are the first `results_bytes` of the arena (one read-back copy)
     int n_steps = 0;
     size_t ir_commands = 0;
     uint64_t key = 0;

@@ -176,6 +176,8 @@ struct adb_device {
     };
     std::vector<HostResult> results;
     std::vector<std::pair<float*, size_t>> pinned_pool;
+    float* result_block = nullptr;   // pinned; holds the kept tensors of plans whose results sit side by side in the arena
+    size_t result_block_cap = 0;
     adb_stats stats{};
     ncclComm_t nccl_comm = nullptr;
     GemmContext gemm;
@@ -946,9 +948,22 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
 
     // read-back of dep-list ids (src/devices/opencl/device.rs:82-87)
     for (auto& r : d->results) {
-        if (r.host) d->pinned_pool.push_back({r.host, r.host_cap});
+        if (r.host && r.host_cap) d->pinned_pool.push_back({r.host, r.host_cap});
     }
     d->results.clear();
+    // small kept tensors sit side by side at the start of the arena: one copy brings all of them back
+    float* block = nullptr;
+    if (plan.results_bytes > 0) {
+        if (d->result_block_cap < size_t(plan.results_bytes)) {
+            if (d->result_block) cudaFreeHost(d->result_block);
+            d->result_block = nullptr;
+            ck(cudaMallocHost(&d->result_block, size_t(plan.results_bytes)), "cudaMallocHost");
+            d->result_block_cap = size_t(plan.results_bytes);
+        }
+        block = d->result_block;
+        ck(cudaMemcpyAsync(block, d->arena, size_t(plan.results_bytes), cudaMemcpyDeviceToHost, d->stream), "read-back");
+        d->stats.d2h_bytes += uint64_t(plan.results_bytes);
+    }
     for (auto& ri : plan.results) {
         adb_device::HostResult hr;
         hr.id = ri.id;
@@ -957,9 +972,15 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
             for (auto x : ri.shape) hr.dims.push_back(uint64_t(x));
             hr.n = size_t(numel(ri.shape));
             hr.dev = ex.buf_ptr(ri.buf, ri.off);
-            hr.host = pinned_alloc(d, hr.n * 4, hr.host_cap);
-            if (hr.n) ck(cudaMemcpyAsync(hr.host, hr.dev, hr.n * 4, cudaMemcpyDeviceToHost, d->stream), "read-back");
-            d->stats.d2h_bytes += hr.n * 4;
+            const BufferInfo& bi = plan.bufs[size_t(ri.buf)];
+            if (block && !bi.external && bi.arena_off >= 0 && bi.arena_off + (ri.off + int64_t(hr.n)) * 4 <= plan.results_bytes) {
+                hr.host = block + bi.arena_off / 4 + ri.off;   // inside the shared block: not returned to the pool
+                hr.host_cap = 0;
+            } else {
+                hr.host = pinned_alloc(d, hr.n * 4, hr.host_cap);
+                if (hr.n) ck(cudaMemcpyAsync(hr.host, hr.dev, hr.n * 4, cudaMemcpyDeviceToHost, d->stream), "read-back");
+                d->stats.d2h_bytes += hr.n * 4;
+            }
             hr.fetched = true;
         }
         d->results.push_back(std::move(hr));
@@ -1114,7 +1135,8 @@ void adb_destroy(adb_device* d) {
     for (auto& k : d->kernels)
         if (k.lib) cudaLibraryUnload(k.lib);
     for (auto& r : d->results)
-        if (r.host) cudaFreeHost(r.host);
+        if (r.host && r.host_cap) cudaFreeHost(r.host);
+    if (d->result_block) cudaFreeHost(d->result_block);
     for (auto& p : d->pinned_pool) cudaFreeHost(p.first);
     for (auto e : d->ev_pool) cudaEventDestroy(e);
     gemm_destroy(d->gemm);
