@@ -894,14 +894,69 @@ void plan_reduce(KernelSpec& k, int sm_count) {
 
 int elw_vec(const KernelSpec& k) { return elw_vec_impl(k); }
 
+bool elw_uses_tile(const KernelSpec& k) {
+    KernelSpec probe = k;
+    return gen_transpose(probe);
+}
+
+namespace {
+
+void replace_all(std::string& s, const std::string& from, const std::string& to) {
+    for (size_t p = 0; (p = s.find(from, p)) != std::string::npos; p += to.size()) s.replace(p, from.size(), to);
+}
+
+// One launch for several independent kernels: every member's source becomes a device function that takes its block
+// index and block count as arguments, and the entry point hands each range of blockIdx.x to one member.  The
+// argument block is the members' argument blocks one after another, then the first block index of each member.
+void gen_group(Plan& plan, KernelSpec& g) {
+    static const std::string sig_head = "extern \"C\" __global__ void __launch_bounds__(256) ";
+    static const std::string sig_tail = "(const __grid_constant__ Args a) {";
+    std::ostringstream o;
+    o << helpers();
+    const std::string help = helpers();
+    for (size_t m = 0; m < g.members.size(); m++) {
+        const KernelSpec& k = plan.kernels[size_t(g.members[m])];
+        const std::string tag = std::to_string(m);
+        std::string src = k.source;
+        if (!help.empty() && src.compare(0, help.size(), help) == 0) src.erase(0, help.size());
+        const size_t h = src.find(sig_head), t = src.find(sig_tail);
+        if (h == std::string::npos || t == std::string::npos || t < h) { g.source.clear(); g.entry.clear(); return; }
+        src.replace(h, t + sig_tail.size() - h,
+                    "__device__ void adb_member" + tag + "(const Args" + tag + "& a, const unsigned int adb_bid, const unsigned int adb_nb) {");
+        replace_all(src, "struct Args ", "struct Args" + tag + " ");
+        replace_all(src, "ADB_IDENT", "ADB_IDENT" + tag);
+        replace_all(src, "adb_comb", "adb_comb" + tag);
+        replace_all(src, "blockIdx.x", "adb_bid");
+        replace_all(src, "gridDim.x", "adb_nb");
+        replace_all(src, "blockIdx.y", "0u");
+        replace_all(src, "gridDim.y", "1u");
+        o << src;
+    }
+    const size_t n = g.members.size();
+    o << "struct Args {";
+    for (size_t m = 0; m < n; m++) o << " Args" << m << " a" << m << ";";
+    o << " unsigned int start[" << n + 1 << "]; };\n";
+    o << "extern \"C\" __global__ void __launch_bounds__(256) @ENTRY@(const __grid_constant__ Args a) {\n";
+    o << "  const unsigned int b = blockIdx.x;\n";
+    for (size_t m = 0; m < n; m++)
+        o << "  " << (m ? "else " : "") << "if (b < a.start[" << m + 1 << "]) adb_member" << m << "(a.a" << m << ", b - a.start[" << m
+          << "], a.start[" << m + 1 << "] - a.start[" << m << "]);\n";
+    o << "}\n";
+    finish(g, o.str(), "adb_group");
+}
+
+}  // namespace
+
 void generate_kernels(Plan& plan) {
     g_exact_div = plan.exact_div;
     for (auto& k : plan.kernels) {
-        if (!k.source.empty() || k.dead) continue;
+        if (!k.source.empty() || k.dead || k.type == KernelSpec::GROUP) continue;
         if (k.type == KernelSpec::ELW) gen_elw(k);
         else if (k.type == KernelSpec::ROWS) gen_rows(k);
         else gen_reduce(k);
     }
+    for (auto& k : plan.kernels)
+        if (k.type == KernelSpec::GROUP && k.source.empty() && !k.dead) gen_group(plan, k);
 }
 
 }  // namespace adb

@@ -105,6 +105,11 @@ class Lowerer {
         fuse_reductions();
         if (!opt_.no_fusion && !opt_.no_dot_epilogue) fuse_dot_epilogues(plan_.main);
         if (!opt_.no_fusion) drop_unread_outputs();
+        if (!opt_.no_fusion && !opt_.no_grouping) {
+            std::vector<int> uses(plan_.kernels.size(), 0);
+            count_kernel_uses(plan_.main, uses);
+            group_kernels(plan_.main, uses);
+        }
         plan_arena();
     }
 
@@ -1497,14 +1502,9 @@ class Lowerer {
         rd.clear();
         wr.clear();
         switch (s.kind) {
-        case Step::ELW: case Step::REDUCE: {
-            const KernelSpec& k = plan_.kernels[size_t(s.kernel)];
-            for (auto& in : k.ins) rd.push_back(in.buf);
-            for (auto& o : k.outs) wr.push_back(o.dst.buf);
-            for (auto& r : k.reds) wr.push_back(r.dst.buf);
-            for (auto& ph : k.phases) wr.push_back(ph.dst.buf);
+        case Step::ELW: case Step::REDUCE:
+            kernel_rw(plan_, s.kernel, rd, wr);
             break;
-        }
         case Step::GEMM:
             rd = {s.gemm.a, s.gemm.b};
             wr = {s.gemm.c};
@@ -2419,6 +2419,92 @@ class Lowerer {
         }
     }
 
+    // ------------------------------------------------------------------ independent kernels in one launch
+    // A step list often holds runs of small kernels that do not depend on one another (the bias updates of an
+    // optimiser step, the pieces of a concat, a gradient that is a constant fill next to the sums that feed the
+    // next layer).  Launched one after another each pays a launch and leaves most SMs idle; here they become one
+    // GROUP kernel whose grid is the concatenation of the members' grids.  A member may be picked from further down
+    // the step list when nothing it would jump over (or join) writes what it reads or touches what it writes.  At most
+    // one member may be large: the small ones then run in its shadow.  The reference's fusion passes merge kernels
+    // only along producer -> consumer edges (src/kernel/fusion/elw.rs, reduce_elw.rs); it has no counterpart of this.
+    static constexpr int64_t GROUP_BIG = int64_t(1) << 22;
+    static constexpr size_t GROUP_MAX = 8, GROUP_LOOKAHEAD = 24;
+    static int64_t kernel_work(const KernelSpec& k) {
+        if (k.type == KernelSpec::REDUCE) return k.n * std::max<int64_t>(1, k.r);
+        if (k.type == KernelSpec::ROWS) return k.p2 * k.q2;
+        return k.n;
+    }
+    void count_kernel_uses(const StepBlock& blk, std::vector<int>& uses) const {
+        for (auto& s : blk.steps) {
+            if ((s.kind == Step::ELW || s.kind == Step::REDUCE) && s.kernel >= 0) uses[size_t(s.kernel)]++;
+            if (s.body) count_kernel_uses(*s.body, uses);
+            for (auto& br : s.branches) count_kernel_uses(*br.body, uses);
+            if (s.else_body) count_kernel_uses(*s.else_body, uses);
+        }
+    }
+    bool groupable(const std::vector<Step>& steps, size_t i, const std::vector<int>& uses) const {
+        const Step& s = steps[i];
+        if (s.kind != Step::ELW && s.kind != Step::REDUCE) return false;
+        if (size_t(s.kernel) >= uses.size() || uses[size_t(s.kernel)] != 1) return false;
+        const KernelSpec& k = plan_.kernels[size_t(s.kernel)];
+        if (k.dead || k.type == KernelSpec::GROUP) return false;
+        if (k.type == KernelSpec::ELW && (!k.reds.empty() || elw_uses_tile(k))) return false;   // 2-d grids, 16 KB of shared memory
+        if (k.type == KernelSpec::REDUCE && (k.split != 1 || k.scratch >= 0)) return false;
+        // the kernel that scales the operand of a collective stays next to it (the runtime moves the pair to the
+        // communication stream)
+        if (opt_.world > 1 && i + 1 < steps.size() && steps[i + 1].kind == Step::ALLREDUCE) return false;
+        return true;
+    }
+    void group_kernels(StepBlock& blk, const std::vector<int>& uses) {
+        for (auto& s : blk.steps) {
+            if (s.body) group_kernels(*s.body, uses);
+            for (auto& br : s.branches) group_kernels(*br.body, uses);
+            if (s.else_body) group_kernels(*s.else_body, uses);
+        }
+        auto& steps = blk.steps;
+        std::vector<int> rd, wr, seen_rd, seen_wr;
+        for (size_t i = 0; i < steps.size(); i++) {
+            if (!groupable(steps, i, uses)) continue;
+            std::vector<size_t> members = {i};
+            step_rw(steps[i], seen_rd, seen_wr);
+            int big = kernel_work(plan_.kernels[size_t(steps[i].kernel)]) > GROUP_BIG ? 1 : 0;
+            for (size_t j = i + 1; j < steps.size() && j <= i + GROUP_LOOKAHEAD && members.size() < GROUP_MAX; j++) {
+                if (is_barrier(steps[j])) break;
+                step_rw(steps[j], rd, wr);
+                bool ok = groupable(steps, j, uses) && !hits(seen_wr, rd) && !hits(seen_wr, wr) && !hits(wr, seen_rd);
+                if (ok) {
+                    const int b = kernel_work(plan_.kernels[size_t(steps[j].kernel)]) > GROUP_BIG ? 1 : 0;
+                    if (big + b > 1) ok = false;
+                    else big += b;
+                }
+                if (ok) members.push_back(j);
+                seen_rd.insert(seen_rd.end(), rd.begin(), rd.end());
+                seen_wr.insert(seen_wr.end(), wr.begin(), wr.end());
+            }
+            if (members.size() < 2) continue;
+            KernelSpec g;
+            g.type = KernelSpec::GROUP;
+            const int head_pos = steps[i].pos;
+            for (size_t m : members) {
+                const int ki = steps[m].kernel;
+                g.members.push_back(ki);
+                g.n += kernel_work(plan_.kernels[size_t(ki)]);
+                plan_.kernels[size_t(ki)].grouped = true;
+                step_rw(steps[m], rd, wr);
+                for (int x : rd) touch(x, head_pos);
+                for (int x : wr) touch(x, head_pos);
+            }
+            // small members first: their blocks are scheduled ahead of a large member's
+            std::stable_sort(g.members.begin(), g.members.end(), [&](int a, int b) {
+                return kernel_work(plan_.kernels[size_t(a)]) < kernel_work(plan_.kernels[size_t(b)]);
+            });
+            for (size_t q = members.size(); q-- > 1;) steps.erase(steps.begin() + long(members[q]));
+            steps[i].kind = Step::ELW;
+            steps[i].kernel = int(plan_.kernels.size());
+            plan_.kernels.push_back(std::move(g));
+        }
+    }
+
     // ------------------------------------------------------------------ arena
     void plan_arena() {
         auto& bufs = plan_.bufs;
@@ -2525,39 +2611,51 @@ static std::string subs_str(const std::vector<Sub>& s) {
     return o.str();
 }
 
+static void dump_kernel(const Plan& p, const KernelSpec& k, const std::string& label, const std::string& pad, bool src,
+                        std::ostringstream& o) {
+    const bool is_reduce = k.type == KernelSpec::REDUCE;
+    int nops = 0;
+    for (auto& x : k.ssa) nops += x.kind == Ssa::OP;
+    if (k.type == KernelSpec::ROWS) o << pad << label << " rows [" << k.p2 << "," << k.q2 << "] phases=" << k.phases.size();
+    else if (!is_reduce) o << pad << label << " elw n=" << k.n;
+    else o << pad << label << (k.red_op ? " reduce(max) rows=" : " reduce rows=") << k.n << " len=" << k.r << " mode=" << (k.mode ? "col" : "row") << " split=" << k.split;
+    o << " ops=" << nops << " vec=" << k.vec << " ins=" << k.ins.size() << " outs=" << k.outs.size() << " " << k.entry << "\n";
+    for (auto& in : k.ins)
+        o << pad << "    in  " << p.bufs[in.buf].name << "+" << in.offset << " " << (is_reduce ? subs_str(in.xsubs) + "," : "") << subs_str(in.subs) << "\n";
+    for (auto& out : k.outs)
+        o << pad << "    out " << p.bufs[out.dst.buf].name << "+" << out.dst.offset << " " << (is_reduce ? subs_str(out.dst.xsubs) : subs_str(out.dst.subs)) << "\n";
+    for (auto& ph : k.phases)
+        o << pad << "    " << (ph.red_op ? "max" : "sum") << " v" << ph.ssa << " along each row -> " << p.bufs[ph.dst.buf].name << "+"
+          << ph.dst.offset << "\n";
+    for (auto& rd : k.reds)
+        o << pad << "    sum v" << rd.ssa << " over " << (rd.axis == 0 ? "columns" : "rows") << " of [" << k.p2 << "," << k.q2
+          << "] -> " << p.bufs[rd.dst.buf].name << " " << subs_str(rd.dst.subs) << " (rows per block " << k.row_chunk << ")\n";
+    if (src) {
+        for (size_t i = 0; i < k.ssa.size(); i++) {
+            auto& x = k.ssa[i];
+            o << pad << "      v" << i << " = ";
+            if (x.kind == Ssa::LOAD) o << "load in" << x.operand;
+            else if (x.kind == Ssa::RED) o << "row result " << x.operand;
+            else if (x.kind == Ssa::CONST) o << x.c;
+            else if (x.b >= 0) o << "v" << x.a << " " << eop_name(x.op) << " v" << x.b;
+            else o << eop_name(x.op) << "(v" << x.a << ")";
+            o << "\n";
+        }
+    }
+}
+
 static void dump_block(const Plan& p, const StepBlock& b, int ind, bool src, std::ostringstream& o) {
     std::string pad(size_t(ind) * 2, ' ');
     for (auto& s : b.steps) {
         switch (s.kind) {
         case Step::ELW: case Step::REDUCE: {
             auto& k = p.kernels[s.kernel];
-            int nops = 0;
-            for (auto& x : k.ssa) nops += x.kind == Ssa::OP;
-            if (k.type == KernelSpec::ROWS) o << pad << "#" << s.pos << " rows [" << k.p2 << "," << k.q2 << "] phases=" << k.phases.size();
-            else if (s.kind == Step::ELW) o << pad << "#" << s.pos << " elw n=" << k.n;
-            else o << pad << "#" << s.pos << (k.red_op ? " reduce(max) rows=" : " reduce rows=") << k.n << " len=" << k.r << " mode=" << (k.mode ? "col" : "row") << " split=" << k.split;
-            o << " ops=" << nops << " vec=" << k.vec << " ins=" << k.ins.size() << " outs=" << k.outs.size() << " " << k.entry << "\n";
-            for (auto& in : k.ins)
-                o << pad << "    in  " << p.bufs[in.buf].name << "+" << in.offset << " " << (s.kind == Step::REDUCE ? subs_str(in.xsubs) + "," : "") << subs_str(in.subs) << "\n";
-            for (auto& out : k.outs)
-                o << pad << "    out " << p.bufs[out.dst.buf].name << "+" << out.dst.offset << " " << (s.kind == Step::REDUCE ? subs_str(out.dst.xsubs) : subs_str(out.dst.subs)) << "\n";
-            for (auto& ph : k.phases)
-                o << pad << "    " << (ph.red_op ? "max" : "sum") << " v" << ph.ssa << " along each row -> " << p.bufs[ph.dst.buf].name << "+"
-                  << ph.dst.offset << "\n";
-            for (auto& rd : k.reds)
-                o << pad << "    sum v" << rd.ssa << " over " << (rd.axis == 0 ? "columns" : "rows") << " of [" << k.p2 << "," << k.q2
-                  << "] -> " << p.bufs[rd.dst.buf].name << " " << subs_str(rd.dst.subs) << " (rows per block " << k.row_chunk << ")\n";
-            if (src) {
-                for (size_t i = 0; i < k.ssa.size(); i++) {
-                    auto& x = k.ssa[i];
-                    o << pad << "      v" << i << " = ";
-                    if (x.kind == Ssa::LOAD) o << "load in" << x.operand;
-                    else if (x.kind == Ssa::RED) o << "row result " << x.operand;
-                    else if (x.kind == Ssa::CONST) o << x.c;
-                    else if (x.b >= 0) o << "v" << x.a << " " << eop_name(x.op) << " v" << x.b;
-                    else o << eop_name(x.op) << "(v" << x.a << ")";
-                    o << "\n";
-                }
+            const std::string label = "#" + std::to_string(s.pos);
+            if (k.type == KernelSpec::GROUP) {
+                o << pad << label << " group of " << k.members.size() << " kernels in one launch " << k.entry << "\n";
+                for (int m : k.members) dump_kernel(p, p.kernels[size_t(m)], "  -", pad + "  ", src, o);
+            } else {
+                dump_kernel(p, k, label, pad, src, o);
             }
             break;
         }
@@ -2611,7 +2709,7 @@ static void dump_block(const Plan& p, const StepBlock& b, int ind, bool src, std
 std::string dump_plan(const Plan& plan, bool with_source) {
     std::ostringstream o;
     size_t live = 0;
-    for (auto& k : plan.kernels) live += !k.dead;
+    for (auto& k : plan.kernels) live += !k.dead && !k.grouped;
     o << "plan: " << plan.ir_commands << " IR commands -> " << plan.n_steps << " steps, " << live
       << " kernels, arena " << plan.arena_bytes << " B, " << plan.bufs.size() << " buffers\n";
     dump_block(plan, plan.main, 0, with_source, o);

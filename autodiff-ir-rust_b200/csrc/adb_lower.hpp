@@ -21,6 +21,9 @@ void plan_reduce(KernelSpec& k, int sm_count);
 // four consecutive lanes, else 1); the lowering needs it to size the partial-sum buffers of fused sums.
 int elw_vec(const KernelSpec& k);
 
+// True when the code generator will emit this element-wise kernel as a shared-memory tiled axis swap.
+bool elw_uses_tile(const KernelSpec& k);
+
 // Fills KernelSpec::source / entry / launch shape for every kernel of the plan.
 void generate_kernels(Plan& plan);
 

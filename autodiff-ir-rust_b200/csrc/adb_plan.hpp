@@ -48,7 +48,11 @@ struct Ssa {
 struct KernelSpec {
     // ROWS: several reductions along the rows of a [p2, q2] space and the element-wise work that uses their
     // results, one block per row at a time (a normalisation layer in one pass over its input)
-    enum Type { ELW, REDUCE, ROWS } type = ELW;
+    // GROUP: several independent kernels of the other types launched as one grid (each member takes a range of
+    // block indices); `members` are indices into Plan::kernels
+    enum Type { ELW, REDUCE, ROWS, GROUP } type = ELW;
+    std::vector<int> members;
+    bool grouped = false;   // runs only as a member of a GROUP kernel: source is generated, no module of its own
     int64_t n = 0;  // ELW: elements; REDUCE: rows kept (V)
     int64_t r = 0;  // REDUCE: elements summed per row (R)
     int red_op = 0; // REDUCE: 0 = sum, 1 = maximum (fmaxf)
@@ -185,7 +189,21 @@ struct Plan {
     bool exact_div = false;  // 1/x and sqrt correctly rounded instead of the <= 1 ulp hardware approximations
 };
 
+// buffers a kernel reads and writes (a GROUP: those of all its members); appended to rd / wr
+inline void kernel_rw(const Plan& p, int kernel, std::vector<int>& rd, std::vector<int>& wr) {
+    const KernelSpec& k = p.kernels[size_t(kernel)];
+    if (k.type == KernelSpec::GROUP) {
+        for (int m : k.members) kernel_rw(p, m, rd, wr);
+        return;
+    }
+    for (auto& in : k.ins) rd.push_back(in.buf);
+    for (auto& o : k.outs) wr.push_back(o.dst.buf);
+    for (auto& r : k.reds) wr.push_back(r.dst.buf);
+    for (auto& ph : k.phases) wr.push_back(ph.dst.buf);
+}
+
 struct LowerOptions {
+    bool no_grouping = false;       // every kernel in a launch of its own
     bool no_fusion = false;
     bool no_reduce_fusion = false;  // keep every Sum in a kernel of its own
     bool fuse_small_sums = false;   // fold sums into element-wise kernels of any size (the thresholds only exist for speed)

@@ -266,9 +266,10 @@ class Executor {
         return reinterpret_cast<float*>(d_->arena + b.arena_off) + elem_off;
     }
 
-    void launch_kernel(const KernelSpec& k, int slot) {
+    // argument block and grid of one generated kernel
+    void kernel_launch_shape(const KernelSpec& k, std::vector<uint64_t>& args, dim3& grid) {
         // Args { const float* in[max(1,NI)]; float* out[NO + sums]; long long n; }
-        std::vector<uint64_t> args;
+        args.clear();
         size_t ni = std::max<size_t>(1, k.ins.size());
         const size_t no = k.outs.size() + k.reds.size();
         args.resize(ni + no + 1, 0);
@@ -278,7 +279,7 @@ class Executor {
         for (size_t i = 0; i < k.reds.size(); i++)
             args[ni + k.outs.size() + i] = uint64_t(uintptr_t(buf_ptr(k.reds[i].dst.buf, k.reds[i].dst.offset)));
         args[ni + no] = uint64_t(k.n);
-        dim3 grid(1, 1, 1), block(256, 1, 1);
+        grid = dim3(1, 1, 1);
         const int64_t cap = int64_t(d_->sm_count) * 16;
         if (k.type == KernelSpec::ROWS) {
             // one block per row at a time; phase results follow the outputs in the argument block
@@ -308,10 +309,33 @@ class Executor {
             grid.x = unsigned(std::max<int64_t>(1, (k.n + 32 * k.vec - 1) / (32 * k.vec)));
             grid.y = unsigned(k.split);
         }
+    }
+
+    void launch_kernel(const KernelSpec& k, int slot) {
+        std::vector<uint64_t> args;
+        dim3 grid(1, 1, 1), block(256, 1, 1);
+        if (k.type == KernelSpec::GROUP) {
+            // the members' argument blocks one after another, then the first block index of every member
+            std::vector<uint64_t> one;
+            std::vector<uint32_t> start = {0};
+            for (int m : k.members) {
+                dim3 g;
+                kernel_launch_shape(plan_.kernels[size_t(m)], one, g);
+                if (g.y != 1 || g.z != 1) throw CudaFail{"internal: grouped kernel with a 2-d grid"};
+                args.insert(args.end(), one.begin(), one.end());
+                start.push_back(start.back() + g.x);
+            }
+            if (start.size() & 1) start.push_back(0);
+            for (size_t i = 0; i < start.size(); i += 2) args.push_back(uint64_t(start[i]) | (uint64_t(start[i + 1]) << 32));
+            grid.x = start[k.members.size()];
+        } else {
+            kernel_launch_shape(k, args, grid);
+        }
         void* params[1] = {args.data()};
         ck(cudaLaunchKernel((const void*)d_->kernels[slot].fn, grid, block, params, 0, cur_stream_), k.entry.c_str());
         launches_++;
     }
+
 
     static double operand_bytes(const Operand& o) {
         double n = 1;
@@ -320,8 +344,9 @@ class Executor {
         return 4.0 * n;
     }
     // bytes a kernel has to move: every distinct operand once
-    static double kernel_bytes(const KernelSpec& k) {
+    double kernel_bytes(const KernelSpec& k) const {
         double b = 0;
+        for (int m : k.members) b += kernel_bytes(plan_.kernels[size_t(m)]);
         for (auto& in : k.ins) b += operand_bytes(in);
         for (auto& o : k.outs) b += k.type == KernelSpec::REDUCE ? 4.0 * double(k.n) * double(k.split) : operand_bytes(o.dst);
         for (auto& r : k.reds) b += operand_bytes(r.dst);
@@ -490,12 +515,9 @@ class Executor {
     void step_buffers(const Step& s, std::vector<int>& bufs) const {
         bufs.clear();
         switch (s.kind) {
-        case Step::ELW: case Step::REDUCE: {
-            const KernelSpec& k = plan_.kernels[s.kernel];
-            for (auto& in : k.ins) bufs.push_back(in.buf);
-            for (auto& o : k.outs) bufs.push_back(o.dst.buf);
+        case Step::ELW: case Step::REDUCE:
+            kernel_rw(plan_, s.kernel, bufs, bufs);
             break;
-        }
         case Step::GEMM:
             bufs = {s.gemm.a, s.gemm.b, s.gemm.c};
             if (s.gemm.out >= 0) bufs.push_back(s.gemm.out);
@@ -874,6 +896,7 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
         opt.no_fusion = (d->flags & ADB_FLAG_NO_FUSION) != 0;
         opt.exact_div = (d->flags & ADB_FLAG_EXACT_DIV) != 0;
         opt.fuse_small_sums = (d->flags & ADB_FLAG_FUSE_SMALL_SUMS) != 0;
+        opt.no_grouping = (d->flags & ADB_FLAG_NO_GROUPING) != 0;
         opt.rank = d->rank;
         opt.world = d->world;
         opt.sm_count = d->sm_count;
@@ -881,7 +904,7 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
         generate_kernels(fresh->plan);
         fresh->kernel_slot.resize(fresh->plan.kernels.size());
         for (size_t i = 0; i < fresh->plan.kernels.size(); i++)
-            fresh->kernel_slot[i] = fresh->plan.kernels[i].dead ? -1 : ensure_kernel(d, fresh->plan.kernels[i]);
+            fresh->kernel_slot[i] = (fresh->plan.kernels[i].dead || fresh->plan.kernels[i].grouped) ? -1 : ensure_kernel(d, fresh->plan.kernels[i]);
         fresh->plan.key = key;
         fresh->lower_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
         d->stats.lower_ms = fresh->lower_ms;
@@ -1241,6 +1264,7 @@ adb_status adb_lower_check(const uint8_t* blob, size_t nbytes, const adb_config*
             opt.no_fusion = (cfg->flags & ADB_FLAG_NO_FUSION) != 0;
             opt.exact_div = (cfg->flags & ADB_FLAG_EXACT_DIV) != 0;
             opt.fuse_small_sums = (cfg->flags & ADB_FLAG_FUSE_SMALL_SUMS) != 0;
+            opt.no_grouping = (cfg->flags & ADB_FLAG_NO_GROUPING) != 0;
             opt.rank = cfg->rank;
             opt.world = cfg->world_size > 0 ? cfg->world_size : 1;
             std::vector<std::string> ids = config_shard_ids(cfg);
@@ -1251,7 +1275,7 @@ adb_status adb_lower_check(const uint8_t* blob, size_t nbytes, const adb_config*
         generate_kernels(plan);
         std::unordered_map<std::string, bool> done;
         for (auto& k : plan.kernels) {
-            if (k.dead || done.count(k.entry)) continue;
+            if (k.dead || k.grouped || done.count(k.entry)) continue;
             done[k.entry] = true;
             std::vector<char> cubin;
             std::string log;

@@ -95,6 +95,8 @@ typedef struct adb_config {
 #define ADB_FLAG_FUSE_SMALL_SUMS 128u /* fold sums into neighbouring element-wise kernels whatever their size (by default
                                          only above 2^18 elements and 128 columns, where it pays); lets small tests reach
                                          that path */
+#define ADB_FLAG_NO_GROUPING 256u     /* every generated kernel in a launch of its own (by default independent kernels
+                                         that follow one another share one grid) */
 
 /* Replaces OpenCL::new (src/devices/opencl/device.rs:41-58) + autodiff::set_device's device slot
  * (src/core/autodiff.rs:82-97).  Fails with ADB_ERR_NO_DEVICE when no GPU is present. */

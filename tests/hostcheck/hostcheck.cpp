@@ -27,20 +27,16 @@
 //   1. step positions increase in execution order (nested blocks lie between their parent and its successor);
 //   2. a buffer is alive at every step that touches it (external and whole-program buffers always are);
 //   3. buffers that are alive at the same time do not overlap in the arena;
-//   5. a dot product never writes into one of its own operands.
+//   5. a dot product never writes into one of its own operands;
+//   6. the kernels that share one launch are independent: none writes a buffer that another reads or writes.
 // Returns an empty string or a description of the first violation.
 static void step_buffers(const adb::Plan& plan, const adb::Step& s, std::vector<int>& bufs) {
     using adb::Step;
     bufs.clear();
     switch (s.kind) {
-    case Step::ELW: case Step::REDUCE: {
-        const adb::KernelSpec& k = plan.kernels[size_t(s.kernel)];
-        for (auto& in : k.ins) bufs.push_back(in.buf);
-        for (auto& o : k.outs) bufs.push_back(o.dst.buf);
-        for (auto& r : k.reds) bufs.push_back(r.dst.buf);
-        for (auto& ph : k.phases) bufs.push_back(ph.dst.buf);
+    case Step::ELW: case Step::REDUCE:
+        adb::kernel_rw(plan, s.kernel, bufs, bufs);
         break;
-    }
     case Step::GEMM:
         bufs = {s.gemm.a, s.gemm.b, s.gemm.c};
         if (s.gemm.out >= 0) bufs.push_back(s.gemm.out);
@@ -60,6 +56,20 @@ static std::string check_block(const adb::Plan& plan, const adb::StepBlock& blk,
         last_pos = s.pos;
         if ((s.kind == adb::Step::ELW || s.kind == adb::Step::REDUCE) && plan.kernels[size_t(s.kernel)].dead)
             return "step at " + std::to_string(s.pos) + " runs a kernel that was marked dead";
+        if ((s.kind == adb::Step::ELW || s.kind == adb::Step::REDUCE) && plan.kernels[size_t(s.kernel)].type == adb::KernelSpec::GROUP) {
+            const auto& g = plan.kernels[size_t(s.kernel)];
+            for (size_t x = 0; x < g.members.size(); x++)
+                for (size_t y = 0; y < g.members.size(); y++) {
+                    if (x == y) continue;
+                    std::vector<int> rx, wx, ry, wy;
+                    adb::kernel_rw(plan, g.members[x], rx, wx);
+                    adb::kernel_rw(plan, g.members[y], ry, wy);
+                    for (int w : wx) {
+                        for (int r : ry) if (w == r) return "grouped launch at " + std::to_string(s.pos) + ": a member reads '" + plan.bufs[size_t(w)].name + "' that another member writes";
+                        for (int r : wy) if (w == r) return "grouped launch at " + std::to_string(s.pos) + ": two members write '" + plan.bufs[size_t(w)].name + "'";
+                    }
+                }
+        }
         if (s.kind == adb::Step::GEMM && (s.gemm.c == s.gemm.a || s.gemm.c == s.gemm.b || (s.gemm.out >= 0 && (s.gemm.out == s.gemm.a || s.gemm.out == s.gemm.b))))
             return "dot product at " + std::to_string(s.pos) + " writes into one of its operands";
         step_buffers(plan, s, bufs);
@@ -164,6 +174,7 @@ int main(int argc, char** argv) {
                 opt.fuse_small_sums = flags & 2;
                 opt.exact_div = flags & 4;
                 opt.no_dot_epilogue = flags & 16;
+                opt.no_grouping = flags & 32;
                 opt.rank = rank;
                 opt.world = world;
                 if (world > 1 && batch) adb::shard_program(prog, rank, world, batch);

@@ -164,7 +164,13 @@ struct PlanInterp {
 
     void run_step(const Step& s) {
         switch (s.kind) {
-        case Step::ELW: case Step::REDUCE: run_kernel(plan.kernels[size_t(s.kernel)]); break;
+        case Step::ELW: case Step::REDUCE: {
+            const KernelSpec& k = plan.kernels[size_t(s.kernel)];
+            // a group's members are independent of one another: any order gives the same memory
+            if (k.type == KernelSpec::GROUP) for (size_t m = k.members.size(); m-- > 0;) run_kernel(plan.kernels[size_t(k.members[m])]);
+            else run_kernel(k);
+            break;
+        }
         case Step::GEMM: {
             const auto& g = s.gemm;
           for (int64_t slice = 0; slice < g.batch; slice++) {

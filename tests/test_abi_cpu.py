@@ -68,6 +68,11 @@ class _LowerOnly:
         return adb.autodiff.ValueData([1], np.zeros(1, np.float32), id_, False)
 
 
+def _kernel_lines(plan):
+    """One line per step of the plan listing; the members of a grouped launch ('  - ...') count as steps."""
+    return [l for l in plan.splitlines() if l.startswith("#") or l.lstrip().startswith("- ")]
+
+
 @pytest.mark.parametrize("name", sorted(ref_programs.ALL))
 def test_reference_programs_lower_and_compile(name):
     dev = _LowerOnly()
@@ -79,7 +84,7 @@ def test_fusion_shapes_of_the_benchmark_programs():
     cfg = adb.configs
     dev = _LowerOnly()
     cfg.c2_fused_elementwise(dev, rows=64, cols=128)
-    steps = [l for l in dev.plan.splitlines() if l.startswith("#")]
+    steps = _kernel_lines(dev.plan)
     # forward chain fused into the row sum; both input gradients from one element-wise kernel
     assert any(" reduce " in l and "ops=2" in l for l in steps)
     assert sum(" elw n=8192" in l for l in steps) == 1
@@ -99,7 +104,7 @@ def test_sums_ride_along_with_the_element_wise_pass_over_the_same_memory():
     cfg = adb.configs
     dev = _LowerOnly(with_source=True)
     cfg.c2_fused_elementwise(dev, rows=512, cols=1024)
-    steps = [l for l in dev.plan.splitlines() if l.startswith("#")]
+    steps = _kernel_lines(dev.plan)
     big = [l for l in steps if " elw n=524288" in l or "rows=512 len=1024" in l or "rows=1024 len=512" in l]
     assert len(big) == 1 and "adb_elwsum_" in big[0], steps
     assert dev.plan.count("    sum v") == 2
@@ -124,7 +129,7 @@ def test_normalisation_layers_lower_to_one_kernel():
     y = adb.nn.LayerNorm(512).f(ad.tensor(x, [1024, 512])).forward()
     y.keep()
     ad.execute()
-    steps = [l for l in dev.plan.splitlines() if l.startswith("#")]
+    steps = _kernel_lines(dev.plan)
     assert sum(" rows [1024,512] phases=2" in l for l in steps) == 1 and not any(" reduce " in l for l in steps), steps
     assert "red0" in dev.plan and "red1" in dev.plan
 
@@ -134,7 +139,7 @@ def test_no_fusion_flag_gives_one_kernel_per_command():
     ref_programs.ct(dev)
     fused = _LowerOnly()
     ref_programs.ct(fused)
-    count = lambda p: sum(1 for l in p.splitlines() if l.startswith("#") and " elw " in l)
+    count = lambda p: sum(1 for l in _kernel_lines(p) if " elw " in l)
     assert count(dev.plan) > 20 and count(fused.plan) == 1
 
 

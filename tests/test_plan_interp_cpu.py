@@ -71,7 +71,7 @@ def _compare(got, kept, tol, atol=0.0):
         assert diff <= tol * scale + atol, f"{name}: error {diff:.3e} on a tensor of magnitude {scale:.3e}"
 
 
-@pytest.mark.parametrize("flags", [0, 1, 2], ids=["default", "one-kernel-per-command", "fusions-at-any-size"])
+@pytest.mark.parametrize("flags", [0, 1, 2, 32], ids=["default", "one-kernel-per-command", "fusions-at-any-size", "one-launch-per-kernel"])
 def test_reference_and_benchmark_programs(hostcheck, tmp_path, flags):
     programs = [(n, ref_programs.ALL[n], {}) for n in sorted(ref_programs.ALL)]
     programs += [("c1", cfg.c1_readme_mlp, {}),
@@ -285,3 +285,21 @@ def test_matrix_vector_products_through_the_reduce_kernels(hostcheck, tmp_path, 
     ad.execute()
     for flags in (0, 2):
         _compare(_interpret(hostcheck, tmp_path, dev.blobs[-1], flags, f"mv{flags}"), {y.id: y.get()}, 1e-5)
+
+
+def test_independent_kernels_share_one_launch(hostcheck, tmp_path):
+    """Row sums of a, an element-wise kernel over a and b, and a product-fed sum: kernels that do not depend on one
+    another become one launch (hostcheck also verifies, for every plan it sees, that no member of such a launch
+    touches what another member writes); the flag that turns grouping off gives the same results."""
+    rng = np.random.default_rng(3)
+    A, B = rng.standard_normal(96).astype(np.float32), rng.standard_normal(96).astype(np.float32)
+    proc, dep = _raw([("CreateMat", A, [2, 48], "a"), ("CreateMat", B, [2, 48], "b"), ("CreateConstant", 3.0, "k", [2, 48]),
+                      ("ElwMultiply", "a", "a", "x"), ("ElwAdd", "b", "b", "y"), ("Sum", "x", "s"),
+                      ("ElwMultiply", "y", "k", "z"), ("ElwAdd", "x", "y", "w")], ["x", "y", "s", "z", "w"])
+    dev = _Both()
+    dev.execute(proc, dep)
+    kept = {d: dev.get_tensor(d) for d in dep}
+    assert "group of 2 kernels in one launch" in adb.devices.lower_check(proc, dep)
+    assert "group of" not in adb.devices.lower_check(proc, dep, flags=adb.devices.FLAG_NO_GROUPING)
+    for flags in (0, 32):
+        _compare(_interpret(hostcheck, tmp_path, dev.blobs[-1], flags, f"group{flags}"), kept, 1e-6)
