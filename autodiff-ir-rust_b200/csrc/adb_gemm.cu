@@ -953,7 +953,7 @@ static bool plan_k_split(tc::Params& p, long long tiles, int workers, const Gemm
     p.k_splits = 1;
     p.kb_per_split = p.k_blocks;
     // a chain that runs on the finished sum needs one owner per tile
-    if (a.epi.mode == 2) return true;
+    if (a.epi.mode == 2 || a.no_k_split) return true;
     if (p.k_blocks < 2 * CHUNK_KB || workers <= 0) return true;
     auto cost = [&](long long per, long long splits) {
         const long long units = tiles * splits, waves = (units + workers - 1) / workers;

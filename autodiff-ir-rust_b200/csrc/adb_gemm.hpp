@@ -33,6 +33,7 @@ struct GemmArgs {
     int64_t batch = 1, a_bs = 0, b_bs = 0, c_bs = 0; // batched product: slices this many elements apart
     bool force_simt = false;
     bool no_pair = false;  // keep the tensor-core kernel on one SM per tile
+    bool no_k_split = false;  // one owner per output tile: the order of the additions into C never depends on timing
     int reserve_sms = 0;   // leave this many SMs to a kernel running beside the product (a collective on another stream)
     GemmEpilogue epi;
 };

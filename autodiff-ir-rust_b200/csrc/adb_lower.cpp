@@ -2424,9 +2424,10 @@ class Lowerer {
     // optimiser step, the pieces of a concat, a gradient that is a constant fill next to the sums that feed the
     // next layer).  Launched one after another each pays a launch and leaves most SMs idle; here they become one
     // GROUP kernel whose grid is the concatenation of the members' grids.  A member may be picked from further down
-    // the step list when nothing it would jump over (or join) writes what it reads or touches what it writes.  At most
-    // one member may be large: the small ones then run in its shadow.  The reference's fusion passes merge kernels
-    // only along producer -> consumer edges (src/kernel/fusion/elw.rs, reduce_elw.rs); it has no counterpart of this.
+    // the step list when nothing it would jump over (or join) writes what it reads or touches what it writes.  Only
+    // small kernels are grouped: a large one would hold back everything that waits for the group, and the executor
+    // already lets independent kernels of a captured graph run side by side.  The reference's fusion passes merge
+    // kernels only along producer -> consumer edges (src/kernel/fusion/elw.rs, reduce_elw.rs); it has no counterpart.
     static constexpr int64_t GROUP_BIG = int64_t(1) << 22;
     static constexpr size_t GROUP_MAX = 8, GROUP_LOOKAHEAD = 24;
     static int64_t kernel_work(const KernelSpec& k) {
@@ -2447,7 +2448,7 @@ class Lowerer {
         if (s.kind != Step::ELW && s.kind != Step::REDUCE) return false;
         if (size_t(s.kernel) >= uses.size() || uses[size_t(s.kernel)] != 1) return false;
         const KernelSpec& k = plan_.kernels[size_t(s.kernel)];
-        if (k.dead || k.type == KernelSpec::GROUP) return false;
+        if (k.dead || k.type == KernelSpec::GROUP || kernel_work(k) > GROUP_BIG) return false;
         if (k.type == KernelSpec::ELW && (!k.reds.empty() || elw_uses_tile(k))) return false;   // 2-d grids, 16 KB of shared memory
         if (k.type == KernelSpec::REDUCE && (k.split != 1 || k.scratch >= 0)) return false;
         // the kernel that scales the operand of a collective stays next to it (the runtime moves the pair to the
@@ -2467,16 +2468,10 @@ class Lowerer {
             if (!groupable(steps, i, uses)) continue;
             std::vector<size_t> members = {i};
             step_rw(steps[i], seen_rd, seen_wr);
-            int big = kernel_work(plan_.kernels[size_t(steps[i].kernel)]) > GROUP_BIG ? 1 : 0;
             for (size_t j = i + 1; j < steps.size() && j <= i + GROUP_LOOKAHEAD && members.size() < GROUP_MAX; j++) {
                 if (is_barrier(steps[j])) break;
                 step_rw(steps[j], rd, wr);
                 bool ok = groupable(steps, j, uses) && !hits(seen_wr, rd) && !hits(seen_wr, wr) && !hits(wr, seen_rd);
-                if (ok) {
-                    const int b = kernel_work(plan_.kernels[size_t(steps[j].kernel)]) > GROUP_BIG ? 1 : 0;
-                    if (big + b > 1) ok = false;
-                    else big += b;
-                }
                 if (ok) members.push_back(j);
                 seen_rd.insert(seen_rd.end(), rd.begin(), rd.end());
                 seen_wr.insert(seen_wr.end(), wr.begin(), wr.end());

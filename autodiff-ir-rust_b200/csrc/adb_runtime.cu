@@ -149,6 +149,8 @@ struct adb_device {
     cudaStream_t stream = nullptr;
     cudaStream_t copy_stream = nullptr;  // host->device prefetch of in-loop payloads
     cudaStream_t comm_stream = nullptr;  // collectives (and the small kernels that feed them), high priority
+    static constexpr int SIDE_LANES = 3;
+    cudaStream_t lane_stream[SIDE_LANES] = {};  // kernels that do not depend on one another, while a graph is captured
     std::string err;
     // kernels compiled so far, by entry name
     std::unordered_map<std::string, int> kernel_index;
@@ -386,6 +388,7 @@ class Executor {
             a.batch = g.batch; a.a_bs = g.a_bs; a.b_bs = g.b_bs; a.c_bs = g.c_bs;
             a.force_simt = (d_->flags & ADB_FLAG_SIMT_DOT) != 0;
             a.no_pair = (d_->flags & ADB_FLAG_SINGLE_SM_DOT) != 0;
+            a.no_k_split = (d_->flags & ADB_FLAG_DETERMINISTIC) != 0;
             a.reserve_sms = gemm_reserve_;
             if (g.epi != Step::Gemm::EPI_NONE) {
                 a.epi.mode = int(g.epi);
@@ -599,6 +602,7 @@ class Executor {
     void run_range(const StepBlock& blk, size_t begin, size_t end) {
         RangeSched& rs = schedule(blk, begin, end);
         if (!rs.any_comm) {
+            if (capturing_ && !(d_->flags & ADB_FLAG_SERIAL_GRAPHS) && end - begin >= 3) { run_range_lanes(blk, begin, end); return; }
             for (size_t t = begin; t < end; t++) run_step(blk.steps[t]);
             return;
         }
@@ -625,6 +629,119 @@ class Executor {
             }
         }
         if (last_comm >= 0) ck(cudaStreamWaitEvent(d_->stream, rs.steps[size_t(last_comm)].done, 0), "join");
+    }
+
+    // While a graph is captured, generated kernels that do not depend on one another are issued on different streams, so
+    // the graph holds their true dependencies and the GPU may run them side by side (a gradient that is a constant
+    // fill beside the reductions that feed the next layer; the many small kernels of a small network).  Dependencies
+    // are taken on the memory ranges each kernel reads and writes.  Dot products, collectives and copies stay on the
+    // main stream and everything issued before them is joined first: a dot product fills every SM by itself.
+    struct LaneAccess { uintptr_t lo, hi; bool write; };
+    void lane_accesses(const Step& s, std::vector<LaneAccess>& acc) {
+        acc.clear();
+        std::vector<int> rd, wr;
+        kernel_rw(plan_, s.kernel, rd, wr);
+        auto add = [&](int b, bool w) {
+            uintptr_t lo = reinterpret_cast<uintptr_t>(buf_ptr(b));
+            acc.push_back({lo, lo + uintptr_t(plan_.bufs[size_t(b)].numel) * 4, w});
+        };
+        for (int b : rd) add(b, false);
+        for (int b : wr) add(b, true);
+    }
+    static bool lane_conflict(const std::vector<LaneAccess>& a, const std::vector<LaneAccess>& b) {
+        for (auto& x : a)
+            for (auto& y : b)
+                if ((x.write || y.write) && x.lo < y.hi && y.lo < x.hi) return true;
+        return false;
+    }
+    void run_range_lanes(const StepBlock& blk, size_t begin, size_t end) {
+        constexpr int L = adb_device::SIDE_LANES + 1;
+        cudaStream_t lane[L];
+        lane[0] = d_->stream;
+        for (int l = 1; l < L; l++) {
+            if (!d_->lane_stream[l - 1]) ck(cudaStreamCreateWithFlags(&d_->lane_stream[l - 1], cudaStreamNonBlocking), "cudaStreamCreate");
+            lane[l] = d_->lane_stream[l - 1];
+        }
+        // events only carry the dependencies into the captured graph; they can go once the capture of this range is over
+        struct Events {
+            std::vector<cudaEvent_t> all;
+            ~Events() { for (auto e : all) cudaEventDestroy(e); }
+        } events;
+        auto record = [&](cudaStream_t st) {
+            cudaEvent_t e;
+            ck(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "event create");
+            events.all.push_back(e);
+            ck(cudaEventRecord(e, st), "event");
+            return e;
+        };
+        struct Issued { int lane; cudaEvent_t done; std::vector<LaneAccess> acc; };
+        std::vector<Issued> issued;          // kernels since the last join
+        int lane_last[L];                    // index into `issued` of the last kernel on each lane, -1 = none since the join
+        bool forked[L];
+        cudaEvent_t fork = nullptr;          // recorded on the main stream at the last join
+        auto reset = [&]() {
+            issued.clear();
+            for (int l = 0; l < L; l++) { lane_last[l] = -1; forked[l] = l == 0; }
+            fork = nullptr;
+        };
+        auto join = [&]() {
+            for (int l = 1; l < L; l++)
+                if (lane_last[l] >= 0) ck(cudaStreamWaitEvent(lane[0], issued[size_t(lane_last[l])].done, 0), "join");
+            reset();
+        };
+        reset();
+        std::vector<LaneAccess> acc;
+        std::vector<char> dep;
+        for (size_t t = begin; t < end; t++) {
+            const Step& s = blk.steps[t];
+            if (s.kind != Step::ELW && s.kind != Step::REDUCE) {
+                join();
+                run_step(s);
+                continue;
+            }
+            if (!fork) fork = record(lane[0]);
+            lane_accesses(s, acc);
+            dep.assign(issued.size(), 0);
+            for (size_t i = 0; i < issued.size(); i++) dep[i] = lane_conflict(acc, issued[i].acc) ? 1 : 0;
+            // the lane whose last kernel this one waits for anyway (the latest such kernel), else an idle lane
+            int pick = -1;
+            for (int l = 0; l < L; l++)
+                if (lane_last[l] >= 0 && dep[size_t(lane_last[l])] && (pick < 0 || lane_last[l] > lane_last[pick])) pick = l;
+            if (pick < 0)
+                for (int l = 0; l < L && pick < 0; l++)
+                    if (lane_last[l] < 0) pick = l;
+            if (pick < 0) {
+                pick = 0;
+                for (int l = 1; l < L; l++)
+                    if (lane_last[l] < lane_last[pick]) pick = l;
+            }
+            if (!forked[pick]) {
+                ck(cudaStreamWaitEvent(lane[pick], fork, 0), "fork");
+                forked[pick] = true;
+            }
+            for (int l = 0; l < L; l++) {
+                if (l == pick) continue;
+                int latest = -1;
+                for (size_t i = 0; i < issued.size(); i++)
+                    if (dep[i] && issued[i].lane == l) latest = int(i);
+                if (latest >= 0) ck(cudaStreamWaitEvent(lane[pick], issued[size_t(latest)].done, 0), "lane waits");
+            }
+            cur_stream_ = lane[pick];
+            try {
+                run_step(s);
+            } catch (...) {
+                cur_stream_ = d_->stream;
+                throw;
+            }
+            cur_stream_ = d_->stream;
+            Issued rec;
+            rec.lane = pick;
+            rec.done = record(lane[pick]);
+            rec.acc = acc;
+            issued.push_back(std::move(rec));
+            lane_last[pick] = int(issued.size()) - 1;
+        }
+        join();
     }
 
     static bool capturable(const Step& s, const Plan& plan) {
@@ -1153,6 +1270,7 @@ void adb_destroy(adb_device* d) {
     if (d->stream) cudaStreamSynchronize(d->stream);
     if (d->copy_stream) cudaStreamSynchronize(d->copy_stream);
     if (d->comm_stream) cudaStreamSynchronize(d->comm_stream);
+    for (auto& ls : d->lane_stream) if (ls) cudaStreamSynchronize(ls);
     for (auto& kv : d->plans) { destroy_graphs(*kv.second); destroy_prefetch(*kv.second); destroy_sched(*kv.second); }
     d->plans.clear();
     for (auto& k : d->kernels)
@@ -1168,6 +1286,7 @@ void adb_destroy(adb_device* d) {
     if (d->cond_host) cudaFreeHost(d->cond_host);
     if (d->copy_stream) cudaStreamDestroy(d->copy_stream);
     if (d->comm_stream) cudaStreamDestroy(d->comm_stream);
+    for (auto& ls : d->lane_stream) if (ls) cudaStreamDestroy(ls);
     if (d->stream) cudaStreamDestroy(d->stream);
     delete d;
 }

@@ -27,6 +27,8 @@ STATUS = {0: "ADB_OK", 1: "ADB_NONE", 2: "ADB_ERR_INVALID", 3: "ADB_ERR_CUDA", 4
 
 FLAG_NO_GRAPHS, FLAG_NO_FUSION, FLAG_SIMT_DOT, FLAG_PROFILE, FLAG_COMM_STREAM, FLAG_SINGLE_SM_DOT, FLAG_EXACT_DIV, FLAG_FUSE_SMALL_SUMS = 1, 2, 4, 8, 16, 32, 64, 128
 FLAG_NO_GROUPING = 256
+FLAG_DETERMINISTIC = 512
+FLAG_SERIAL_GRAPHS = 1024
 
 EXPORTS = ["adb_create", "adb_destroy", "adb_execute", "adb_get_tensor", "adb_get_tensor_device",
            "adb_dot_prod_shape", "adb_last_error", "adb_get_stats", "adb_dump_plan", "adb_lower_check",

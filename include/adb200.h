@@ -95,6 +95,12 @@ typedef struct adb_config {
 #define ADB_FLAG_FUSE_SMALL_SUMS 128u /* fold sums into neighbouring element-wise kernels whatever their size (by default
                                          only above 2^18 elements and 128 columns, where it pays); lets small tests reach
                                          that path */
+#define ADB_FLAG_DETERMINISTIC 512u    /* dot products never split the k axis across clusters: by default a product with few
+                                         output tiles and a long k axis is cut into k ranges whose partial sums meet in C
+                                         through red.global.add, in an order that depends on timing (results then differ
+                                         in the last bits from run to run); with this flag every run gives the same bits */
+#define ADB_FLAG_SERIAL_GRAPHS 1024u   /* captured graphs keep the kernels in one chain (by default generated kernels that do not
+                                         depend on one another are captured on different streams and may run side by side) */
 #define ADB_FLAG_NO_GROUPING 256u     /* every generated kernel in a launch of its own (by default independent kernels
                                          that follow one another share one grid) */
 

@@ -176,3 +176,20 @@ def test_matrix_vector_products_run_as_row_sums(M, K, N, ta):
     g = np.asarray(got.data, np.float64).reshape(M, N)
     assert got.dim == [M, N]
     assert np.abs(g - ref).max() / np.abs(ref).max() < 1e-5
+
+
+def test_deterministic_flag_gives_the_same_bits_on_every_run():
+    """512 x 8192 x 512 is cut into k ranges by default (partial sums meet in C in timing order); with
+    FLAG_DETERMINISTIC one cluster owns each tile and ten runs give bit-identical results within the accuracy bar."""
+    M, K, N = 512, 8192, 512
+    a = RNG.standard_normal(M * K).astype(np.float32)
+    b = RNG.standard_normal(K * N).astype(np.float32)
+    dev = adb.devices.B200(0, flags=adb.devices.FLAG_DETERMINISTIC)
+    try:
+        runs = [np.asarray(_dot(dev, a, b, False, False, M, K, N).data, np.float32).copy() for _ in range(10)]
+    finally:
+        dev.close()
+    for r in runs[1:]:
+        np.testing.assert_array_equal(r, runs[0])
+    ref = a.reshape(M, K).astype(np.float64) @ b.reshape(K, N).astype(np.float64)
+    assert np.abs(runs[0].reshape(M, N) - ref).max() / np.abs(ref).max() < 2e-5
