@@ -1208,6 +1208,30 @@ class Lowerer {
                 return;
             }
         }
+        // A product of a few hundred multiply-adds is an element-wise expression: sum over k of (column k of A, repeated
+        // along the columns) * (row k of B, repeated along the rows), k ascending like the dot kernels.  It then fuses with
+        // whatever surrounds it (the whole training step of a 2 x 5 network becomes a handful of kernels instead of one
+        // launch per product), and the expression limit of after_op keeps chains of such products from growing.
+        if (!opt_.no_fusion && K <= TINY_DOT_K && M * N * K <= TINY_DOT_WORK) {
+            Node* acc = nullptr;
+            bool ok = true;
+            for (int64_t k = 0; k < K && ok; k++) {
+                Node* ak = g_.index(a, 1, k);
+                if (ak) ak = g_.reshape(ak, {M, 1});
+                if (ak) ak = g_.broadcast(ak, 1, N);
+                Node* bk = g_.index(b, 0, k);
+                if (bk) bk = g_.reshape(bk, {1, N});
+                if (bk) bk = g_.broadcast(bk, 0, M);
+                if (!ak || !bk) { ok = false; break; }
+                Node* t = elementwise2(E_MUL, ak, bk);
+                acc = acc ? elementwise2(E_ADD, acc, t) : t;
+                if (!acc) ok = false;
+            }
+            if (ok && acc) {
+                after_op(c.res, acc);
+                return;
+            }
+        }
         std::pair<Node*, Node*> dot_key{a, b};
         {
             auto it = dot_cse_.find(dot_key);
@@ -2428,6 +2452,7 @@ class Lowerer {
     // small kernels are grouped: a large one would hold back everything that waits for the group, and the executor
     // already lets independent kernels of a captured graph run side by side.  The reference's fusion passes merge
     // kernels only along producer -> consumer edges (src/kernel/fusion/elw.rs, reduce_elw.rs); it has no counterpart.
+    static constexpr int64_t TINY_DOT_K = 8, TINY_DOT_WORK = 256;
     static constexpr int64_t GROUP_BIG = int64_t(1) << 22;
     static constexpr size_t GROUP_MAX = 8, GROUP_LOOKAHEAD = 24;
     static int64_t kernel_work(const KernelSpec& k) {

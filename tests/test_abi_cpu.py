@@ -160,3 +160,17 @@ def test_read_before_definition_is_an_error_not_a_crash():
     with pytest.raises(adb.devices.AdbError) as e:
         adb.devices.lower_check(proc, {"c"})
     assert "before it is defined" in str(e.value)
+
+
+def test_products_of_a_few_multiply_adds_become_element_wise_expressions():
+    """The README-sized network (2 x 5 inputs, 3 hidden units): its six dot products are sums of at most five products
+    per element, so they fuse with the sigmoid, the loss and the update around them -- no dot-product launch is left;
+    with one kernel per command they are dot-product steps again."""
+    dev = _LowerOnly()
+    adb.configs.c1_readme_mlp(dev)
+    steps = [l for l in dev.plan.splitlines() if l.startswith("#") and " upload " not in l and " exit" not in l]
+    assert not any(" gemm " in l for l in steps), dev.plan
+    assert len(steps) <= 4, dev.plan
+    unfused = _LowerOnly(flags=adb.devices.FLAG_NO_FUSION)
+    adb.configs.c1_readme_mlp(unfused)
+    assert sum(" gemm " in l for l in unfused.plan.splitlines()) == 6
