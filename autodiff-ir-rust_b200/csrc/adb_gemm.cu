@@ -183,6 +183,7 @@ constexpr int STAGES = 2;
 // CHUNK_KB k-blocks (1024 elements): each chunk accumulates into a fresh TMEM buffer and the epilogue warps add
 // finished chunks into C with round-to-nearest fp32 adds (the C tile stays in L2 between chunks).
 constexpr int CHUNK_KB = 32;
+static_assert(CHUNK_KB * BK == GEMM_CHUNK_K, "accumulation chunk");
 constexpr int A_BYTES = BM * BK * 4;                  // 16 KiB
 constexpr int B_BYTES = BN * BK * 4;                  // 32 KiB
 constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);  // hi and lo copies of both operands: 96 KiB

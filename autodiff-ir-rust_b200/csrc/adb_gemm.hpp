@@ -11,6 +11,7 @@ namespace adb {
 // Element-wise work on the product while it is still in registers (see Step::Gemm in adb_plan.hpp): a chain
 // v = acc; v = op_i(v, operand_i).  Passed to the kernels by value.
 constexpr int GEMM_EPI_MAX_OPS = 12;
+constexpr int GEMM_CHUNK_K = 1024;   // k elements per accumulation chunk of the tensor-core kernels
 struct GemmEpilogue {
     int mode = 0;                 // 0 none, 1 scale (every partial product; optionally added to C), 2 chain on the finished sum
     int accumulate = 0;           // mode 1: C += scaled product instead of C = scaled product

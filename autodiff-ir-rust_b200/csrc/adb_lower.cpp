@@ -105,6 +105,7 @@ class Lowerer {
         fuse_reductions();
         if (!opt_.no_fusion && !opt_.no_dot_epilogue) fuse_dot_epilogues(plan_.main);
         if (!opt_.no_fusion) drop_unread_outputs();
+        if (opt_.bucket_collectives && opt_.world > 1 && scale_all(4)) bucket_collectives(plan_.main);
         if (!opt_.no_fusion && !opt_.no_grouping) {
             std::vector<int> uses(plan_.kernels.size(), 0);
             count_kernel_uses(plan_.main, uses);
@@ -1537,7 +1538,11 @@ class Lowerer {
             if (s.gemm.out >= 0) wr.push_back(s.gemm.out);
             break;
         case Step::UPLOAD: wr = {s.buf}; break;
-        case Step::ALLREDUCE: rd = {s.buf}; wr = {s.buf}; break;
+        case Step::ALLREDUCE:
+            rd = {s.buf};
+            rd.insert(rd.end(), s.more_bufs.begin(), s.more_bufs.end());
+            wr = rd;
+            break;
         default: break;
         }
     }
@@ -1549,25 +1554,30 @@ class Lowerer {
     }
     static bool is_barrier(const Step& s) { return s.kind == Step::WHILE || s.kind == Step::IF || s.kind == Step::EXIT; }
 
-    void scale_positions(StepBlock& blk) {
+    void scale_positions(StepBlock& blk, int f) {
         for (auto& s : blk.steps) {
-            s.pos *= POS_SCALE;
-            if (s.body) scale_positions(*s.body);
-            for (auto& br : s.branches) scale_positions(*br.body);
-            if (s.else_body) scale_positions(*s.else_body);
+            s.pos *= f;
+            if (s.body) scale_positions(*s.body, f);
+            for (auto& br : s.branches) scale_positions(*br.body, f);
+            if (s.else_body) scale_positions(*s.else_body, f);
         }
+    }
+    // multiplies every step position (and everything measured in positions) by f: room for steps that passes add
+    bool scale_all(int f) {
+        if (pos_ >= INT_MAX / f - 1) return false;
+        scale_positions(plan_.main, f);
+        for (auto& b : plan_.bufs) {
+            if (b.first != INT_MAX) b.first *= f;
+            if (b.last >= 0) b.last *= f;
+        }
+        for (auto& sp : loop_spans_) { sp.first *= f; sp.second *= f; }
+        pos_ *= f;
+        return true;
     }
 
     void fuse_reductions() {
         if (opt_.no_fusion || opt_.no_reduce_fusion) return;
-        if (pos_ >= INT_MAX / POS_SCALE - 1) return;
-        scale_positions(plan_.main);
-        for (auto& b : plan_.bufs) {
-            if (b.first != INT_MAX) b.first *= POS_SCALE;
-            if (b.last >= 0) b.last *= POS_SCALE;
-        }
-        for (auto& sp : loop_spans_) { sp.first *= POS_SCALE; sp.second *= POS_SCALE; }
-        pos_ *= POS_SCALE;
+        if (!scale_all(POS_SCALE)) return;
         fuse_rows(plan_.main);
         fuse_block(plan_.main);
         if (opt_.world > 1) hoist_collectives(plan_.main);
@@ -2306,6 +2316,11 @@ class Lowerer {
                 bool scale_only = true;
                 for (auto& op : ch.ops) scale_only = scale_only && op.op == E_MUL && op.operand == 1;
                 if (ch.acc_mat && !scale_only) continue;
+                // `W += s * product` inside the product would add every k chunk's partial sum to W on its own: each add
+                // rounds at the precision of W, and an update of a hundred ulps of W spread over 64 chunks comes out
+                // percents off (measured on the first layer of the benchmark network at batch 65536).  With more than
+                // one chunk the gradient is finished first and added once, by the element-wise kernel, as written.
+                if (ch.acc_mat && steps[gi].gemm.K > DOT_CHUNK_K) continue;
                 // who else reads the plain product?
                 int other_readers = 0;
                 all_readers(plan_.main, cb, nullptr, other_readers);
@@ -2443,6 +2458,82 @@ class Lowerer {
         }
     }
 
+    // ------------------------------------------------------------------ neighbouring collectives as one
+    // Data-parallel training all-reduces every gradient: four weight matrices and four bias vectors per step in the
+    // benchmark network, each collective paying its own latency and none of them long enough to reach the link's peak.
+    // An all-reduce of a temporary is held back until a step needs the buffer (or a block ends); the collectives held
+    // back together become one ALLREDUCE over buffers that the arena places side by side.  Kept tensors and buffers
+    // of the caller stay as they are.  (With collectives on their own stream the pass is off: there each collective
+    // should start as early as it can.)
+    bool bucketable(const Step& s) const {
+        if (s.kind != Step::ALLREDUCE || !s.more_bufs.empty() || s.off != 0) return false;
+        const BufferInfo& b = plan_.bufs[size_t(s.buf)];
+        if (b.external || s.nelem != b.numel || b.numel <= 0) return false;
+        for (auto& r : plan_.results)
+            if (r.buf == s.buf) return false;
+        for (auto& pk : plan_.packs)
+            for (int x : pk)
+                if (x == s.buf) return false;
+        return true;
+    }
+    void bucket_collectives(StepBlock& blk) {
+        for (auto& s : blk.steps) {
+            if (s.body) bucket_collectives(*s.body);
+            for (auto& br : s.branches) bucket_collectives(*br.body);
+            if (s.else_body) bucket_collectives(*s.else_body);
+        }
+        std::vector<Step> out;
+        std::vector<Step> held;            // collectives waiting for the first step that needs one of their buffers
+        std::vector<int> rd, wr;
+        auto flush = [&](int pos_before) {
+            if (held.empty()) return;
+            if (held.size() == 1) {
+                held[0].pos = std::max(held[0].pos, pos_before);
+                touch(held[0].buf, held[0].pos);
+                out.push_back(std::move(held[0]));
+                held.clear();
+                return;
+            }
+            Step m = std::move(held[0]);
+            std::vector<int> pack = {m.buf};
+            int64_t span = ((plan_.bufs[size_t(m.buf)].numel * 4 + 255) / 256) * 256;
+            for (size_t i = 1; i < held.size(); i++) {
+                m.more_bufs.push_back(held[i].buf);
+                pack.push_back(held[i].buf);
+                const int64_t bytes = plan_.bufs[size_t(held[i].buf)].numel * 4;
+                span += i + 1 < held.size() ? ((bytes + 255) / 256) * 256 : bytes;
+                m.pos = std::max(m.pos, held[i].pos);
+            }
+            m.pos = std::max(m.pos, pos_before);
+            m.nelem = span / 4;
+            for (int b : pack) touch(b, m.pos);
+            plan_.packs.push_back(std::move(pack));
+            out.push_back(std::move(m));
+            held.clear();
+        };
+        for (auto& s : blk.steps) {
+            if (bucketable(s)) {
+                bool dup = false;
+                for (auto& h : held) dup = dup || h.buf == s.buf;
+                if (!dup) { held.push_back(std::move(s)); continue; }
+            }
+            if (!held.empty()) {
+                bool needed = is_barrier(s);
+                if (!needed) {
+                    step_rw(s, rd, wr);
+                    for (auto& h : held)
+                        for (int b : {h.buf})
+                            needed = needed || std::find(rd.begin(), rd.end(), b) != rd.end() || std::find(wr.begin(), wr.end(), b) != wr.end();
+                }
+                // the merged collective takes the position of the last one held back; it must still lie in front of `s`
+                if (needed) flush(out.empty() ? INT_MIN : out.back().pos + 1);
+            }
+            out.push_back(std::move(s));
+        }
+        flush(out.empty() ? INT_MIN : out.back().pos + 1);
+        blk.steps = std::move(out);
+    }
+
     // ------------------------------------------------------------------ independent kernels in one launch
     // A step list often holds runs of small kernels that do not depend on one another (the bias updates of an
     // optimiser step, the pieces of a concat, a gradient that is a constant fill next to the sums that feed the
@@ -2576,8 +2667,39 @@ class Lowerer {
             } else
                 std::fill(is_result.begin(), is_result.end(), 0);
         }
+        auto lowest_fit = [&](int64_t size, int first, int last) {
+            std::vector<std::pair<int64_t, int64_t>> busy;
+            for (auto& p : placed)
+                if (!(p.last < first || last < p.first)) busy.push_back({p.off, p.off + p.size});
+            std::sort(busy.begin(), busy.end());
+            int64_t off = 0;
+            for (auto& iv : busy) {
+                if (off + size <= iv.first) break;
+                off = std::max(off, iv.second);
+            }
+            return off;
+        };
+        // buffers that one collective covers: one block, members in order, alive for as long as any member is
+        std::vector<char> packed(bufs.size(), 0);
+        for (auto& pk : plan_.packs) {
+            int64_t size = 0;
+            int first = INT_MAX, last = INT_MIN;
+            for (int i : pk) {
+                size += ((bufs[size_t(i)].numel * 4 + 255) / 256) * 256;
+                first = std::min(first, bufs[size_t(i)].persistent ? INT_MIN : bufs[size_t(i)].first);
+                last = std::max(last, bufs[size_t(i)].persistent ? INT_MAX : bufs[size_t(i)].last);
+            }
+            int64_t off = lowest_fit(size, first, last);
+            placed.push_back({off, size, first, last});
+            top = std::max(top, off + size);
+            for (int i : pk) {
+                bufs[size_t(i)].arena_off = off;
+                off += ((bufs[size_t(i)].numel * 4 + 255) / 256) * 256;
+                packed[size_t(i)] = 1;
+            }
+        }
         for (int i : order) {
-            if (is_result[size_t(i)]) continue;
+            if (is_result[size_t(i)] || packed[size_t(i)]) continue;
             auto& b = bufs[i];
             int first = b.persistent ? INT_MIN : b.first;
             int last = b.persistent ? INT_MAX : b.last;
@@ -2702,7 +2824,9 @@ static void dump_block(const Plan& p, const StepBlock& b, int ind, bool src, std
             o << pad << "#" << s.pos << " upload " << p.bufs[s.buf].name << " n=" << s.nelem << "\n";
             break;
         case Step::ALLREDUCE:
-            o << pad << "#" << s.pos << " allreduce " << p.bufs[s.buf].name << " n=" << s.nelem << "\n";
+            o << pad << "#" << s.pos << " allreduce " << p.bufs[s.buf].name;
+            for (int b : s.more_bufs) o << " + " << p.bufs[size_t(b)].name;
+            o << " n=" << s.nelem << "\n";
             break;
         case Step::WHILE:
             o << pad << "#" << s.pos << " while (" << p.bufs[s.cond_buf].name << "+" << s.cond_off << " != 0) {\n";

@@ -100,6 +100,9 @@ struct KernelSpec {
 
 struct StepBlock;
 
+// k elements the dot kernels accumulate in tensor memory before the partial sum is added into C with a rounded fp32 add
+constexpr int64_t DOT_CHUNK_K = 1024;
+
 struct Step {
     enum Kind { ELW, REDUCE, GEMM, UPLOAD, ALLREDUCE, WHILE, IF, EXIT } kind = EXIT;
     int pos = 0;
@@ -139,6 +142,9 @@ struct Step {
         std::vector<EpiOp> ops;
     } gemm;
     // UPLOAD: payload slot -> buffer; ALLREDUCE: buffer range
+    // (a bucketed ALLREDUCE covers `buf` and `more_bufs`, which the arena keeps side by side in that order: one
+    // collective over [start of buf, end of the last member))
+    std::vector<int> more_bufs;
     int buf = -1;
     int payload = -1;
     int64_t off = 0, nelem = 0;
@@ -182,6 +188,7 @@ struct Plan {
     std::vector<PayloadSlot> payloads;
     std::vector<ResultInfo> results;
     int64_t arena_bytes = 0;
+    std::vector<std::vector<int>> packs;   // buffers that must lie side by side in the arena, in this order
     int64_t results_bytes = 0;   // > 0: the kept tensors' buffers are the first `results_bytes` of the arena (one read-back copy)
     int n_steps = 0;
     size_t ir_commands = 0;
@@ -204,6 +211,7 @@ inline void kernel_rw(const Plan& p, int kernel, std::vector<int>& rd, std::vect
 
 struct LowerOptions {
     bool no_grouping = false;       // every kernel in a launch of its own
+    bool bucket_collectives = false;  // all-reduces of neighbouring gradients become one collective over adjacent buffers
     bool no_fusion = false;
     bool no_reduce_fusion = false;  // keep every Sum in a kernel of its own
     bool fuse_small_sums = false;   // fold sums into element-wise kernels of any size (the thresholds only exist for speed)

@@ -257,6 +257,8 @@ bool payload_uniform(const float* p, int64_t n, float v) {
     return n > 0;
 }
 
+static_assert(GEMM_CHUNK_K == DOT_CHUNK_K, "the lowering and the dot kernels must agree on the accumulation chunk");
+
 class Executor {
   public:
     Executor(adb_device* d, CompiledPlan* cp) : d_(d), cp_(cp), plan_(cp->plan) { cur_stream_ = d->stream; }
@@ -526,7 +528,10 @@ class Executor {
             if (s.gemm.out >= 0) bufs.push_back(s.gemm.out);
             if (s.gemm.colvec >= 0) bufs.push_back(s.gemm.colvec);
             break;
-        case Step::UPLOAD: case Step::ALLREDUCE: bufs = {s.buf}; break;
+        case Step::UPLOAD: case Step::ALLREDUCE:
+            bufs = {s.buf};
+            bufs.insert(bufs.end(), s.more_bufs.begin(), s.more_bufs.end());
+            break;
         default: break;
         }
     }
@@ -1014,6 +1019,7 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
         opt.exact_div = (d->flags & ADB_FLAG_EXACT_DIV) != 0;
         opt.fuse_small_sums = (d->flags & ADB_FLAG_FUSE_SMALL_SUMS) != 0;
         opt.no_grouping = (d->flags & ADB_FLAG_NO_GROUPING) != 0;
+        opt.bucket_collectives = d->world > 1 && !(d->flags & (ADB_FLAG_COMM_STREAM | ADB_FLAG_NO_BUCKETS));
         opt.rank = d->rank;
         opt.world = d->world;
         opt.sm_count = d->sm_count;
@@ -1384,6 +1390,7 @@ adb_status adb_lower_check(const uint8_t* blob, size_t nbytes, const adb_config*
             opt.exact_div = (cfg->flags & ADB_FLAG_EXACT_DIV) != 0;
             opt.fuse_small_sums = (cfg->flags & ADB_FLAG_FUSE_SMALL_SUMS) != 0;
             opt.no_grouping = (cfg->flags & ADB_FLAG_NO_GROUPING) != 0;
+            opt.bucket_collectives = cfg->world_size > 1 && !(cfg->flags & (ADB_FLAG_COMM_STREAM | ADB_FLAG_NO_BUCKETS));
             opt.rank = cfg->rank;
             opt.world = cfg->world_size > 0 ? cfg->world_size : 1;
             std::vector<std::string> ids = config_shard_ids(cfg);

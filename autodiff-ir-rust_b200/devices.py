@@ -29,6 +29,7 @@ FLAG_NO_GRAPHS, FLAG_NO_FUSION, FLAG_SIMT_DOT, FLAG_PROFILE, FLAG_COMM_STREAM, F
 FLAG_NO_GROUPING = 256
 FLAG_DETERMINISTIC = 512
 FLAG_SERIAL_GRAPHS = 1024
+FLAG_NO_BUCKETS = 2048
 
 EXPORTS = ["adb_create", "adb_destroy", "adb_execute", "adb_get_tensor", "adb_get_tensor_device",
            "adb_dot_prod_shape", "adb_last_error", "adb_get_stats", "adb_dump_plan", "adb_lower_check",

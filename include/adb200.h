@@ -101,6 +101,8 @@ typedef struct adb_config {
                                          in the last bits from run to run); with this flag every run gives the same bits */
 #define ADB_FLAG_SERIAL_GRAPHS 1024u   /* captured graphs keep the kernels in one chain (by default generated kernels that do not
                                          depend on one another are captured on different streams and may run side by side) */
+#define ADB_FLAG_NO_BUCKETS 2048u      /* every all-reduce of the data-parallel rewrite as a collective of its own (by default
+                                         the gradients that are reduced next to one another share one collective) */
 #define ADB_FLAG_NO_GROUPING 256u     /* every generated kernel in a launch of its own (by default independent kernels
                                          that follow one another share one grid) */
 

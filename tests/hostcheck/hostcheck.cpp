@@ -28,6 +28,7 @@
 //   2. a buffer is alive at every step that touches it (external and whole-program buffers always are);
 //   3. buffers that are alive at the same time do not overlap in the arena;
 //   5. a dot product never writes into one of its own operands;
+//   7. a collective over several buffers finds them side by side in the arena, in order, and covers exactly their span;
 //   6. the kernels that share one launch are independent: none writes a buffer that another reads or writes.
 // Returns an empty string or a description of the first violation.
 static void step_buffers(const adb::Plan& plan, const adb::Step& s, std::vector<int>& bufs) {
@@ -42,7 +43,10 @@ static void step_buffers(const adb::Plan& plan, const adb::Step& s, std::vector<
         if (s.gemm.out >= 0) bufs.push_back(s.gemm.out);
         if (s.gemm.colvec >= 0) bufs.push_back(s.gemm.colvec);
         break;
-    case Step::UPLOAD: case Step::ALLREDUCE: bufs = {s.buf}; break;
+    case Step::UPLOAD: case Step::ALLREDUCE:
+        bufs = {s.buf};
+        bufs.insert(bufs.end(), s.more_bufs.begin(), s.more_bufs.end());
+        break;
     case Step::WHILE: bufs = {s.cond_buf}; break;
     case Step::IF: for (auto& br : s.branches) bufs.push_back(br.cond_buf); break;
     default: break;
@@ -69,6 +73,20 @@ static std::string check_block(const adb::Plan& plan, const adb::StepBlock& blk,
                         for (int r : wy) if (w == r) return "grouped launch at " + std::to_string(s.pos) + ": two members write '" + plan.bufs[size_t(w)].name + "'";
                     }
                 }
+        }
+        if (s.kind == adb::Step::ALLREDUCE && !s.more_bufs.empty()) {
+            int64_t at = plan.bufs[size_t(s.buf)].arena_off;
+            std::vector<int> all = {s.buf};
+            all.insert(all.end(), s.more_bufs.begin(), s.more_bufs.end());
+            int64_t end = at;
+            for (size_t i = 0; i < all.size(); i++) {
+                const adb::BufferInfo& bi = plan.bufs[size_t(all[i])];
+                if (bi.external || bi.arena_off != at) return "collective at " + std::to_string(s.pos) + ": '" + bi.name + "' is not where the bucket expects it";
+                end = at + bi.numel * 4;
+                at += ((bi.numel * 4 + 255) / 256) * 256;
+            }
+            if (s.off != 0 || s.nelem * 4 != end - plan.bufs[size_t(s.buf)].arena_off)
+                return "collective at " + std::to_string(s.pos) + " does not cover its bucket";
         }
         if (s.kind == adb::Step::GEMM && (s.gemm.c == s.gemm.a || s.gemm.c == s.gemm.b || (s.gemm.out >= 0 && (s.gemm.out == s.gemm.a || s.gemm.out == s.gemm.b))))
             return "dot product at " + std::to_string(s.pos) + " writes into one of its operands";
@@ -175,6 +193,7 @@ int main(int argc, char** argv) {
                 opt.exact_div = flags & 4;
                 opt.no_dot_epilogue = flags & 16;
                 opt.no_grouping = flags & 32;
+                opt.bucket_collectives = world > 1 && !(flags & 64);
                 opt.rank = rank;
                 opt.world = world;
                 if (world > 1 && batch) adb::shard_program(prog, rank, world, batch);

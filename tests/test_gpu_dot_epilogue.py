@@ -94,12 +94,10 @@ def test_epilogue_agrees_with_the_unfused_program_and_the_oracle():
 
 
 @pytest.mark.parametrize("kind", ["tc", "simt"])
-@pytest.mark.parametrize("B,K2,N", [(4096, 512, 384), (8192, 256, 256), (3000, 200, 1000), (65536, 128, 256), (512, 640, 520)])
+@pytest.mark.parametrize("B,K2,N", [(512, 640, 520), (1024, 256, 256), (768, 200, 1000), (300, 384, 136)])
 def test_sgd_update_runs_in_the_epilogue(B, K2, N, kind):
-    """`W += -1 * (lr * dot(x^T, g))`: the gradient is never written; long k loops add chunk after chunk (and range
-    after range, when k is split over the SMs) straight into W, which must not be cleared first."""
-    if kind == "simt" and B * K2 * N > 1 << 28:
-        pytest.skip("CUDA-core kernel: small cases only")
+    """`W += -1 * (lr * dot(x^T, g))` with a k axis of one accumulation chunk (<= 1024): the gradient is never written,
+    the product adds its scaled sum straight into W, which must not be cleared first."""
     x = RNG.standard_normal(B * K2).astype(np.float32)
     g = (RNG.standard_normal(B * N) / np.sqrt(B)).astype(np.float32)
     w0 = RNG.standard_normal(K2 * N).astype(np.float32)
@@ -120,6 +118,31 @@ def test_sgd_update_runs_in_the_epilogue(B, K2, N, kind):
     ref = w0.reshape(K2, N).astype(np.float64) - lr * (x.reshape(B, K2).astype(np.float64).T @ g.reshape(B, N).astype(np.float64))
     got = np.asarray(w.val().get().data, np.float64).reshape(K2, N)
     assert np.abs(got - ref).max() / np.abs(ref).max() < 2e-5
+
+
+@pytest.mark.parametrize("lr", [0.25, 1e-5], ids=["large-update", "update-of-a-few-hundred-ulps"])
+@pytest.mark.parametrize("B,K2,N", [(4096, 512, 384), (8192, 256, 256), (3000, 200, 1000), (65536, 128, 256)])
+def test_sgd_update_over_several_k_chunks_is_added_once(B, K2, N, lr):
+    """A k axis of several accumulation chunks (or k ranges split over the SMs): adding every chunk's partial sum to W
+    on its own would round each at the precision of W -- an update of a few hundred ulps of W, spread over 64 chunks,
+    came out percents off.  The gradient is finished first (its scale still rides in the product's epilogue) and
+    added once: the UPDATE W received is within 2e-5 of its largest entry plus half an ulp of W."""
+    x = RNG.standard_normal(B * K2).astype(np.float32)
+    g = (RNG.standard_normal(B * N) / np.sqrt(B)).astype(np.float32)
+    w0 = RNG.standard_normal(K2 * N).astype(np.float32)
+    dev = b200()
+    ad.set_device(dev)
+    ad.eager_dep_opt()
+    w = ad.tensor(w0, [K2, N])
+    w += -1.0 * (lr * ad.dot(ad.tensor(x, [B, K2]).t(), ad.tensor(g, [B, N])))
+    w.forward()
+    w.val().keep()
+    ad.execute()
+    assert "+= product" not in dev.dump_plan(), dev.dump_plan()
+    du_ref = -lr * (x.reshape(B, K2).astype(np.float64).T @ g.reshape(B, N).astype(np.float64))
+    du_got = np.asarray(w.val().get().data, np.float64).reshape(K2, N) - w0.reshape(K2, N).astype(np.float64)
+    half_ulp = np.abs(w0.reshape(K2, N)).astype(np.float64) * 2.0 ** -24 * 1.01
+    assert (np.abs(du_got - du_ref) <= 2e-5 * np.abs(du_ref).max() + half_ulp).all()
 
 
 @pytest.mark.parametrize("B,K2,N", [(4096, 512, 384), (16384, 256, 256)])

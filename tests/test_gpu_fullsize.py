@@ -140,3 +140,49 @@ def test_more_than_2_31_elements_use_64_bit_indices(flags):
     assert np.abs(got_rows - want_rows).max() / np.abs(want_rows).max() < 1e-4
     assert np.abs(got_rows[-8:] - want_rows[-8:]).max() < 1e-2
     assert np.abs(got_tot - want_tot).max() / np.abs(want_tot).max() < 1e-4
+
+
+def test_c4_full_size_step_against_float64_on_the_gpu():
+    """Config 4 at the benchmark's size (batch 65536, 4096-8192-8192-4096-1000; 5e13 flop), one step at lr 10 (at the
+    benchmark's 1e-3 one step moves the first layers by about an ulp): the loss and the update every parameter received
+    match a float64 evaluation of the same step (torch autograd on the same GPU, used as a checker only)."""
+    import torch
+    widths, batch, lr = cfg.C4_WIDTHS, 65536, 10.0
+    small = cfg.c4_inputs(batch=0, widths=widths)
+    g = torch.Generator(device="cuda").manual_seed(11)
+    x = torch.randn(batch * widths[0], device="cuda", generator=g)
+    t = torch.randn(batch * widths[-1], device="cuda", generator=g)
+    w = {k: torch.from_numpy(v).cuda() for k, v in small.items() if k[0] in "wb"}
+    DP = adb.ir.DevicePayload
+    inputs = {k: DP(v.data_ptr(), v.numel(), v) for k, v in w.items()}
+    inputs["x"] = DP(x.data_ptr(), x.numel(), x)
+    inputs["t"] = DP(t.data_ptr(), t.numel(), t)
+    got = cfg.c4_mlp_train(b200(), batch=batch, widths=widths, steps=1, lr=lr, inputs=inputs)
+    st = b200().stats()
+    assert st["tc_gemm_launches"] == st["gemm_launches"] == 11, st
+
+    n_layers = len(widths) - 1
+    params = {}
+    for i in range(n_layers):
+        params[f"w{i}"] = w[f"w{i}"].double().view(widths[i], widths[i + 1]).requires_grad_(True)
+        params[f"b{i}"] = w[f"b{i}"].double().requires_grad_(True)
+    a = x.view(batch, widths[0]).double()
+    for i in range(n_layers):
+        a = a @ params[f"w{i}"] + params[f"b{i}"]
+        if i < n_layers - 1:
+            a = torch.sigmoid(a)
+    loss = ((a - t.view(batch, widths[-1]).double()) ** 2).sum() / (batch * widths[-1])
+    loss.backward()
+    del a
+    ref_loss = float(loss.detach())
+    assert abs(float(got["loss"].data[0]) - ref_loss) / ref_loss < 1e-5
+    for k, p in params.items():
+        du_ref = (-lr * p.grad).reshape(-1)
+        p0 = w[k].double().reshape(-1)
+        du_got = torch.from_numpy(np.asarray(got[k].data, np.float32)).cuda().double() - p0
+        biggest = float(du_ref.abs().max())
+        assert biggest > 100 * 6e-8 * float(p0.abs().max()), k          # the parameter really moved
+        err = float((du_got - du_ref).abs().max()) / biggest
+        # the fp32 parameter rounds its own update: half an ulp of the parameter on top of the arithmetic error
+        floor = 6e-8 * float(p0.abs().max()) / biggest
+        assert err < 2e-3 + floor, (k, err)

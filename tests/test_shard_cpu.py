@@ -46,10 +46,17 @@ def _batch_ids(kw):
 
 def test_rewrite_places_one_allreduce_per_parameter_and_one_for_the_loss():
     cap, handles, _ = _traced_c4()
-    plan = adb.devices.lower_check(adb.autodiff.current_ir(), set(cap.ids), rank=0, world=2, shard_batch=KW["batch"])
+    plan = adb.devices.lower_check(adb.autodiff.current_ir(), set(cap.ids), rank=0, world=2, shard_batch=KW["batch"],
+                                   flags=adb.devices.FLAG_NO_BUCKETS)
     lines = [l for l in plan.splitlines() if " allreduce " in l]
     assert len(lines) == 9, plan   # 4 weights + 4 biases + the kept loss
     assert all("  #" in l for l in lines), "collectives belong inside the training loop"
+    # by default the eight gradients, which nothing reads before the optimiser step, share one collective over buffers
+    # that the arena keeps side by side; the kept loss stays on its own
+    plan = adb.devices.lower_check(adb.autodiff.current_ir(), set(cap.ids), rank=0, world=2, shard_batch=KW["batch"])
+    lines = [l for l in plan.splitlines() if " allreduce " in l]
+    assert len(lines) == 2 and sum(l.count(" + ") for l in lines) == 7, plan
+    assert all("  #" in l for l in lines)
     sharded = adb.devices.shard_ir(cap.blob, 1, 2, KW["batch"])
     assert sharded != cap.blob
 
