@@ -48,6 +48,25 @@ def test_programs_agree_with_sums_fused_at_any_size(seed):
             assert_rel(k, got[k], want[k], 1e-4)
 
 
+@pytest.mark.parametrize("seed", list(range(0, 60, 2)) + list(range(100, 160, 2)))
+def test_replayed_graphs_agree_with_the_first_execute(seed):
+    """The first execute of a program launches its kernels one by one; from the second on the cached plan is captured as
+    a CUDA graph in which kernels that do not depend on one another sit on different streams, and replayed.  Every
+    execute must give the oracle's result."""
+    from helpers import b200
+    exact = seed < 100
+    prog = fuzz_programs.build(seed, exact=exact)
+    with np.errstate(all="ignore"):
+        want = prog(oracle())
+        for rep in range(3):
+            got = prog(b200())
+            for k in want:
+                if exact:
+                    assert_exact(f"{k} (execute {rep})", got[k], want[k])
+                elif np.isfinite(np.asarray(want[k].data, np.float64)).all():
+                    assert_rel(f"{k} (execute {rep})", got[k], want[k], 1e-4)
+
+
 @pytest.mark.parametrize("chunk", range(6))
 def test_raw_ir_programs_agree_bit_for_bit(chunk):
     """Programs written directly as IR commands (ids reused as results, op-assigns on views, views made inside
