@@ -667,15 +667,11 @@ class Executor {
             if (!d_->lane_stream[l - 1]) ck(cudaStreamCreateWithFlags(&d_->lane_stream[l - 1], cudaStreamNonBlocking), "cudaStreamCreate");
             lane[l] = d_->lane_stream[l - 1];
         }
-        // events only carry the dependencies into the captured graph; they can go once the capture of this range is over
-        struct Events {
-            std::vector<cudaEvent_t> all;
-            ~Events() { for (auto e : all) cudaEventDestroy(e); }
-        } events;
+        // events only carry the dependencies into the captured graph; they are destroyed when the capture has ended
         auto record = [&](cudaStream_t st) {
             cudaEvent_t e;
             ck(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "event create");
-            events.all.push_back(e);
+            lane_events_.push_back(e);
             ck(cudaEventRecord(e, st), "event");
             return e;
         };
@@ -780,10 +776,13 @@ class Executor {
                     capturing_ = false;
                     cudaStreamEndCapture(d_->stream, &graph);
                     if (graph) cudaGraphDestroy(graph);
+                    drop_lane_events();
                     throw;
                 }
                 capturing_ = false;
-                ck(cudaStreamEndCapture(d_->stream, &graph), "end capture");
+                cudaError_t end_rc = cudaStreamEndCapture(d_->stream, &graph);
+                drop_lane_events();
+                ck(end_rc, "end capture");
                 g.launches = launches_ - l0;
                 g.gemms = gemms_ - g0;
                 g.tc = tc_ - t0;
@@ -900,6 +899,11 @@ class Executor {
     int gemm_reserve_ = 0;
     uint64_t launches_ = 0, gemms_ = 0, tc_ = 0;
     bool capturing_ = false;
+    std::vector<cudaEvent_t> lane_events_;   // dependency events of the capture in progress
+    void drop_lane_events() {
+        for (auto e : lane_events_) cudaEventDestroy(e);
+        lane_events_.clear();
+    }
     int loop_depth_ = 0;
     uint64_t loop_iter_ = 0;
     cudaStream_t cur_stream_ = nullptr;
