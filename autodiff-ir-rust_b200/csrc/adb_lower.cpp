@@ -2545,7 +2545,7 @@ class Lowerer {
     // kernels only along producer -> consumer edges (src/kernel/fusion/elw.rs, reduce_elw.rs); it has no counterpart.
     static constexpr int64_t TINY_DOT_K = 8, TINY_DOT_WORK = 256;
     static constexpr int64_t GROUP_BIG = int64_t(1) << 22;
-    static constexpr size_t GROUP_MAX = 8, GROUP_LOOKAHEAD = 24;
+    static constexpr size_t GROUP_MAX = 8, GROUP_LOOKAHEAD = 24, GROUP_ARG_WORDS = 384;
     static int64_t kernel_work(const KernelSpec& k) {
         if (k.type == KernelSpec::REDUCE) return k.n * std::max<int64_t>(1, k.r);
         if (k.type == KernelSpec::ROWS) return k.p2 * k.q2;
@@ -2584,11 +2584,22 @@ class Lowerer {
             if (!groupable(steps, i, uses)) continue;
             std::vector<size_t> members = {i};
             step_rw(steps[i], seen_rd, seen_wr);
+            // the members' argument blocks travel in one kernel parameter block: keep it well under 4 KB
+            auto arg_words = [&](const Step& st) {
+                const KernelSpec& k = plan_.kernels[size_t(st.kernel)];
+                return k.ins.size() + k.outs.size() + k.phases.size() + 2;
+            };
+            size_t words = arg_words(steps[i]);
+            if (words > GROUP_ARG_WORDS) continue;
             for (size_t j = i + 1; j < steps.size() && j <= i + GROUP_LOOKAHEAD && members.size() < GROUP_MAX; j++) {
                 if (is_barrier(steps[j])) break;
                 step_rw(steps[j], rd, wr);
                 bool ok = groupable(steps, j, uses) && !hits(seen_wr, rd) && !hits(seen_wr, wr) && !hits(wr, seen_rd);
-                if (ok) members.push_back(j);
+                if (ok && words + arg_words(steps[j]) > GROUP_ARG_WORDS) ok = false;
+                if (ok) {
+                    members.push_back(j);
+                    words += arg_words(steps[j]);
+                }
                 seen_rd.insert(seen_rd.end(), rd.begin(), rd.end());
                 seen_wr.insert(seen_wr.end(), wr.begin(), wr.end());
             }
