@@ -1588,6 +1588,14 @@ class Lowerer {
     // kernel that scales its operand) sits at the end of the step, behind the last dot product.  Each such pair is
     // moved up to right behind the step that produces the gradient: a runtime that issues collectives on their own
     // stream can then overlap them with the remaining dot products.  On a single stream the order is immaterial.
+    static int last_pos(const Step& s) {
+        int p = s.pos;
+        if (s.body && !s.body->steps.empty()) p = std::max(p, last_pos(s.body->steps.back()));
+        for (auto& br : s.branches)
+            if (!br.body->steps.empty()) p = std::max(p, last_pos(br.body->steps.back()));
+        if (s.else_body && !s.else_body->steps.empty()) p = std::max(p, last_pos(s.else_body->steps.back()));
+        return p;
+    }
     void hoist_collectives(StepBlock& blk) {
         for (auto& s : blk.steps) {
             if (s.body) hoist_collectives(*s.body);
@@ -1610,9 +1618,12 @@ class Lowerer {
                 if (hits(wr, prd) || hits(wr, pwr) || hits(rd, pwr)) break;
                 i--;
             }
+            // never to the very head of a block: positions in front of a body's first step belong to the enclosing block
+            // (its While / If step sits right there), and the pair is as early behind the first step
+            if (i == 0) i = 1;
             if (i + 1 >= j) continue;          // nowhere to go (also: i == j - 1 means "stay")
-            // positions right behind steps[i - 1] (or in front of steps[i] at the head of the block)
-            const int base = i > 0 ? steps[i - 1].pos : steps[i].pos - POS_SCALE;
+            // positions right behind steps[i - 1] (behind everything nested in it, when it is a While / If)
+            const int base = last_pos(steps[i - 1]);
             int next_pos = base + 1;
             size_t ins_at = i;
             while (ins_at < steps.size() && steps[ins_at].pos < base + POS_SCALE && ins_at < j - 1) { next_pos = steps[ins_at].pos + 1; ins_at++; }
@@ -2526,11 +2537,11 @@ class Lowerer {
                             needed = needed || std::find(rd.begin(), rd.end(), b) != rd.end() || std::find(wr.begin(), wr.end(), b) != wr.end();
                 }
                 // the merged collective takes the position of the last one held back; it must still lie in front of `s`
-                if (needed) flush(out.empty() ? INT_MIN : out.back().pos + 1);
+                if (needed) flush(out.empty() ? INT_MIN : last_pos(out.back()) + 1);
             }
             out.push_back(std::move(s));
         }
-        flush(out.empty() ? INT_MIN : out.back().pos + 1);
+        flush(out.empty() ? INT_MIN : last_pos(out.back()) + 1);
         blk.steps = std::move(out);
     }
 

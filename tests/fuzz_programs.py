@@ -177,11 +177,14 @@ def build_loop(seed: int):
     return prog
 
 
-def build_raw(seed: int):
+def build_raw(seed: int, allreduce: bool = False):
     """A random program written directly as IR commands (no frontend in between): ids are reused as results, op-assigns
     hit ids that are views / permutes of other tensors, views are created inside branches, branches are not taken and
     loops run zero times.  Square [n, n] tensors of small integers and a few additions / multiplications per path, so
     every value is exact in fp32 and device and oracle must agree bit for bit.
+
+    With `allreduce`, about a third of the values are all-reduced right after they are assigned (the caller runs the
+    program on ranks that hold identical data, so the sum over ranks is a multiplication by their number).
 
     Returns `prog(dev) -> {id: ValueData}`.  Only ids that are certainly defined are read: an id first assigned inside
     a block is local to that block."""
@@ -287,6 +290,8 @@ def build_raw(seed: int):
                     continue
                 else:
                     continue
+                if allreduce and kind in (0, 1, 2, 3, 6, 7) and rng.random() < 0.35:
+                    block.push(("AllReduce", res))
                 if res not in pool:
                     pool.append(res)
             return pool

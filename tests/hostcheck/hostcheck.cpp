@@ -206,8 +206,11 @@ int main(int argc, char** argv) {
                 }
                 std::string listing = adb::dump_plan(plan, true);
                 if (listing.empty()) return 3;
-                if ((flags & 8) && world == 1) {
+                // several ranks are only interpreted when nothing is sharded (batch 0): every rank then holds the same
+                // data and an all-reduce is a multiplication by the number of ranks
+                if ((flags & 8) && (world == 1 || (batch == 0 && rank == 0))) {
                     adbtest::PlanInterp run(plan);
+                    run.world = world;
                     run.run();
                     std::ofstream res(std::string(argv[f]) + ".out", std::ios::binary);
                     for (auto& r : plan.results) {

@@ -19,6 +19,7 @@ namespace adbtest {
 using namespace adb;
 
 struct PlanInterp {
+    int world = 1;   // ranks simulated as identical copies (ALLREDUCE multiplies by it)
     const Plan& plan;
     std::vector<float> arena;
     bool exited = false;
@@ -212,7 +213,16 @@ struct PlanInterp {
             std::memcpy(ptr(s.buf), reinterpret_cast<const void*>(uintptr_t(p.addr)), size_t(s.nelem) * 4);
             break;
         }
-        case Step::ALLREDUCE: break;   // one rank: the sum over ranks is the value itself
+        case Step::ALLREDUCE: {
+            // one rank: the sum over ranks is the value itself; several ranks that all hold the same data (the only
+            // multi-rank case this interpreter runs): the sum is `world` times the value, over the whole range the
+            // step covers (a bucket's alignment padding included, as on the device)
+            if (world > 1) {
+                float* p = ptr(s.buf, s.off);
+                for (int64_t i = 0; i < s.nelem; i++) p[i] *= float(world);
+            }
+            break;
+        }
         case Step::WHILE:
             while (!exited && *ptr(s.cond_buf, s.cond_off) != 0.0f) {
                 run_block(*s.body);

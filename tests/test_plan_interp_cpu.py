@@ -303,3 +303,75 @@ def test_independent_kernels_share_one_launch(hostcheck, tmp_path):
     assert "group of" not in adb.devices.lower_check(proc, dep, flags=adb.devices.FLAG_NO_GROUPING)
     for flags in (0, 32):
         _compare(_interpret(hostcheck, tmp_path, dev.blobs[-1], flags, f"group{flags}"), kept, 1e-6)
+
+
+class _BothRanks(_Both):
+    """Oracle whose all-reduce multiplies by the number of ranks: every rank holds the same data."""
+
+    def __init__(self, world):
+        OracleDevice.__init__(self, allreduce=lambda arr: np.multiply(arr, np.float32(world), out=arr))
+        self.blobs = []
+
+
+def _interpret_ranks(binary, tmp_path, blob, flags, tag, world):
+    f = tmp_path / f"{tag}.adir"
+    f.write_bytes(blob)
+    r = subprocess.run([binary, str(flags | 8), str(world), "0", str(f)], capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-3000:] + r.stdout[-2000:]
+    assert "executed=1" in r.stdout, r.stdout
+    return _read_results(str(f) + ".out")
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_bucketed_all_reduces_on_identical_ranks(hostcheck, tmp_path, world):
+    """All-reduces written into the IR by hand, on ranks that all hold the same data (the sum over ranks is then
+    `world` times the value): three gradients that nothing reads before the update share one collective over adjacent
+    buffers (sizes that are not multiples of the arena's alignment: the padding in between is reduced along with them
+    and must not leak); a value that is read right after its all-reduce, a kept value and all-reduces inside a loop
+    keep their order.  With and without buckets, against the oracle."""
+    rng = np.random.default_rng(7)
+    A = rng.integers(-3, 4, 70).astype(np.float32)
+    B = rng.integers(-3, 4, 3).astype(np.float32)
+    C = rng.integers(-3, 4, 130).astype(np.float32)
+    loop = _block(("ElwMultiply", "a", "a", "g1"), ("AllReduce", "g1"), ("ElwAdd", "b", "b", "g2"), ("AllReduce", "g2"),
+                  ("ElwMultiply", "c", "h", "g3"), ("AllReduce", "g3"),
+                  ("ElwAddEq", "a", "g1"), ("ElwAddEq", "b", "g2"), ("ElwAddEq", "c", "g3"), ("ElwAddEq", "n", "k"))
+    proc, dep = _raw([("CreateMat", A, [7, 10], "a"), ("CreateMat", B, [3], "b"), ("CreateMat", C, [2, 65], "c"),
+                      ("CreateMat", np.array([2.0], np.float32), [1], "n"), ("CreateConstant", -1.0, "k", [1]),
+                      ("CreateConstant", 0.5, "h", [2, 65]),
+                      ("ElwMultiply", "a", "a", "t1"), ("AllReduce", "t1"),
+                      ("ElwAdd", "b", "b", "t2"), ("AllReduce", "t2"),
+                      ("ElwMultiply", "c", "c", "t3"), ("AllReduce", "t3"),
+                      ("ElwAdd", "t1", "a", "u"), ("ElwMultiply", "t2", "b", "v"), ("ElwAdd", "t3", "c", "w"),
+                      ("ElwAdd", "b", "b", "s1"), ("AllReduce", "s1"), ("ElwMultiply", "s1", "s1", "s2"), ("AllReduce", "s2"),
+                      ("While", "n", loop)], ["u", "v", "w", "t2", "s2", "a", "b", "c"])
+    dev = _BothRanks(world)
+    dev.execute(proc, dep)
+    kept = {d: dev.get_tensor(d) for d in dep}
+    assert np.array_equal(kept["s2"].numpy(), (2 * B * world) ** 2 * world)
+    listing = adb.devices.lower_check(proc, dep, world=world)
+    assert " + " in "".join(l for l in listing.splitlines() if " allreduce " in l), listing
+    for flags in (0, 64, 1):            # buckets, one collective per command, one kernel per command
+        _compare(_interpret_ranks(hostcheck, tmp_path, dev.blobs[-1], flags, f"ar{world}_{flags}", world), kept, 0.0)
+
+
+def test_raw_ir_programs_with_all_reduces_on_identical_ranks(hostcheck, tmp_path):
+    """The raw-IR programs with all-reduces sprinkled over their values (top level, branches, loops), on two ranks that
+    hold the same data: bucketed and one collective per command, bit for bit against the oracle."""
+    refused = 0
+    seeds = range(120)
+    for seed in seeds:
+        dev = _BothRanks(2)
+        kept = fuzz_programs.build_raw(seed, allreduce=True)(dev)
+        for flags in (0, 64):
+            f = tmp_path / f"rawar{seed}_{flags}.adir"
+            f.write_bytes(dev.blobs[-1])
+            r = subprocess.run([hostcheck, str(flags | 8), "2", "0", str(f)], capture_output=True, text=True, timeout=900)
+            assert r.returncode == 0, (seed, r.stderr[-3000:] + r.stdout[-1500:])
+            if "rejected:" in r.stdout:
+                assert REFUSAL in r.stdout, r.stdout
+                refused += 1
+                break
+            assert "executed=1" in r.stdout, r.stdout
+            _compare(_read_results(str(f) + ".out"), kept, 0.0)
+    assert refused <= len(seeds) // 4, refused
