@@ -123,6 +123,7 @@ class Lowerer {
     std::vector<Binding> bind_;
     std::vector<char> is_dep_;
     std::vector<uint32_t> lazy_ids_;   // ids bound to values that do not live in their own buffer yet
+    std::vector<uint32_t> materializing_;  // ids whose values are being written out (materialize_ids calls in progress)
     StepBlock* cur_ = nullptr;
     int pos_ = 0;
     int tmp_counter_ = 0;
@@ -244,6 +245,20 @@ class Lowerer {
             const Cmd& c = *bind_[x].cmd;
             if (f.sources.insert(c.a).second) st.push_back(c.a);
             if (c.op == OP_CONCAT && f.sources.insert(c.b).second) st.push_back(c.b);
+        }
+        // ids that already look through `id` (views of the view made earlier) read the copy from now on as well
+        {
+            std::vector<uint32_t> up{id};
+            while (!up.empty()) {
+                uint32_t x = up.back();
+                up.pop_back();
+                for (uint32_t k : info_[x].alias_kids) {
+                    if (bind_[k].kind != Binding::ALIAS || !bind_[k].cmd) continue;
+                    const Cmd& kc = *bind_[k].cmd;
+                    if (kc.a != x && !(kc.op == OP_CONCAT && kc.b == x)) continue;
+                    if (f.readers.insert(k).second) up.push_back(k);
+                }
+            }
         }
         uint8_t state = scan_cmds(blk, from, S_WINDOW, f);
         for (size_t d = frames_.size(); d-- > 0 && !f.conflict;) {
@@ -610,13 +625,28 @@ class Lowerer {
         }
         if (work.empty()) return;
         std::vector<int> dst(work.size());
+        std::vector<char> parked(work.size(), 0);
         for (size_t k = 0; k < work.size(); k++) {
             uint32_t id = work[k];
             Node* n = g_.canon(bind_[id].node);
-            dst[k] = info_[id].needs_buffer() ? id_buffer(id, n->shape) : temp_buffer(numel(n->shape));
+            bool own = info_[id].needs_buffer();
+            int target = own ? id_buffer(id, n->shape) : -1;
+            // x' = f(y), y' = g(x), each written out on its own (an all-reduce of x): writing x needs y' out of the way
+            // first (it reads the old x), and y' cannot go to y's buffer because x' still reads the old y.  A value
+            // that something further up this call chain still reads the target of goes to a temporary for now and
+            // reaches its own buffer at the next flush.
+            for (size_t q = 0; own && q < materializing_.size(); q++) {
+                const uint32_t other = materializing_[q];
+                if (other != id && bind_[other].kind == Binding::VALUE && depends_on(bind_[other].node, target)) own = false;
+            }
+            parked[k] = info_[id].needs_buffer() && !own;
+            dst[k] = own ? target : temp_buffer(numel(n->shape));
         }
         // old contents of the targets may still be needed by other lazy values
+        const size_t depth = materializing_.size();
+        materializing_.insert(materializing_.end(), work.begin(), work.end());
         for (size_t k = 0; k < work.size(); k++) before_write(dst[k], work);
+        materializing_.resize(depth);
         std::vector<StoreTask> tasks;
         std::vector<std::pair<size_t, size_t>> span(work.size());
         for (size_t k = 0; k < work.size(); k++) {
@@ -633,6 +663,10 @@ class Lowerer {
             g_.buf_version[dst[k]]++;
             Node* ld = g_.load(dst[k], oldc->shape, contiguous_view(oldc->shape));
             if (oldc->kind == N_OP || oldc->kind == N_PIECE) oldc->fwd = ld;
+            if (parked[k]) {
+                bind_value(id, ld);      // still owes its own buffer a copy
+                continue;
+            }
             bind_[id].node = ld;
             bind_[id].pending = false;
         }

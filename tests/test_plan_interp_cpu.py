@@ -272,6 +272,20 @@ def test_path_dependent_view_is_refused(hostcheck, tmp_path):
     assert _interpret_or_refused(hostcheck, tmp_path, blob, 0, "pathdep") is None
 
 
+def test_view_of_a_view_that_a_loop_rebinds_is_refused(hostcheck, tmp_path):
+    """v2 = Permute(v3); v5 = Permute(v2); While c {v3 = v3 . v3; v2 = v5 + v1; ...}: on the first pass v5 looks through
+    v2 at the v3 the loop has just changed, from the second pass on at the tensor v2 has become.  The copy of v2 taken in
+    front of the loop cannot follow v3, and v5 -- a view made BEFORE the loop -- reads it: refused (this used to lower,
+    with the stale v3 in the first pass)."""
+    proc, dep = _raw([("CreateMat", M4, [4, 4], "v1"), ("CreateMat", M4 * 0, [4, 4], "v2"), ("CreateMat", M4 + 1, [4, 4], "v3"),
+                      ("CreateConstant", -1.0, "k", [1]), ("Permute", "v3", [1, 0], "v2"), ("Permute", "v2", [1, 0], "v5"),
+                      ("CreateMat", np.array([2.0], np.float32), [1], "c"),
+                      ("While", "c", _block(("DotProduct", "v3", "v3", "v3"), ("ElwAdd", "v5", "v1", "v2"), ("ElwAddEq", "c", "k")))],
+                     ["v1", "v2", "v3", "v5"])
+    blob = adb.ir.serialize(proc, dep, inline_limit=1 << 40)[0]
+    assert _interpret_or_refused(hostcheck, tmp_path, blob, 0, "viewofview") is None
+
+
 @pytest.mark.parametrize("M,K,N", [(300, 256, 1), (1, 300, 260)])
 def test_matrix_vector_products_through_the_reduce_kernels(hostcheck, tmp_path, M, K, N):
     rng = np.random.default_rng(M + N)
@@ -375,3 +389,20 @@ def test_raw_ir_programs_with_all_reduces_on_identical_ranks(hostcheck, tmp_path
             assert "executed=1" in r.stdout, r.stdout
             _compare(_read_results(str(f) + ".out"), kept, 0.0)
     assert refused <= len(seeds) // 4, refused
+
+
+def test_values_that_read_each_others_buffers_are_written_out_through_a_temporary(hostcheck, tmp_path):
+    """a' = b + 1 and b' = (old a) + 1, both still expressions when an all-reduce forces a' into a's buffer: b' must be
+    out of the way first (it reads the old a) and cannot go to b's buffer (a' still reads the old b).  The lowering used to
+    recurse without end here; one of the two now waits in a temporary."""
+    A = np.arange(4, dtype=np.float32)
+    B = np.arange(4, dtype=np.float32) * 10
+    proc, dep = _raw([("CreateMat", A, [2, 2], "a"), ("CreateMat", B, [2, 2], "b"), ("CreateConstant", 1.0, "c", [2, 2]),
+                      ("Contigious", "a", "s"), ("ElwAdd", "b", "c", "a"), ("ElwAdd", "s", "c", "b"), ("AllReduce", "a")],
+                     ["a", "b"])
+    dev = _BothRanks(2)
+    dev.execute(proc, dep)
+    kept = {d: dev.get_tensor(d) for d in dep}
+    assert np.array_equal(kept["a"].numpy().reshape(-1), 2 * (B + 1)) and np.array_equal(kept["b"].numpy().reshape(-1), A + 1)
+    for flags in (0, 1, 64):
+        _compare(_interpret_ranks(hostcheck, tmp_path, dev.blobs[-1], flags, f"swap{flags}", 2), kept, 0.0)
