@@ -1247,7 +1247,7 @@ class Lowerer {
         // along the columns) * (row k of B, repeated along the rows), k ascending like the dot kernels.  It then fuses with
         // whatever surrounds it (the whole training step of a 2 x 5 network becomes a handful of kernels instead of one
         // launch per product), and the expression limit of after_op keeps chains of such products from growing.
-        if (!opt_.no_fusion && K <= TINY_DOT_K && M * N * K <= TINY_DOT_WORK) {
+        if (!opt_.no_fusion && !opt_.no_tiny_dot && K <= TINY_DOT_K && M * N * K <= TINY_DOT_WORK) {
             Node* acc = nullptr;
             bool ok = true;
             for (int64_t k = 0; k < K && ok; k++) {

@@ -211,6 +211,7 @@ inline void kernel_rw(const Plan& p, int kernel, std::vector<int>& rd, std::vect
 
 struct LowerOptions {
     bool no_grouping = false;       // every kernel in a launch of its own
+    bool no_tiny_dot = false;       // dot products of a few multiply-adds stay dot-product steps
     bool bucket_collectives = false;  // all-reduces of neighbouring gradients become one collective over adjacent buffers
     bool no_fusion = false;
     bool no_reduce_fusion = false;  // keep every Sum in a kernel of its own

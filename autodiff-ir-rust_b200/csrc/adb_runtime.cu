@@ -1023,6 +1023,7 @@ adb_status do_execute(adb_device* d, const uint8_t* blob, size_t nbytes) {
         opt.exact_div = (d->flags & ADB_FLAG_EXACT_DIV) != 0;
         opt.fuse_small_sums = (d->flags & ADB_FLAG_FUSE_SMALL_SUMS) != 0;
         opt.no_grouping = (d->flags & ADB_FLAG_NO_GROUPING) != 0;
+        opt.no_tiny_dot = (d->flags & ADB_FLAG_NO_TINY_DOT) != 0;
         opt.bucket_collectives = d->world > 1 && !(d->flags & (ADB_FLAG_COMM_STREAM | ADB_FLAG_NO_BUCKETS));
         opt.rank = d->rank;
         opt.world = d->world;
@@ -1394,6 +1395,7 @@ adb_status adb_lower_check(const uint8_t* blob, size_t nbytes, const adb_config*
             opt.exact_div = (cfg->flags & ADB_FLAG_EXACT_DIV) != 0;
             opt.fuse_small_sums = (cfg->flags & ADB_FLAG_FUSE_SMALL_SUMS) != 0;
             opt.no_grouping = (cfg->flags & ADB_FLAG_NO_GROUPING) != 0;
+            opt.no_tiny_dot = (cfg->flags & ADB_FLAG_NO_TINY_DOT) != 0;
             opt.bucket_collectives = cfg->world_size > 1 && !(cfg->flags & (ADB_FLAG_COMM_STREAM | ADB_FLAG_NO_BUCKETS));
             opt.rank = cfg->rank;
             opt.world = cfg->world_size > 0 ? cfg->world_size : 1;

@@ -103,6 +103,9 @@ typedef struct adb_config {
                                          depend on one another are captured on different streams and may run side by side) */
 #define ADB_FLAG_NO_BUCKETS 2048u      /* every all-reduce of the data-parallel rewrite as a collective of its own (by default
                                          the gradients that are reduced next to one another share one collective) */
+#define ADB_FLAG_NO_TINY_DOT 4096u     /* dot products of a few multiply-adds (K <= 8, M*N*K <= 256) stay dot-product steps
+                                         instead of becoming element-wise sums of products (lets small tests reach the dot
+                                         kernels) */
 #define ADB_FLAG_NO_GROUPING 256u     /* every generated kernel in a launch of its own (by default independent kernels
                                          that follow one another share one grid) */
 

@@ -193,6 +193,7 @@ int main(int argc, char** argv) {
                 opt.exact_div = flags & 4;
                 opt.no_dot_epilogue = flags & 16;
                 opt.no_grouping = flags & 32;
+                opt.no_tiny_dot = flags & 128;
                 opt.bucket_collectives = world > 1 && !(flags & 64);
                 opt.rank = rank;
                 opt.world = world;

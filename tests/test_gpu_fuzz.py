@@ -17,11 +17,36 @@ def _fuse_small():
     return _small
 
 
+_steps = None
+
+
+def _dot_steps():
+    """A handle on which the tiny dot products of these programs stay dot-product steps (by default a product of a few
+    multiply-adds is lowered as an element-wise expression and never reaches the dot kernels)."""
+    global _steps
+    if _steps is None:
+        _steps = adb.devices.B200(0, flags=adb.devices.FLAG_NO_TINY_DOT)
+    return _steps
+
+
 @pytest.mark.parametrize("seed", range(60))
 def test_exact_programs_agree_bit_for_bit(seed):
     want, got = run_both(fuzz_programs.build(seed, exact=True))
     for k in want:
         assert_exact(k, got[k], want[k])
+
+
+@pytest.mark.parametrize("seed", list(range(0, 60, 3)) + list(range(100, 160, 3)))
+def test_programs_agree_with_tiny_products_as_dot_product_steps(seed):
+    exact = seed < 100
+    prog = fuzz_programs.build(seed, exact=exact)
+    with np.errstate(all="ignore"):
+        want, got = prog(oracle()), prog(_dot_steps())
+    for k in want:
+        if exact:
+            assert_exact(k, got[k], want[k])
+        elif np.isfinite(np.asarray(want[k].data, np.float64)).all():
+            assert_rel(k, got[k], want[k], 1e-4)
 
 
 @pytest.mark.parametrize("seed", range(100, 160))
@@ -79,12 +104,14 @@ def test_raw_ir_programs_agree_bit_for_bit(chunk):
         want = prog(oracle())
         try:
             got = prog(b200())
+            got_steps = prog(_dot_steps())
         except adb.devices.AdbError as e:
             assert "is a view when control flow joins" in str(e), str(e)
             refused += 1
             continue
         for k in want:
             assert_exact(k, got[k], want[k])
+            assert_exact(k + " (dot-product steps)", got_steps[k], want[k])
     assert refused <= 10
 
 

@@ -114,7 +114,7 @@ def test_random_programs(hostcheck, tmp_path, chunk):
         with np.errstate(all="ignore"):
             kept = fuzz_programs.build(seed if exact else 1000 + seed, exact=exact)(dev)
         by_id = {v.id: v for v in kept.values()}
-        for flags in (0, 2):
+        for flags in (0, 2, 128):          # default, every fusion at any size, tiny dot products as dot-product steps
             got = _interpret(hostcheck, tmp_path, dev.blobs[-1], flags, f"fz{seed}_{flags}")
             _compare(got, by_id, 0.0 if exact else 1e-4)
 
@@ -190,7 +190,7 @@ def test_raw_ir_programs_with_reused_ids_and_views_across_blocks(hostcheck, tmp_
     for seed in seeds:
         dev = _Both()
         kept = fuzz_programs.build_raw(seed)(dev)
-        for flags in (0, 2):
+        for flags in (0, 2, 128):
             got = _interpret_or_refused(hostcheck, tmp_path, dev.blobs[-1], flags, f"raw{seed}_{flags}")
             if got is None:
                 refused += 1
