@@ -11,7 +11,7 @@ namespace adb {
 // Element-wise work on the product while it is still in registers (see Step::Gemm in adb_plan.hpp): a chain
 // v = acc; v = op_i(v, operand_i).  Passed to the kernels by value.
 constexpr int GEMM_EPI_MAX_OPS = 12;
-constexpr int GEMM_CHUNK_K = 1024;   // k elements per accumulation chunk of the tensor-core kernels
+constexpr int GEMM_CHUNK_K = 1024;   // k elements of the shortest accumulation chunk of the tensor-core kernels (and the unit of k splits)
 struct GemmEpilogue {
     int mode = 0;                 // 0 none, 1 scale (every partial product; optionally added to C), 2 chain on the finished sum
     int accumulate = 0;           // mode 1: C += scaled product instead of C = scaled product
@@ -34,6 +34,7 @@ struct GemmArgs {
     int64_t batch = 1, a_bs = 0, b_bs = 0, c_bs = 0; // batched product: slices this many elements apart
     bool force_simt = false;
     bool no_pair = false;  // keep the tensor-core kernel on one SM per tile
+    bool short_chunks = false;  // accumulate 1024 k elements per chunk instead of 4096 (4x smaller truncation error, ~9 % slower)
     bool no_k_split = false;  // one owner per output tile: the order of the additions into C never depends on timing
     int reserve_sms = 0;   // leave this many SMs to a kernel running beside the product (a collective on another stream)
     GemmEpilogue epi;

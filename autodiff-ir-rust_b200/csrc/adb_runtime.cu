@@ -391,6 +391,7 @@ class Executor {
             a.force_simt = (d_->flags & ADB_FLAG_SIMT_DOT) != 0;
             a.no_pair = (d_->flags & ADB_FLAG_SINGLE_SM_DOT) != 0;
             a.no_k_split = (d_->flags & ADB_FLAG_DETERMINISTIC) != 0;
+            a.short_chunks = (d_->flags & ADB_FLAG_SHORT_DOT_CHUNKS) != 0;
             a.reserve_sms = gemm_reserve_;
             if (g.epi != Step::Gemm::EPI_NONE) {
                 a.epi.mode = int(g.epi);

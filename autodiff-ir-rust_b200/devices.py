@@ -31,6 +31,7 @@ FLAG_DETERMINISTIC = 512
 FLAG_SERIAL_GRAPHS = 1024
 FLAG_NO_BUCKETS = 2048
 FLAG_NO_TINY_DOT = 4096
+FLAG_SHORT_DOT_CHUNKS = 8192
 
 EXPORTS = ["adb_create", "adb_destroy", "adb_execute", "adb_get_tensor", "adb_get_tensor_device",
            "adb_dot_prod_shape", "adb_last_error", "adb_get_stats", "adb_dump_plan", "adb_lower_check",
