@@ -111,3 +111,62 @@ def test_batch_equal_to_a_layer_width_with_named_batch_tensors(tmp_path):
             ref = v.numpy()
             err = np.abs(got[k] - ref).max() / max(np.abs(ref).max(), 1e-30)
             assert err < 1e-4, (r, k, err)
+
+
+def _raw_worker(rank, world, port, out_dir, seeds):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    adb = importlib.import_module("autodiff-ir-rust_b200")
+    import fuzz_programs
+    box = [adb.devices.nccl_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    dev = adb.devices.B200(rank, rank=rank, world_size=world, nccl_unique_id=box[0], shard_batch=0)
+    out = {}
+    for seed in seeds:
+        # every rank must issue the same collectives: a program this rank would refuse is refused on all of them
+        try:
+            got = fuzz_programs.build_raw(seed, allreduce=True)(dev)
+        except adb.devices.AdbError as e:
+            assert "is a view when control flow joins" in str(e), str(e)
+            continue
+        for k, v in got.items():
+            out[f"{seed}:{k}"] = v.numpy()
+    np.savez(os.path.join(out_dir, f"raw{rank}.npz"), **out)
+    dev.close()
+    dist.destroy_process_group()
+
+
+def test_hand_written_all_reduces_on_two_identical_ranks(tmp_path):
+    """Raw-IR programs with all-reduces sprinkled over their values, run on two GPUs that hold the same data (nothing
+    is sharded): the sum over ranks is twice the value, which the oracle reproduces with an all-reduce hook.  Exact
+    integer arithmetic: bit for bit, with the collectives bucketed as the default lowering does."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import fuzz_programs
+    from oracle.oracle import OracleDevice
+    seeds = list(range(40))
+    port = 29900 + (os.getpid() % 2000)
+    mp.spawn(_raw_worker, args=(2, port, str(tmp_path), seeds), nprocs=2, join=True)
+    got = [np.load(tmp_path / f"raw{r}.npz") for r in range(2)]
+    checked = 0
+    for seed in seeds:
+        ora = OracleDevice(allreduce=lambda arr: np.multiply(arr, np.float32(2), out=arr))
+        want = fuzz_programs.build_raw(seed, allreduce=True)(ora)
+        for k, v in want.items():
+            key = f"{seed}:{k}"
+            if key not in got[0].files:
+                continue            # refused on the device
+            for r in range(2):
+                np.testing.assert_array_equal(got[r][key].reshape(-1), v.numpy().reshape(-1), err_msg=f"{key} rank {r}")
+            checked += 1
+    assert checked >= 60, checked
