@@ -1398,6 +1398,14 @@ class Lowerer {
     // sums / products are only followed while the buffer they were written to keeps its version, so advancing every
     // version cuts all of those links; ids keep their buffers (refresh_bindings rebinds them at the new version).
     void forget_computed_values() {
+        // an id bound to an expression that has been written out (the expression forwards to a load of the buffer) is
+        // bound to that load first: once the versions move, the forward is no longer followed and the expression's own
+        // operands are out of date as well
+        for (auto& b : bind_)
+            if (b.kind == Binding::VALUE && b.node) {
+                Node* n = g_.canon(b.node);
+                if (n->kind == N_LOAD) b.node = n;
+            }
         for (auto& v : g_.buf_version) v++;
         refresh_bindings();
     }

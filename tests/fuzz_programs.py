@@ -177,11 +177,14 @@ def build_loop(seed: int):
     return prog
 
 
-def build_raw(seed: int, allreduce: bool = False):
+def build_raw(seed: int, allreduce: bool = False, rich: bool = False):
     """A random program written directly as IR commands (no frontend in between): ids are reused as results, op-assigns
     hit ids that are views / permutes of other tensors, views are created inside branches, branches are not taken and
     loops run zero times.  Square [n, n] tensors of small integers and a few additions / multiplications per path, so
     every value is exact in fp32 and device and oracle must agree bit for bit.
+
+    With `rich`, row sums broadcast back to [n, n], single rows repeated over the tensor and halves cut out of a concat
+    join the mix (reductions, Index / Broadcast / Concat / View chains as alias ids).
 
     With `allreduce`, about a third of the values are all-reduced right after they are assigned (the caller runs the
     program on ranks that hold identical data, so the sum over ranks is a multiplication by their number).
@@ -226,7 +229,7 @@ def build_raw(seed: int, allreduce: bool = False):
             """Appends random commands to `block`; `pool` = ids (shape [n, n]) that are defined at this point."""
             pool = list(pool)
             for _ in range(int(rng.integers(2, 7))):
-                kind = int(rng.integers(0, 10))
+                kind = int(rng.integers(0, 13 if rich else 10))
                 a = pool[int(rng.integers(0, len(pool)))]
                 b = pool[int(rng.integers(0, len(pool)))]
                 # results go to a fresh id or overwrite an existing one
@@ -264,6 +267,42 @@ def build_raw(seed: int, allreduce: bool = False):
                         continue
                     budget["mul"] -= 1
                     block.push(("DotProduct", a, b, res))
+                elif kind == 10:
+                    # row sums, repeated along the rows again: [n, n] -> [n] -> [n, 1] -> [n, n]
+                    if budget["mul"] <= 0 or may_alias(res, a):
+                        continue
+                    budget["mul"] -= 1
+                    s_, v_ = fresh("s"), fresh("w")
+                    block.push(("Sum", a, s_))
+                    block.push(("View", s_, [n, 1], v_))
+                    block.push(("Broadcast", v_, 1, n, res))
+                    note_alias(v_, s_)
+                    note_alias(res, v_)
+                elif kind == 11:
+                    # one row of a, repeated over all rows
+                    if may_alias(res, a):
+                        continue
+                    i_, v_ = fresh("i"), fresh("w")
+                    block.push(("Index", a, int(rng.integers(0, n)), 0, i_))
+                    block.push(("View", i_, [1, n], v_))
+                    block.push(("Broadcast", v_, 0, n, res))
+                    note_alias(i_, a)
+                    note_alias(v_, i_)
+                    note_alias(res, v_)
+                elif kind == 12:
+                    # a on top of b, then one of the two halves again
+                    if may_alias(res, a) or may_alias(res, b):
+                        continue
+                    c_, v_, i_ = fresh("c"), fresh("w"), fresh("i")
+                    block.push(("Concat", a, b, 0, c_))
+                    block.push(("View", c_, [2, n * n], v_))
+                    block.push(("Index", v_, int(rng.integers(0, 2)), 0, i_))
+                    block.push(("View", i_, [n, n], res))
+                    note_alias(c_, a)
+                    note_alias(c_, b)
+                    note_alias(v_, c_)
+                    note_alias(i_, v_)
+                    note_alias(res, i_)
                 elif kind == 8 and depth < 2:
                     # If on a flag that is 0 or 1 (optionally with an else block)
                     flag = fresh("f")

@@ -406,3 +406,35 @@ def test_values_that_read_each_others_buffers_are_written_out_through_a_temporar
     assert np.array_equal(kept["a"].numpy().reshape(-1), 2 * (B + 1)) and np.array_equal(kept["b"].numpy().reshape(-1), A + 1)
     for flags in (0, 1, 64):
         _compare(_interpret_ranks(hostcheck, tmp_path, dev.blobs[-1], flags, f"swap{flags}", 2), kept, 0.0)
+
+
+def test_raw_ir_programs_with_sums_rows_and_concats(hostcheck, tmp_path):
+    """The raw-IR generator with its richer command mix (row sums broadcast back, single rows repeated, halves cut out
+    of a concat -- all as alias chains, inside and outside of branches and loops): default lowering and one kernel per
+    command with tiny dot products as dot-product steps, bit for bit or refused for the one documented reason."""
+    refused = 0
+    seeds = range(100)
+    for seed in seeds:
+        dev = _Both()
+        kept = fuzz_programs.build_raw(seed, rich=True)(dev)
+        for flags in (0, 129):
+            got = _interpret_or_refused(hostcheck, tmp_path, dev.blobs[-1], flags, f"rich{seed}_{flags}")
+            if got is None:
+                refused += 1
+                break
+            _compare(got, kept, 0.0)
+    assert refused <= len(seeds) // 3, refused
+
+
+def test_a_value_computed_twice_survives_a_loop_with_one_kernel_per_command(hostcheck, tmp_path):
+    """`v3 = v2 + v2` twice, then a loop: with one kernel per command the second command finds the first one's result
+    in memory and v3 stays bound to the expression that forwards to it; the loop moves every buffer version on, and the
+    id must follow to the buffer, not fall back to the expression with its outdated operands."""
+    proc, dep = _raw([("CreateMat", M4, [4, 4], "v2"), ("ElwAdd", "v2", "v2", "v3"), ("ElwAdd", "v2", "v2", "v3"),
+                      ("CreateMat", np.array([1.0], np.float32), [1], "c"), ("CreateConstant", -1.0, "k", [1]),
+                      ("While", "c", _block(("ElwAddEq", "c", "k")))], ["v2", "v3"])
+    dev = _Both()
+    dev.execute(proc, dep)
+    kept = {d: dev.get_tensor(d) for d in dep}
+    for flags in (0, 1):
+        _compare(_interpret(hostcheck, tmp_path, dev.blobs[-1], flags, f"twice{flags}"), kept, 0.0)
