@@ -115,6 +115,27 @@ def test_raw_ir_programs_agree_bit_for_bit(chunk):
     assert refused <= 10
 
 
+@pytest.mark.parametrize("chunk", range(3))
+def test_raw_ir_programs_with_sums_rows_and_concats(chunk):
+    """The richer raw-IR mix (row sums broadcast back, repeated rows, halves of a concat as alias chains), two executes
+    each (the second one replays the captured graph)."""
+    from helpers import b200
+    refused = 0
+    for seed in range(chunk * 25, chunk * 25 + 25):
+        prog = fuzz_programs.build_raw(seed, rich=True)
+        want = prog(oracle())
+        try:
+            runs = [prog(b200()), prog(b200())]
+        except adb.devices.AdbError as e:
+            assert "is a view when control flow joins" in str(e), str(e)
+            refused += 1
+            continue
+        for got in runs:
+            for k in want:
+                assert_exact(k, got[k], want[k])
+    assert refused <= 12
+
+
 @pytest.mark.parametrize("n", [96, 512])
 def test_dot_product_written_onto_its_own_operand(n):
     """`DotProduct v w -> v` with more than one tile per operand (512: tensor-core kernel, 96: CUDA-core kernel), at top
