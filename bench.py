@@ -278,7 +278,10 @@ def run_ours(args):
     e2e = {"value": K / e2e_s, "unit": UNIT, "h2d_bytes_per_step": int((x_host.numel() + t_host.numel()) * 4),
            "d2h_bytes_per_step": int(st_e["d2h_bytes"] // K), "ms_per_step": e2e_s * 1e3 / K,
            "upload_ms_per_step": st_e["upload_ms"] / K,
-           "read_back": "loop condition (4 B per step) and the loss (4 B per execute); weights stay resident"}
+           "read_back": "loop condition (4 B per step) and the loss (4 B per execute); weights stay resident",
+           "per_execute_upload": "every execute also uploads the initial weights (%d MB, pinned host memory, every rank); "
+                                 "upload_ms_per_step is that copy divided by the %d steps of one execute"
+                                 % (sum(v.numel() for v in pinned.values()) * 4 // 1000000, K)}
     graph_replays = int(st["graph_replays"])
     dev.close()
 
