@@ -478,3 +478,25 @@ def test_checkpoint_of_kept_tensors_round_trips(tmp_path):
     w2 = step(dev, saved.reshape(-1).copy())
     ref = step(oracle(), np.asarray(step(oracle(), w0).val().get().data, np.float32))
     assert_rel("w after resume", w2.val().get(), ref.val().get(), 1e-5)
+
+
+def test_tensors_without_elements():
+    """A [0, 4] tensor through element-wise work, a sum and a concat with a non-empty tensor, executed twice (the second
+    time from the cached plan): shapes and values as the oracle has them."""
+    E = np.zeros(0, np.float32)
+
+    def prog(dev):
+        main = adb.ir.IRProcedure("main")
+        for c in [("CreateMat", E, [0, 4], "a"), ("CreateMat", np.arange(4, dtype=np.float32), [1, 4], "b"),
+                  ("ElwAdd", "a", "a", "c"), ("Sum", "a", "s"), ("ElwAdd", "b", "b", "d"),
+                  ("Concat", "a", "b", 0, "e"), ("Contigious", "e", "f")]:
+            main.push(c)
+        dep = ["c", "s", "d", "f"]
+        dev.execute(main, dep)
+        return {k: dev.get_tensor(k) for k in dep}
+    want = prog(oracle())
+    for _ in range(2):
+        got = prog(b200())
+        for k in want:
+            assert got[k].dim == want[k].dim, k
+            assert_exact(k, got[k], want[k])

@@ -438,3 +438,18 @@ def test_a_value_computed_twice_survives_a_loop_with_one_kernel_per_command(host
     kept = {d: dev.get_tensor(d) for d in dep}
     for flags in (0, 1):
         _compare(_interpret(hostcheck, tmp_path, dev.blobs[-1], flags, f"twice{flags}"), kept, 0.0)
+
+
+def test_tensors_without_elements(hostcheck, tmp_path):
+    """A [0, 4] tensor through element-wise work, a sum, a concat with a non-empty tensor: shapes come back as the oracle
+    has them, nothing is launched for the empty parts."""
+    E = np.zeros(0, np.float32)
+    proc, dep = _raw([("CreateMat", E, [0, 4], "a"), ("CreateMat", np.arange(4, dtype=np.float32), [1, 4], "b"),
+                      ("ElwAdd", "a", "a", "c"), ("Sum", "a", "s"), ("ElwAdd", "b", "b", "d"),
+                      ("Concat", "a", "b", 0, "e"), ("Contigious", "e", "f")], ["c", "s", "d", "f"])
+    dev = _Both()
+    dev.execute(proc, dep)
+    kept = {d: dev.get_tensor(d) for d in dep}
+    assert kept["c"].dim == [0, 4] and kept["s"].dim == [0] and kept["f"].dim == [1, 4]
+    for flags in (0, 1):
+        _compare(_interpret(hostcheck, tmp_path, dev.blobs[-1], flags, f"empty{flags}"), kept, 0.0)
