@@ -9,6 +9,7 @@
 
 #include <algorithm>
 #include <cstdio>
+#include <limits>
 #include <map>
 #include <set>
 #include <sstream>
@@ -1053,6 +1054,11 @@ class Lowerer {
     // the row reduction of a 2-d value `a` into the id c.res (also used by matrix-vector products)
     void lower_sum_node(const Cmd& c, Node* a, int red_op) {
         int64_t V = a->shape[0], R = a->shape[1];
+        if (R == 0) {
+            // nothing to reduce: the identity of the operation (the oracle's accumulators start there as well)
+            after_op(c.res, g_.constant(red_op == 1 ? -std::numeric_limits<float>::infinity() : 0.0f, {V}));
+            return;
+        }
         if (a->kind == N_CONST && (red_op == 1 || a->cval == 0.0f)) {
             after_op(c.res, g_.constant(a->cval, {V}));   // maximum of a constant row; sum of zeros
             return;
@@ -1220,6 +1226,11 @@ class Lowerer {
         int64_t M = a->shape[0], K = a->shape[1], N = b->shape[1];
         consume(c.a);
         consume(c.b);
+        // nothing to sum over, or nothing to produce: the product is all zeros / has no elements
+        if (K == 0 || M * N == 0) {
+            after_op(c.res, g_.constant(0.0f, {M, N}));
+            return;
+        }
         // Matrix times vector (or vector times matrix) is a row sum of products: one pass over the matrix at memory
         // speed through the reduce kernels, instead of a tile kernel that would keep one column of its tiles busy.
         // (Summation order differs from the dot kernels' k-ascending one, like every other reduction here.)
@@ -1322,6 +1333,10 @@ class Lowerer {
         const int64_t B = a->shape[0], M = a->shape[1], K = a->shape[2], N = b->shape[2];
         consume(c.a);
         consume(c.b);
+        if (K == 0 || B * M * N == 0) {
+            after_op(c.res, g_.constant(0.0f, {B, M, N}));
+            return;
+        }
         struct Op3 { int buf; int64_t off, bs, rs, cs; };
         auto operand = [&](Node* n) -> Op3 {
             n = g_.canon(n);

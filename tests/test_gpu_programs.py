@@ -489,9 +489,12 @@ def test_tensors_without_elements():
         main = adb.ir.IRProcedure("main")
         for c in [("CreateMat", E, [0, 4], "a"), ("CreateMat", np.arange(4, dtype=np.float32), [1, 4], "b"),
                   ("ElwAdd", "a", "a", "c"), ("Sum", "a", "s"), ("ElwAdd", "b", "b", "d"),
-                  ("Concat", "a", "b", 0, "e"), ("Contigious", "e", "f")]:
+                  ("Concat", "a", "b", 0, "e"), ("Contigious", "e", "f"),
+                  ("CreateMat", E, [3, 0], "p"), ("CreateMat", E, [0, 4], "q"), ("DotProduct", "p", "q", "pq"),
+                  ("CreateMat", np.ones(8, np.float32), [4, 2], "w"), ("DotProduct", "a", "w", "aw"),
+                  ("Sum", "p", "ps"), ("Max", "p", "pm")]:
             main.push(c)
-        dep = ["c", "s", "d", "f"]
+        dep = ["c", "s", "d", "f", "pq", "aw", "ps", "pm"]
         dev.execute(main, dep)
         return {k: dev.get_tensor(k) for k in dep}
     want = prog(oracle())

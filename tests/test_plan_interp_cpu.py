@@ -446,10 +446,19 @@ def test_tensors_without_elements(hostcheck, tmp_path):
     E = np.zeros(0, np.float32)
     proc, dep = _raw([("CreateMat", E, [0, 4], "a"), ("CreateMat", np.arange(4, dtype=np.float32), [1, 4], "b"),
                       ("ElwAdd", "a", "a", "c"), ("Sum", "a", "s"), ("ElwAdd", "b", "b", "d"),
-                      ("Concat", "a", "b", 0, "e"), ("Contigious", "e", "f")], ["c", "s", "d", "f"])
+                      ("Concat", "a", "b", 0, "e"), ("Contigious", "e", "f"),
+                      # products and sums over an axis of length 0 (all zeros; -inf for a maximum) and with no rows
+                      ("CreateMat", E, [3, 0], "p"), ("CreateMat", E, [0, 4], "q"), ("DotProduct", "p", "q", "pq"),
+                      ("CreateMat", np.ones(8, np.float32), [4, 2], "w"), ("DotProduct", "a", "w", "aw"),
+                      ("Sum", "p", "ps"), ("Max", "p", "pm")], ["c", "s", "d", "f", "pq", "aw", "ps", "pm"])
     dev = _Both()
     dev.execute(proc, dep)
     kept = {d: dev.get_tensor(d) for d in dep}
     assert kept["c"].dim == [0, 4] and kept["s"].dim == [0] and kept["f"].dim == [1, 4]
-    for flags in (0, 1):
-        _compare(_interpret(hostcheck, tmp_path, dev.blobs[-1], flags, f"empty{flags}"), kept, 0.0)
+    assert kept["pq"].dim == [3, 4] and not kept["pq"].numpy().any() and kept["aw"].dim == [0, 2]
+    assert np.isneginf(kept["pm"].numpy()).all() and not kept["ps"].numpy().any()
+    for flags in (0, 1, 128):
+        got = _interpret(hostcheck, tmp_path, dev.blobs[-1], flags, f"empty{flags}")
+        for k, v in kept.items():
+            assert got[k][0] == list(v.dim), k
+            np.testing.assert_array_equal(got[k][1], v.numpy().reshape(-1), err_msg=k)
