@@ -174,3 +174,44 @@ def test_products_of_a_few_multiply_adds_become_element_wise_expressions():
     unfused = _LowerOnly(flags=adb.devices.FLAG_NO_FUSION)
     adb.configs.c1_readme_mlp(unfused)
     assert sum(" gemm " in l for l in unfused.plan.splitlines()) == 6
+
+
+_M6 = np.arange(6, dtype=np.float32)
+_BAD = {
+    "element-wise operands of different size": ([("ElwAdd", "a", "v", "r")], "differ in size"),
+    "index beyond the axis": ([("Index", "a", 5, 0, "r")], "Index out of range"),
+    "index on an axis that does not exist": ([("Index", "a", 0, 7, "r")], "Index out of range"),
+    "view that changes the element count": ([("View", "a", [4, 2], "r")], "changes the element count"),
+    "permute of the wrong rank": ([("Permute", "a", [0], "r")], "Permute rank mismatch"),
+    "permute that repeats an axis": ([("Permute", "a", [0, 0], "r")], "not a permutation"),
+    "concat of different ranks": ([("Concat", "a", "v", 0, "r")], "Concat rank mismatch"),
+    "dot product with unequal inner dimensions": ([("DotProduct", "a", "a", "r")], "second dimension must equal"),
+    "dot product of a vector": ([("DotProduct", "a", "v", "r")], "must be a 2d array"),
+    "sum of a vector": ([("Sum", "v", "r")], "needs dim=2"),
+    "broadcast of an axis longer than 1": ([("Broadcast", "a", 0, 4, "r")], "length-1 axis"),
+    "loop condition that is not one float": ([("While", "a", [("ElwAddEq", "a", "a")])], "must have dim of [1]"),
+    "batched product of matrices": ([("BatchDot", "a", "b", "r")], "3-d operands"),
+    "alias written onto its own operand": ([("Permute", "a", [1, 0], "a")], "its own operand"),
+}
+
+
+@pytest.mark.parametrize("case", sorted(_BAD))
+def test_malformed_programs_are_refused_with_a_reason(case):
+    """What the reference answers with a panic (`expect` / `panic!` in its lowering and its device), the boundary answers
+    with ADB_ERR_INVALID and a sentence that names the command: never a crash, never a silent result."""
+    ir = adb.ir
+    cmds, reason = _BAD[case]
+    proc = ir.IRProcedure("main")
+    proc.push(("CreateMat", _M6, [2, 3], "a"))
+    proc.push(("CreateMat", _M6 * 2, [3, 2], "b"))
+    proc.push(("CreateMat", np.arange(4, dtype=np.float32), [4], "v"))
+    for c in cmds:
+        if c[0] == "While":
+            body = ir.IRProcedure("body")
+            for bc in c[2]:
+                body.push(bc)
+            c = ("While", c[1], body)
+        proc.push(c)
+    with pytest.raises(adb.devices.AdbError) as e:
+        adb.devices.lower_check(proc, {"r"} if any(c[-1] == "r" for c in cmds) else {"a"})
+    assert e.value.status == 2 and reason in str(e.value), str(e.value)
