@@ -525,7 +525,7 @@ adb_dot_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                 // Every byte less through shared memory counts: the MMAs' own operand reads take 3/4 of its bandwidth.
                 const uint4* raw = reinterpret_cast<const uint4*>(gen_base + s * STAGE_BYTES);
                 uint4* lo = reinterpret_cast<uint4*>(gen_base + s * STAGE_BYTES + A_BYTES + B_BYTES);
-#pragma unroll 4
+#pragma unroll 8
                 for (int i = t; i < (A_BYTES + B_BYTES) / 16; i += 128) {
                     const uint4 v = raw[i];
                     uint4 l;
@@ -802,7 +802,7 @@ adb_dot_tc_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 if (!mbar_wait_warp(bar_raw(s), ph, stop, p.status, TIMEOUT_RAW)) { ok = false; break; }
                 const uint4* raw = reinterpret_cast<const uint4*>(gen_base + s * PSTAGE_BYTES);
                 uint4* lo = reinterpret_cast<uint4*>(gen_base + s * PSTAGE_BYTES + RAW_BYTES);
-#pragma unroll 4
+#pragma unroll 16
                 for (int i = t; i < RAW_BYTES / 16; i += 128) {
                     const uint4 v = raw[i];
                     uint4 l;
