@@ -45,6 +45,27 @@ extern "C" {
 /// Payloads larger than this travel by address instead of being copied into the blob.
 const INLINE_LIMIT: usize = 1 << 16;
 
+/// `adb_config.flags` (include/adb200.h); 0 is the fast path, the rest are switches for debugging, tests and callers
+/// with special needs.
+pub mod flags {
+    pub const NO_GRAPHS: u32 = 1;
+    pub const NO_FUSION: u32 = 2;
+    pub const SIMT_DOT: u32 = 4;
+    pub const PROFILE: u32 = 8;
+    pub const COMM_STREAM: u32 = 16;
+    pub const SINGLE_SM_DOT: u32 = 32;
+    pub const EXACT_DIV: u32 = 64;
+    pub const FUSE_SMALL_SUMS: u32 = 128;
+    pub const NO_GROUPING: u32 = 256;
+    /// dot products never split their k axis over clusters: the same bits on every run
+    pub const DETERMINISTIC: u32 = 512;
+    pub const SERIAL_GRAPHS: u32 = 1024;
+    pub const NO_BUCKETS: u32 = 2048;
+    pub const NO_TINY_DOT: u32 = 4096;
+    /// accumulate 1024 instead of 4096 k elements per chunk in the dot kernels: 8e-6 instead of 3e-5 of max|C|, 9 % slower
+    pub const SHORT_DOT_CHUNKS: u32 = 8192;
+}
+
 pub struct B200 {
     h: *mut c_void,
     /// the program captured by `ir_callback`; it owns the `CreateMat` vectors the blob points into
