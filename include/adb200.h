@@ -95,6 +95,8 @@ typedef struct adb_config {
 #define ADB_FLAG_FUSE_SMALL_SUMS 128u /* fold sums into neighbouring element-wise kernels whatever their size (by default
                                          only above 2^18 elements and 128 columns, where it pays); lets small tests reach
                                          that path */
+#define ADB_FLAG_NO_GROUPING 256u     /* every generated kernel in a launch of its own (by default independent kernels
+                                         that follow one another share one grid) */
 #define ADB_FLAG_DETERMINISTIC 512u    /* dot products never split the k axis across clusters: by default a product with few
                                          output tiles and a long k axis is cut into k ranges whose partial sums meet in C
                                          through red.global.add, in an order that depends on timing (results then differ
@@ -110,8 +112,6 @@ typedef struct adb_config {
                                          of every 4096: the tensor core truncates when it accumulates, so the error
                                          relative to max|C| drops from 3e-5 to 8e-6 (the contract is 1e-4), at ~9 % of the
                                          dot products' speed */
-#define ADB_FLAG_NO_GROUPING 256u     /* every generated kernel in a launch of its own (by default independent kernels
-                                         that follow one another share one grid) */
 
 /* Replaces OpenCL::new (src/devices/opencl/device.rs:41-58) + autodiff::set_device's device slot
  * (src/core/autodiff.rs:82-97).  Fails with ADB_ERR_NO_DEVICE when no GPU is present. */
